@@ -1,0 +1,152 @@
+/* sapa_b200.h — C ABI of libsapa_b200.so: SAPA upsampling kernels for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point replaces one function of the reference's pybind11 extension modules and follows
+ * their ownership rule: the CALLER allocates every tensor, the library allocates nothing, keeps no
+ * reference and writes results in place.  What differs from the reference:
+ *   - plain device pointers + sizes + a dtype code + a CUDA stream instead of at::Tensor;
+ *   - launches go to the stream passed in (the reference uses the legacy default stream);
+ *   - an int status is returned and the text is available from sapa_last_error(); the process is
+ *     never terminated (the reference calls exit(-1) on a launch error, qk_cuda_kernel.cu:92-96);
+ *   - gradient outputs are OVERWRITTEN (the reference accumulates with atomics into buffers the caller
+ *     must have zeroed); zeroing them first is unnecessary but harmless.
+ *
+ * Layout: all tensors are dense NCHW, as the reference requires (CHECK_CONTIGUOUS, qk_cuda.cpp:34-39).
+ * H and W are always the LOW-resolution (key / value) height and width; query, attention, offset and
+ * output tensors are s*H x s*W.  Window slot k = dy*K+dx addresses the low-res neighbour
+ * (ph/s - (K-1)/2 + dy, pw/s - (K-1)/2 + dx); neighbours outside the image contribute zero
+ * (qk_cuda_kernel.cu:50-66, av_cuda_kernel.cu:57-61).
+ *
+ * Pointers must be aligned to 16 bytes.  `stream` is a cudaStream_t passed as void* (NULL = default
+ * stream).  The current CUDA device must be the one that owns the pointers.  Functions are re-entrant
+ * and do not synchronise.
+ */
+#ifndef SAPA_B200_H_
+#define SAPA_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype codes (element type of every tensor of a call) */
+#define SAPA_F32  0
+#define SAPA_F16  1
+#define SAPA_BF16 2
+#define SAPA_F64  3   /* generic kernels only; kept so that float64 gradcheck scripts run (grad_check.py:17-22) */
+
+/* status codes */
+#define SAPA_OK               0
+#define SAPA_ERR_ARGUMENT    -1   /* null pointer, non-positive size, even K, d % G != 0 ... */
+#define SAPA_ERR_DTYPE       -2
+#define SAPA_ERR_ALIGNMENT   -3
+#define SAPA_ERR_LAUNCH      -4   /* cudaGetLastError() after the launch; text in sapa_last_error() */
+#define SAPA_ERR_UNSUPPORTED -5   /* no kernel for this (K, s, P) in the fused path: use the separate ops */
+#define SAPA_ERR_WORKSPACE   -6   /* workspace missing or too small */
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char *sapa_last_error(void);
+/* ABI version of this header (bumped on any signature change). */
+int sapa_abi_version(void);
+
+/* ------------------------------------------------------------------ SAPA-B, separate ops ------------- */
+
+/* sim: out[B,K*K,sH,sW] = local query.key similarity.
+ * Replaces qk_forward(features=key, masks=query, K, s, output)  — sapa/sapa/src/qk_ext.cpp:22-34,
+ * qk_forward_cuda qk_cuda.cpp:41-60, QKForwardLauncher qk_cuda_kernel.cu:71-99. d = query channels. */
+int sapa_qk_forward(const void *query, const void *key, void *out,
+                    int B, int d, int H, int W, int K, int s, int dtype, void *stream);
+
+/* Gradients of sim.  Replaces qk_backward(top_grad, key, query, K, s, grad_key, grad_query)
+ * — qk_ext.cpp:36-50, qk_backward_cuda qk_cuda.cpp:62-84, QKBackwardLauncher qk_cuda_kernel.cu:139-171.
+ * Deterministic (gather form, no atomics). */
+int sapa_qk_backward(const void *grad_out, const void *query, const void *key,
+                     void *grad_query, void *grad_key,
+                     int B, int d, int H, int W, int K, int s, int dtype, void *stream);
+
+/* atn: out[B,C,sH,sW] = attention-weighted sum over the K x K value window.
+ * Replaces av_forward(features=value, masks=attn, K, s, output) — sapa/sapa/src/av_ext.cpp:18-30,
+ * av_forward_cuda av_cuda.cpp:28-47, AVForwardLauncher av_cuda_kernel.cu:77-101. */
+int sapa_av_forward(const void *attn, const void *value, void *out,
+                    int B, int C, int H, int W, int K, int s, int dtype, void *stream);
+
+/* Gradients of atn.  Replaces av_backward(top_grad, value, attn, K, s, grad_value, grad_attn)
+ * — av_ext.cpp:32-46, av_backward_cuda av_cuda.cpp:49-70, AVBackwardLauncher av_cuda_kernel.cu:150-181.
+ * Deterministic (gather form, no atomics). */
+int sapa_av_backward(const void *grad_out, const void *attn, const void *value,
+                     void *grad_attn, void *grad_value,
+                     int B, int C, int H, int W, int K, int s, int dtype, void *stream);
+
+/* ------------------------------------------------------------------ SAPA-B, fused --------------------- */
+
+/* out = atn(softmax_k(sim(query, key)), value) in one kernel: what SAPA.attention computes with three
+ * launches and two HBM round trips of the attention map (sapa_base.py:38-40).  `attn` may be NULL
+ * (inference); when given, the [B,K*K,sH,sW] softmax output is also stored for the backward pass.
+ * Returns SAPA_ERR_UNSUPPORTED for (K, s) without a fused kernel (supported: K in {3,5}, s = 2, and
+ * dtype != SAPA_F64). */
+int sapa_fused_forward(const void *query, const void *key, const void *value, void *out, void *attn,
+                       int B, int d, int C, int H, int W, int K, int s, int dtype, void *stream);
+
+/* Row-slab form of sapa_fused_forward for one spatial shard of a larger image: key and value hold
+ * `halo_top` extra low-res rows above and `halo_bottom` below the H rows whose outputs are produced
+ * (so they are [B, ., halo_top+H+halo_bottom, W]); rows beyond those halos read as zero.  With a halo of
+ * (K-1)/2 rows taken from the neighbouring shards the result equals the matching rows of the unsharded
+ * call.  No counterpart in the reference (it has no multi-device code). */
+int sapa_fused_forward_slab(const void *query, const void *key, const void *value, void *out, void *attn,
+                            int B, int d, int C, int H, int W, int halo_top, int halo_bottom,
+                            int K, int s, int dtype, void *stream);
+
+/* Bytes of scratch sapa_fused_backward needs (grad of the logits, [B,K*K,sH,sW] elements of dtype). */
+size_t sapa_fused_backward_workspace(int B, int H, int W, int K, int s, int dtype);
+
+/* Gradients of the fused op with respect to query, key and value from grad_out and the attention map
+ * saved by sapa_fused_forward: the chain AVBackward -> softmax backward -> QKBackward of the reference
+ * (sapa_func.py:80-93, 35-48).  Works for every odd K and s >= 1.  Deterministic. */
+int sapa_fused_backward(const void *grad_out, const void *query, const void *key, const void *value,
+                        const void *attn, void *grad_query, void *grad_key, void *grad_value,
+                        void *workspace, size_t workspace_bytes,
+                        int B, int d, int C, int H, int W, int K, int s, int dtype, void *stream);
+
+/* ------------------------------------------------------------------ SAPA-D (deformable) -------------- */
+/* offset is [B, G*P*2, sH, sW]; channel 2*(g*P+p) is the x (w) offset and 2*(g*P+p)+1 the y (h) offset,
+ * in low-res pixels, added to the integer parent index (qh/s, qw/s) (deform_qk_cuda_kernel.cu:172-183).
+ * Sampling is bilinear with zero outside the image; a point outside (-1,H)x(-1,W) contributes nothing. */
+
+/* out[B,G,P,sH,sW].  Replaces deform_qk_forward(query,key,offset,P,s,G,output) — deformsapa/deformsapa/
+ * src/deform_qk.cpp:32-48, deform_qk_forward_cuda deform_qk_cuda.cpp:45-68, launcher
+ * deform_qk_cuda_kernel.cu:199-230.  Cq = number of query/key channels (all groups). */
+int sapa_deform_qk_forward(const void *query, const void *key, const void *offset, void *out,
+                           int B, int Cq, int H, int W, int P, int s, int G, int dtype, void *stream);
+
+/* Replaces deform_qk_backward(top_grad,query,key,offset,P,s,G,grad_query,grad_key,grad_offset)
+ * — deform_qk.cpp:50-70, deform_qk_cuda.cpp:70-100, launcher deform_qk_cuda_kernel.cu:298-337.
+ * grad_query and grad_key are accumulated with atomics (data-dependent scatter), so for SAPA_F16 /
+ * SAPA_BF16 they must be FLOAT32 buffers of the same shape (the caller casts afterwards); grad_offset
+ * has the call's dtype.  All three are overwritten. */
+int sapa_deform_qk_backward(const void *grad_out, const void *query, const void *key, const void *offset,
+                            void *grad_query, void *grad_key, void *grad_offset,
+                            int B, int Cq, int H, int W, int P, int s, int G, int dtype, void *stream);
+
+/* out[B,C,sH,sW].  Replaces deform_av_forward(attn,value,offset,P,s,G,output) — deform_av.cpp:32-48,
+ * deform_av_cuda.cpp:45-68, launcher deform_av_cuda_kernel.cu:197-228. */
+int sapa_deform_av_forward(const void *attn, const void *value, const void *offset, void *out,
+                           int B, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
+
+/* Replaces deform_av_backward(top_grad,attn,value,offset,P,s,G,grad_attn,grad_value,grad_offset)
+ * — deform_av.cpp:50-70, deform_av_cuda.cpp:70-100, launcher deform_av_cuda_kernel.cu:294-333.
+ * grad_value is a scatter target: FLOAT32 buffer for SAPA_F16 / SAPA_BF16.  All three are overwritten. */
+int sapa_deform_av_backward(const void *grad_out, const void *attn, const void *value, const void *offset,
+                            void *grad_attn, void *grad_value, void *grad_offset,
+                            int B, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
+
+/* out = deform_av(softmax_p(deform_qk(query, key, offset)), value, offset) in one kernel — what
+ * SAPADeform.attention computes with three launches (sapa_deform.py:51-53).  `attn` ([B,G,P,sH,sW]) may
+ * be NULL.  Supported: P <= 16, dtype != SAPA_F64; otherwise SAPA_ERR_UNSUPPORTED. */
+int sapa_deform_fused_forward(const void *query, const void *key, const void *value, const void *offset,
+                              void *out, void *attn,
+                              int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAPA_B200_H_ */

@@ -1,0 +1,114 @@
+"""ctypes binding of ``libsapa_b200.so`` (the C ABI declared in ``include/sapa_b200.h``).
+
+There is no CPU or PyTorch fallback: if the library cannot be loaded the import of any op fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsapa_b200.so")
+
+SAPA_F32, SAPA_F16, SAPA_BF16, SAPA_F64 = 0, 1, 2, 3
+_DTYPE_CODE = {torch.float32: SAPA_F32, torch.float16: SAPA_F16, torch.bfloat16: SAPA_BF16, torch.float64: SAPA_F64}
+SAPA_ERR_UNSUPPORTED = -5
+ABI_VERSION = 1
+
+_lib = None
+
+_vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+# name -> argument types; every function returns int except the two noted below
+_SIGNATURES = {
+    "sapa_qk_forward": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_qk_backward": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_av_forward": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_av_backward": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_fused_forward": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_fused_forward_slab": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_fused_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_deform_qk_forward": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_deform_qk_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_deform_av_forward": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_deform_av_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_deform_fused_forward": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+}
+EXPORTS = sorted(list(_SIGNATURES) + ["sapa_last_error", "sapa_abi_version", "sapa_fused_backward_workspace"])
+
+
+def lib() -> ctypes.CDLL:
+    """Load (building first if the toolkit is present and the library is missing) and type the library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        try:
+            from . import build as _build
+            _build.build()
+        except Exception as exc:  # no nvcc on this machine
+            raise RuntimeError(
+                f"libsapa_b200.so is missing at {LIB_PATH} and could not be built ({exc}); "
+                "run `python -m sapa_b200.build` on a machine with the CUDA toolkit. "
+                "There is no CPU fallback.") from exc
+    handle = ctypes.CDLL(LIB_PATH)
+    for name, argtypes in _SIGNATURES.items():
+        fn = getattr(handle, name)
+        fn.argtypes = argtypes
+        fn.restype = ctypes.c_int
+    handle.sapa_last_error.argtypes = []
+    handle.sapa_last_error.restype = ctypes.c_char_p
+    handle.sapa_abi_version.argtypes = []
+    handle.sapa_abi_version.restype = ctypes.c_int
+    handle.sapa_fused_backward_workspace.argtypes = [_i, _i, _i, _i, _i, _i]
+    handle.sapa_fused_backward_workspace.restype = ctypes.c_size_t
+    if handle.sapa_abi_version() != ABI_VERSION:
+        raise RuntimeError("libsapa_b200.so has a different ABI version than this Python package; rebuild it")
+    _lib = handle
+    return _lib
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"sapa_b200: unsupported dtype {t.dtype}") from None
+
+
+def check_tensors(*named: tuple[str, torch.Tensor]) -> None:
+    """The reference's CHECK_INPUT (CUDA + contiguous, qk_cuda.cpp:34-39) plus same dtype / device."""
+    first = named[0][1]
+    for name, t in named:
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+        if t.dtype != first.dtype:
+            raise RuntimeError(f"{name} has dtype {t.dtype}, expected {first.dtype} (all tensors of a call share one dtype)")
+        if t.device != first.device:
+            raise RuntimeError(f"{name} is on {t.device}, expected {first.device}")
+
+
+def _arg(a):
+    if isinstance(a, torch.Tensor):
+        return ctypes.c_void_p(a.data_ptr())
+    return a
+
+
+def call(name: str, device: torch.device, *args, allow_unsupported: bool = False) -> int:
+    """Invoke one C entry point on ``device``'s current stream; raises RuntimeError on a failure status."""
+    handle = lib()
+    with torch.cuda.device(device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        status = getattr(handle, name)(*[_arg(a) for a in args], stream)
+    if status != 0:
+        if allow_unsupported and status == SAPA_ERR_UNSUPPORTED:
+            return status
+        msg = handle.sapa_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{name} failed with status {status}: {msg}")
+    return 0
+
+
+def fused_backward_workspace(B, H, W, K, s, code) -> int:
+    return int(lib().sapa_fused_backward_workspace(B, H, W, K, s, code))

@@ -1,0 +1,382 @@
+// sapa_d.cu — SAPA-D (deformable) kernels: similarity and aggregation at per-pixel learned sampling
+// points, forward and backward, plus the fused forward.
+//
+// Every high-res pixel (qh, qw) samples, for each group g and point p, the low-res key / value plane at
+//   (h, w) = (qh / s + off_h, qw / s + off_w)          off_w = offset[b, 2(gP+p)], off_h = offset[b, 2(gP+p)+1]
+// bilinearly; a corner outside the plane reads 0 and a point outside (-1,H) x (-1,W) contributes nothing
+// (forward and backward).  Because the sampling positions are data dependent the key/value gradients are a
+// scatter: they use float atomics into a float32 (float64 for f64) accumulation buffer.  The gradients of
+// the query, the attention and the offsets are owned by one thread each and written without atomics
+// (query: P threads of a group add to one element, so it accumulates too).
+#include "common.cuh"
+
+namespace sapa {
+
+constexpr int MAXP = 16;   // largest num_point handled by the fused kernel
+
+// Bilinear footprint of one sampling point in an H x W plane.
+template <typename A>
+struct Bilinear {
+    int i00, i01, i10, i11;   // plane offsets of the four corners, -1 when the corner is outside
+    A w00, w01, w10, w11;     // corner weights
+    A lh, lw;                 // fractional parts (for the offset derivatives)
+    bool inside;              // the reference's outer guard: -1 < h < H and -1 < w < W
+
+    __device__ __forceinline__ void setup(A h, A w, int H, int W) {
+        inside = (h > A(-1)) && (h < A(H)) && (w > A(-1)) && (w < A(W));
+        const A fh = floor(h), fw = floor(w);
+        const int h0 = (int)fh, w0 = (int)fw, h1 = h0 + 1, w1 = w0 + 1;
+        lh = h - fh;
+        lw = w - fw;
+        const A hh = A(1) - lh, hw = A(1) - lw;
+        w00 = hh * hw; w01 = hh * lw; w10 = lh * hw; w11 = lh * lw;
+        const bool t = h0 >= 0, b = h1 <= H - 1, l = w0 >= 0, r = w1 <= W - 1;
+        i00 = (inside && t && l) ? h0 * W + w0 : -1;
+        i01 = (inside && t && r) ? h0 * W + w1 : -1;
+        i10 = (inside && b && l) ? h1 * W + w0 : -1;
+        i11 = (inside && b && r) ? h1 * W + w1 : -1;
+    }
+    template <typename T>
+    __device__ __forceinline__ void corners(const T *__restrict__ plane, A &v00, A &v01, A &v10, A &v11) const {
+        v00 = i00 >= 0 ? to_acc(__ldg(plane + i00)) : A(0);
+        v01 = i01 >= 0 ? to_acc(__ldg(plane + i01)) : A(0);
+        v10 = i10 >= 0 ? to_acc(__ldg(plane + i10)) : A(0);
+        v11 = i11 >= 0 ? to_acc(__ldg(plane + i11)) : A(0);
+    }
+    template <typename T>
+    __device__ __forceinline__ A sample(const T *__restrict__ plane) const {
+        A v00, v01, v10, v11;
+        corners(plane, v00, v01, v10, v11);
+        return w00 * v00 + w01 * v01 + w10 * v10 + w11 * v11;
+    }
+};
+
+// ---------------------------------------------------------------------------------- forward, separate ops
+
+// one thread per (b, k = g*P+p, qh, qw)
+template <typename T>
+__global__ void deform_qk_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ offset,
+                                     T *__restrict__ out, int B, int Cq, int H, int W, int P, int s, int G) {
+    using A = typename AccOf<T>::type;
+    const int sH = s * H, sW = s * W, AC = G * P, gc = Cq / G;
+    const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
+    const long long total = (long long)B * AC * hi;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const size_t pix = (size_t)(i % hi);
+        const int qw = (int)(pix % sW), qh = (int)(pix / sW);
+        const int k = (int)((i / hi) % AC);
+        const int b = (int)(i / (hi * AC));
+        const int g = k / P;
+        const T *op = offset + ((size_t)b * AC + k) * 2 * hi + pix;
+        Bilinear<A> bl;
+        bl.setup(A(qh / s) + to_acc(op[hi]), A(qw / s) + to_acc(op[0]), H, W);
+        A acc = 0;
+        if (bl.inside) {
+            const T *qp = query + ((size_t)b * Cq + (size_t)g * gc) * hi + pix;
+            const T *kp = key + ((size_t)b * Cq + (size_t)g * gc) * lo;
+            for (int c = 0; c < gc; ++c) acc += bl.sample(kp + (size_t)c * lo) * to_acc(qp[(size_t)c * hi]);
+        }
+        out[i] = from_acc<T>(acc);
+    }
+}
+
+// one thread per (b, chunk of CPT channels of one group, qh, qw): sampling set-up shared by CPT channels
+template <typename T, int CPT>
+__global__ void deform_av_fwd_kernel(const T *__restrict__ attn, const T *__restrict__ value, const T *__restrict__ offset,
+                                     T *__restrict__ out, int B, int C, int H, int W, int P, int s, int G) {
+    using A = typename AccOf<T>::type;
+    const int sH = s * H, sW = s * W, AC = G * P, gc = C / G;
+    const int chunks = (gc + CPT - 1) / CPT;
+    const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
+    const long long total = (long long)B * G * chunks * hi;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const size_t pix = (size_t)(i % hi);
+        const int qw = (int)(pix % sW), qh = (int)(pix / sW);
+        long long t = i / hi;
+        const int ck = (int)(t % chunks); t /= chunks;
+        const int g = (int)(t % G);
+        const int b = (int)(t / G);
+        const int c0 = g * gc + ck * CPT;
+        const int nc = min(CPT, gc - ck * CPT);
+        A o[CPT];
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) o[j] = 0;
+        const T *vp = value + ((size_t)b * C + c0) * lo;
+        for (int p = 0; p < P; ++p) {
+            const size_t k = (size_t)b * AC + (size_t)g * P + p;
+            Bilinear<A> bl;
+            bl.setup(A(qh / s) + to_acc(offset[k * 2 * hi + hi + pix]), A(qw / s) + to_acc(offset[k * 2 * hi + pix]), H, W);
+            if (!bl.inside) continue;
+            const A a = to_acc(attn[k * hi + pix]);
+#pragma unroll
+            for (int j = 0; j < CPT; ++j)
+                if (j < nc) o[j] += bl.sample(vp + (size_t)j * lo) * a;
+        }
+#pragma unroll
+        for (int j = 0; j < CPT; ++j)
+            if (j < nc) out[((size_t)b * C + c0 + j) * hi + pix] = from_acc<T>(o[j]);
+    }
+}
+
+// ---------------------------------------------------------------------------------- forward, fused
+// one thread per (b, g, qh, qw): logits of the P points -> softmax over the points -> aggregation of the
+// group's value channels.  The attention never leaves registers unless `attn_out` is given.
+template <typename T, int CPT>
+__global__ void deform_fused_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ value,
+                                        const T *__restrict__ offset, T *__restrict__ out, T *__restrict__ attn_out,
+                                        int B, int Cq, int C, int H, int W, int P, int s, int G) {
+    const int sH = s * H, sW = s * W, AC = G * P, gq = Cq / G, gc = C / G;
+    const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
+    const long long total = (long long)B * G * hi;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const size_t pix = (size_t)(i % hi);
+        const int qw = (int)(pix % sW), qh = (int)(pix / sW);
+        const int g = (int)((i / hi) % G);
+        const int b = (int)(i / (hi * G));
+        const T *qp = query + ((size_t)b * Cq + (size_t)g * gq) * hi + pix;
+        const T *kp = key + ((size_t)b * Cq + (size_t)g * gq) * lo;
+        const T *op = offset + ((size_t)b * AC + (size_t)g * P) * 2 * hi + pix;
+        float a[MAXP], oh[MAXP], ow[MAXP];
+        float m = -INFINITY;
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p) {
+            a[p] = 0.f; oh[p] = 0.f; ow[p] = 0.f;
+            if (p < P) {
+                ow[p] = float(qw / s) + to_acc(op[(size_t)(2 * p) * hi]);
+                oh[p] = float(qh / s) + to_acc(op[(size_t)(2 * p + 1) * hi]);
+                Bilinear<float> bl;
+                bl.setup(oh[p], ow[p], H, W);
+                float acc = 0.f;
+                if (bl.inside)
+                    for (int c = 0; c < gq; ++c) acc += bl.sample(kp + (size_t)c * lo) * to_acc(qp[(size_t)c * hi]);
+                a[p] = acc;
+                m = fmaxf(m, acc);
+            }
+        }
+        float z = 0.f;
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p)
+            if (p < P) { a[p] = expf(a[p] - m); z += a[p]; }
+        const float inv = 1.f / z;
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p)
+            if (p < P) {
+                a[p] *= inv;
+                if (attn_out != nullptr) attn_out[((size_t)b * AC + (size_t)g * P + p) * hi + pix] = from_acc<T>(a[p]);
+            }
+        // aggregation, CPT value channels at a time
+        for (int c0 = 0; c0 < gc; c0 += CPT) {
+            const T *vp = value + ((size_t)b * C + (size_t)g * gc + c0) * lo;
+            const int nc = min(CPT, gc - c0);
+            float o[CPT];
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) o[j] = 0.f;
+#pragma unroll
+            for (int p = 0; p < MAXP; ++p)
+                if (p < P) {
+                    Bilinear<float> bl;
+                    bl.setup(oh[p], ow[p], H, W);
+                    if (bl.inside) {
+#pragma unroll
+                        for (int j = 0; j < CPT; ++j)
+                            if (j < nc) o[j] += bl.sample(vp + (size_t)j * lo) * a[p];
+                    }
+                }
+#pragma unroll
+            for (int j = 0; j < CPT; ++j)
+                if (j < nc) out[((size_t)b * C + (size_t)g * gc + c0 + j) * hi + pix] = from_acc<T>(o[j]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------- backward
+// one thread per (b, k, qh, qw), looping over the channels of group g(k).
+//   QK: top = dS[b,k,pix], weight_c = Q[b,c,pix]:   dQ_c += top*val_c (atomic), dKey_c[corner] += w*top*Q_c (atomic)
+//   AV: top_c = dOut[b,c,pix], weight = A[b,k,pix]: dA = sum_c top_c*val_c,     dV_c[corner]   += w*top_c*A (atomic)
+// and in both: dOff_w = sum_c (d val_c / d w) * top * weight, dOff_h likewise.
+template <typename T, bool IS_QK>
+__global__ void deform_bwd_kernel(const T *__restrict__ top, const T *__restrict__ hires /* Q | A */,
+                                  const T *__restrict__ plane_src /* Key | V */, const T *__restrict__ offset,
+                                  typename AccOf<T>::type *__restrict__ grad_hi_acc /* dQ (QK only) */,
+                                  T *__restrict__ grad_attn /* dA (AV only) */,
+                                  typename AccOf<T>::type *__restrict__ grad_plane /* dKey | dV */,
+                                  T *__restrict__ grad_offset, int B, int Cc, int H, int W, int P, int s, int G) {
+    using A = typename AccOf<T>::type;
+    const int sH = s * H, sW = s * W, AC = G * P, gc = Cc / G;
+    const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
+    const long long total = (long long)B * AC * hi;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const size_t pix = (size_t)(i % hi);
+        const int qw = (int)(pix % sW), qh = (int)(pix / sW);
+        const int k = (int)((i / hi) % AC);
+        const int b = (int)(i / (hi * AC));
+        const int g = k / P;
+        const size_t off_idx = ((size_t)b * AC + k) * 2 * hi + pix;
+        Bilinear<A> bl;
+        bl.setup(A(qh / s) + to_acc(offset[off_idx + hi]), A(qw / s) + to_acc(offset[off_idx]), H, W);
+        A g_w = 0, g_h = 0, g_attn = 0;
+        if (bl.inside) {
+            const A hh = A(1) - bl.lh, hw = A(1) - bl.lw;
+            const size_t ch0 = (size_t)b * Cc + (size_t)g * gc;
+            const A top_k = IS_QK ? to_acc(top[i]) : A(0);
+            const A wt_k = IS_QK ? A(0) : to_acc(hires[i]);
+            for (int c = 0; c < gc; ++c) {
+                const T *pl = plane_src + (ch0 + c) * lo;
+                A v00, v01, v10, v11;
+                bl.corners(pl, v00, v01, v10, v11);
+                const A val = bl.w00 * v00 + bl.w01 * v01 + bl.w10 * v10 + bl.w11 * v11;
+                A t, wt;
+                if (IS_QK) {
+                    t = top_k;
+                    wt = to_acc(hires[(ch0 + c) * hi + pix]);
+                    atomic_add(grad_hi_acc + (ch0 + c) * hi + pix, t * val);
+                } else {
+                    t = to_acc(top[(ch0 + c) * hi + pix]);
+                    wt = wt_k;
+                    g_attn += t * val;
+                }
+                const A tw = t * wt;
+                A *gp = grad_plane + (ch0 + c) * lo;
+                if (bl.i00 >= 0) atomic_add(gp + bl.i00, bl.w00 * tw);
+                if (bl.i01 >= 0) atomic_add(gp + bl.i01, bl.w01 * tw);
+                if (bl.i10 >= 0) atomic_add(gp + bl.i10, bl.w10 * tw);
+                if (bl.i11 >= 0) atomic_add(gp + bl.i11, bl.w11 * tw);
+                g_w += (-hh * v00 + hh * v01 - bl.lh * v10 + bl.lh * v11) * tw;
+                g_h += (-hw * v00 - bl.lw * v01 + hw * v10 + bl.lw * v11) * tw;
+            }
+        }
+        grad_offset[off_idx] = from_acc<T>(g_w);
+        grad_offset[off_idx + hi] = from_acc<T>(g_h);
+        if (!IS_QK) grad_attn[i] = from_acc<T>(g_attn);
+    }
+}
+
+static inline int grid_1d(long long total, int threads) {
+    long long blocks = (total + threads - 1) / threads;
+    const long long cap = 148LL * 64;
+    return (int)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+
+static int check_deform(const char *fn, int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype) {
+    SAPA_REQUIRE(B > 0 && Cq > 0 && C > 0 && H > 0 && W > 0, SAPA_ERR_ARGUMENT, "%s: sizes must be positive", fn);
+    SAPA_REQUIRE(P >= 1, SAPA_ERR_ARGUMENT, "%s: num_point must be >= 1, got %d", fn, P);
+    SAPA_REQUIRE(s >= 1, SAPA_ERR_ARGUMENT, "%s: scale_factor must be >= 1, got %d", fn, s);
+    SAPA_REQUIRE(G >= 1 && Cq % G == 0 && C % G == 0, SAPA_ERR_ARGUMENT,
+                 "%s: channels (%d, %d) must be divisible by groups (%d)", fn, Cq, C, G);
+    SAPA_REQUIRE(dtype_size(dtype) != 0, SAPA_ERR_DTYPE, "%s: unknown dtype code %d", fn, dtype);
+    SAPA_REQUIRE((long long)s * H * s * W < (1LL << 31), SAPA_ERR_ARGUMENT, "%s: image too large", fn);
+    return SAPA_OK;
+}
+
+
+static int memset_async(void *p, size_t bytes, cudaStream_t st, const char *fn) {
+    const cudaError_t e = cudaMemsetAsync(p, 0, bytes, st);
+    SAPA_REQUIRE(e == cudaSuccess, SAPA_ERR_LAUNCH, "%s: cudaMemsetAsync failed: %s", fn, cudaGetErrorString(e));
+    return SAPA_OK;
+}
+
+}  // namespace sapa
+
+using namespace sapa;
+
+extern "C" {
+
+int sapa_deform_qk_forward(const void *query, const void *key, const void *offset, void *out, int B, int Cq, int H, int W,
+                           int P, int s, int G, int dtype, void *stream) {
+    const char *fn = "sapa_deform_qk_forward";
+    if (int e = check_deform(fn, B, Cq, Cq, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, out);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return SAPA_DISPATCH_ALL(dtype, [&] {
+        const long long total = (long long)B * G * P * s * H * s * W;
+        deform_qk_fwd_kernel<scalar_t><<<grid_1d(total, 256), 256, 0, st>>>(
+            static_cast<const scalar_t *>(query), static_cast<const scalar_t *>(key), static_cast<const scalar_t *>(offset),
+            static_cast<scalar_t *>(out), B, Cq, H, W, P, s, G);
+        return check_launch("deform_qk_fwd_kernel");
+    });
+}
+
+int sapa_deform_av_forward(const void *attn, const void *value, const void *offset, void *out, int B, int C, int H, int W,
+                           int P, int s, int G, int dtype, void *stream) {
+    const char *fn = "sapa_deform_av_forward";
+    if (int e = check_deform(fn, B, C, C, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, out);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return SAPA_DISPATCH_ALL(dtype, [&] {
+        constexpr int CPT = 8;
+        const int chunks = (C / G + CPT - 1) / CPT;
+        const long long total = (long long)B * G * chunks * s * H * s * W;
+        deform_av_fwd_kernel<scalar_t, CPT><<<grid_1d(total, 256), 256, 0, st>>>(
+            static_cast<const scalar_t *>(attn), static_cast<const scalar_t *>(value), static_cast<const scalar_t *>(offset),
+            static_cast<scalar_t *>(out), B, C, H, W, P, s, G);
+        return check_launch("deform_av_fwd_kernel");
+    });
+}
+
+int sapa_deform_fused_forward(const void *query, const void *key, const void *value, const void *offset, void *out,
+                              void *attn, int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream) {
+    const char *fn = "sapa_deform_fused_forward";
+    if (int e = check_deform(fn, B, Cq, C, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset);
+    SAPA_CHECK_PTR(fn, out);
+    SAPA_REQUIRE(P <= MAXP && dtype != SAPA_F64, SAPA_ERR_UNSUPPORTED,
+                 "%s: no fused kernel for num_point=%d dtype=%d (use the separate ops)", fn, P, dtype);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return SAPA_DISPATCH_FAST(dtype, [&] {
+        const long long total = (long long)B * G * s * H * s * W;
+        deform_fused_fwd_kernel<scalar_t, 8><<<grid_1d(total, 128), 128, 0, st>>>(
+            static_cast<const scalar_t *>(query), static_cast<const scalar_t *>(key), static_cast<const scalar_t *>(value),
+            static_cast<const scalar_t *>(offset), static_cast<scalar_t *>(out), static_cast<scalar_t *>(attn), B, Cq, C, H,
+            W, P, s, G);
+        return check_launch("deform_fused_fwd_kernel");
+    });
+}
+
+int sapa_deform_qk_backward(const void *grad_out, const void *query, const void *key, const void *offset, void *grad_query,
+                            void *grad_key, void *grad_offset, int B, int Cq, int H, int W, int P, int s, int G, int dtype,
+                            void *stream) {
+    const char *fn = "sapa_deform_qk_backward";
+    if (int e = check_deform(fn, B, Cq, Cq, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, offset);
+    SAPA_CHECK_PTR(fn, grad_query); SAPA_CHECK_PTR(fn, grad_key); SAPA_CHECK_PTR(fn, grad_offset);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t acc = dtype == SAPA_F64 ? 8 : 4;
+    if (int e = memset_async(grad_query, (size_t)B * Cq * s * H * s * W * acc, st, fn)) return e;
+    if (int e = memset_async(grad_key, (size_t)B * Cq * H * W * acc, st, fn)) return e;
+    return SAPA_DISPATCH_ALL(dtype, [&] {
+        using A = typename AccOf<scalar_t>::type;
+        const long long total = (long long)B * G * P * s * H * s * W;
+        deform_bwd_kernel<scalar_t, true><<<grid_1d(total, 256), 256, 0, st>>>(
+            static_cast<const scalar_t *>(grad_out), static_cast<const scalar_t *>(query), static_cast<const scalar_t *>(key),
+            static_cast<const scalar_t *>(offset), static_cast<A *>(grad_query), nullptr, static_cast<A *>(grad_key),
+            static_cast<scalar_t *>(grad_offset), B, Cq, H, W, P, s, G);
+        return check_launch("deform_bwd_kernel<qk>");
+    });
+}
+
+int sapa_deform_av_backward(const void *grad_out, const void *attn, const void *value, const void *offset, void *grad_attn,
+                            void *grad_value, void *grad_offset, int B, int C, int H, int W, int P, int s, int G, int dtype,
+                            void *stream) {
+    const char *fn = "sapa_deform_av_backward";
+    if (int e = check_deform(fn, B, C, C, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset);
+    SAPA_CHECK_PTR(fn, grad_attn); SAPA_CHECK_PTR(fn, grad_value); SAPA_CHECK_PTR(fn, grad_offset);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t acc = dtype == SAPA_F64 ? 8 : 4;
+    if (int e = memset_async(grad_value, (size_t)B * C * H * W * acc, st, fn)) return e;
+    return SAPA_DISPATCH_ALL(dtype, [&] {
+        using A = typename AccOf<scalar_t>::type;
+        const long long total = (long long)B * G * P * s * H * s * W;
+        deform_bwd_kernel<scalar_t, false><<<grid_1d(total, 256), 256, 0, st>>>(
+            static_cast<const scalar_t *>(grad_out), static_cast<const scalar_t *>(attn), static_cast<const scalar_t *>(value),
+            static_cast<const scalar_t *>(offset), nullptr, static_cast<scalar_t *>(grad_attn), static_cast<A *>(grad_value),
+            static_cast<scalar_t *>(grad_offset), B, C, H, W, P, s, G);
+        return check_launch("deform_bwd_kernel<av>");
+    });
+}
+
+}  // extern "C"

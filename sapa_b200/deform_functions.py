@@ -1,0 +1,176 @@
+"""Autograd functions of SAPA-D: ``deform_qk``, ``deform_av`` and the fused ``deform_sapa_fused``.
+
+Names, positional arguments and assertions follow ``DeformQKFunction`` / ``DeformAVFunction`` of the
+reference (deformsapa/deformsapa/deform_func.py:7-114); the kernels are reached through the C ABI.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from . import _lib
+
+
+def _acc_dtype(t: torch.Tensor) -> torch.dtype:
+    """Scatter targets accumulate with atomics in float32 (float64 for float64 inputs)."""
+    return torch.float64 if t.dtype == torch.float64 else torch.float32
+
+
+def _check_offset(offset, ref_lo, num_point, scale_factor, groups):
+    assert offset.size(0) == ref_lo.size(0)
+    assert offset.size(1) == groups * num_point * 2
+    assert offset.size(2) == ref_lo.size(2) * scale_factor
+    assert offset.size(3) == ref_lo.size(3) * scale_factor
+    assert num_point >= 1
+
+
+class DeformQKFunction(Function):
+    """out[b,g,p,qh,qw] = <query_g[b,:,qh,qw], bilinear(key_g[b], (qh/s, qw/s) + offset[b,g,p])>."""
+
+    @staticmethod
+    def forward(ctx, query, key, offset, num_point, scale_factor, groups):
+        assert scale_factor >= 1
+        assert query.size(0) == key.size(0)
+        assert query.size(1) == key.size(1)
+        assert query.size(2) == key.size(2) * scale_factor
+        assert query.size(3) == key.size(3) * scale_factor
+        _check_offset(offset, key, num_point, scale_factor, groups)
+        assert query.size(1) % groups == 0
+        if not query.is_cuda:
+            raise NotImplementedError
+        _lib.check_tensors(("query", query), ("key", key), ("offset", offset))
+        ctx.cfg = (num_point, scale_factor, groups)
+        n, c, h, w = query.shape
+        out = torch.empty((n, groups, num_point, h, w), dtype=query.dtype, device=query.device)
+        _lib.call("sapa_deform_qk_forward", query.device, query, key, offset, out, n, c, key.size(2), key.size(3),
+                  num_point, scale_factor, groups, _lib.dtype_code(query))
+        if query.requires_grad or key.requires_grad or offset.requires_grad:
+            ctx.save_for_backward(query, key, offset)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        assert grad_output.is_cuda
+        query, key, offset = ctx.saved_tensors
+        num_point, scale_factor, groups = ctx.cfg
+        gq, gk, go = deform_qk_backward_raw(grad_output.contiguous(), query, key, offset, num_point, scale_factor, groups)
+        return gq, gk, go, None, None, None
+
+
+def deform_qk_backward_raw(grad_output, query, key, offset, num_point, scale_factor, groups):
+    acc = _acc_dtype(query)
+    grad_query = torch.empty(query.shape, dtype=acc, device=query.device)
+    grad_key = torch.empty(key.shape, dtype=acc, device=key.device)
+    grad_offset = torch.empty_like(offset)
+    n, c, h, w = key.shape
+    _lib.call("sapa_deform_qk_backward", query.device, grad_output, query, key, offset, grad_query, grad_key,
+              grad_offset, n, c, h, w, num_point, scale_factor, groups, _lib.dtype_code(query))
+    return grad_query.to(query.dtype), grad_key.to(key.dtype), grad_offset
+
+
+deform_qk = DeformQKFunction.apply
+
+
+class DeformAVFunction(Function):
+    """out[b,c,qh,qw] = sum_p attn[b,g(c),p,qh,qw] * bilinear(value[b,c], (qh/s, qw/s) + offset[b,g(c),p])."""
+
+    @staticmethod
+    def forward(ctx, attn, value, offset, num_point, scale_factor, groups):
+        assert scale_factor >= 1
+        assert attn.size(0) == value.size(0)
+        assert attn.size(1) == groups
+        assert attn.size(2) == num_point
+        assert attn.size(3) == value.size(2) * scale_factor
+        assert attn.size(4) == value.size(3) * scale_factor
+        _check_offset(offset, value, num_point, scale_factor, groups)
+        if not attn.is_cuda:
+            raise NotImplementedError
+        _lib.check_tensors(("attn", attn), ("value", value), ("offset", offset))
+        if value.size(1) % groups != 0:
+            raise RuntimeError(f"value channels ({value.size(1)}) must be divisible by groups ({groups})")
+        ctx.cfg = (num_point, scale_factor, groups)
+        n, c, h, w = value.shape
+        out = torch.empty((n, c, scale_factor * h, scale_factor * w), dtype=value.dtype, device=value.device)
+        _lib.call("sapa_deform_av_forward", value.device, attn, value, offset, out, n, c, h, w, num_point, scale_factor,
+                  groups, _lib.dtype_code(value))
+        if attn.requires_grad or value.requires_grad or offset.requires_grad:
+            ctx.save_for_backward(attn, value, offset)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        assert grad_output.is_cuda
+        attn, value, offset = ctx.saved_tensors
+        num_point, scale_factor, groups = ctx.cfg
+        ga, gv, go = deform_av_backward_raw(grad_output.contiguous(), attn, value, offset, num_point, scale_factor, groups)
+        return ga, gv, go, None, None, None
+
+
+def deform_av_backward_raw(grad_output, attn, value, offset, num_point, scale_factor, groups):
+    grad_attn = torch.empty_like(attn)
+    grad_value = torch.empty(value.shape, dtype=_acc_dtype(value), device=value.device)
+    grad_offset = torch.empty_like(offset)
+    n, c, h, w = value.shape
+    _lib.call("sapa_deform_av_backward", value.device, grad_output, attn, value, offset, grad_attn, grad_value,
+              grad_offset, n, c, h, w, num_point, scale_factor, groups, _lib.dtype_code(value))
+    return grad_attn, grad_value.to(value.dtype), grad_offset
+
+
+deform_av = DeformAVFunction.apply
+
+
+def deform_fused_supported(num_point: int, dtype: torch.dtype) -> bool:
+    return num_point <= 16 and dtype in (torch.float32, torch.float16, torch.bfloat16)
+
+
+class DeformSapaFusedFunction(Function):
+    """deform_av(softmax_p(deform_qk(q, k, offset)), v, offset) as one op (``SAPADeform.attention``,
+    sapa_deform.py:51-53).  The backward chains the two separate backward kernels around the softmax
+    gradient and sums the two offset gradients (the offset feeds both ops)."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, offset, num_point, scale_factor, groups):
+        assert scale_factor >= 1
+        assert query.size(0) == key.size(0) == value.size(0)
+        assert query.size(1) == key.size(1)
+        assert query.size(2) == key.size(2) * scale_factor == value.size(2) * scale_factor
+        assert query.size(3) == key.size(3) * scale_factor == value.size(3) * scale_factor
+        _check_offset(offset, key, num_point, scale_factor, groups)
+        assert query.size(1) % groups == 0 and value.size(1) % groups == 0
+        if not query.is_cuda:
+            raise NotImplementedError
+        _lib.check_tensors(("query", query), ("key", key), ("value", value), ("offset", offset))
+        ctx.cfg = (num_point, scale_factor, groups)
+        need_grad = any(ctx.needs_input_grad[:4])
+        n, cq, hq, wq = query.shape
+        c, h, w = value.size(1), key.size(2), key.size(3)
+        if deform_fused_supported(num_point, query.dtype):
+            out = torch.empty((n, c, hq, wq), dtype=value.dtype, device=value.device)
+            attn = torch.empty((n, groups, num_point, hq, wq), dtype=value.dtype, device=value.device) if need_grad else None
+            _lib.call("sapa_deform_fused_forward", value.device, query, key, value, offset, out, attn, n, cq, c, h, w,
+                      num_point, scale_factor, groups, _lib.dtype_code(value))
+        else:
+            attn = torch.softmax(DeformQKFunction.apply(query.detach(), key.detach(), offset.detach(), num_point,
+                                                        scale_factor, groups), dim=2)
+            out = DeformAVFunction.apply(attn, value.detach(), offset.detach(), num_point, scale_factor, groups)
+        if need_grad:
+            ctx.save_for_backward(query, key, value, offset, attn)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        assert grad_output.is_cuda
+        query, key, value, offset, attn = ctx.saved_tensors
+        num_point, scale_factor, groups = ctx.cfg
+        grad_attn, grad_value, goff_av = deform_av_backward_raw(grad_output.contiguous(), attn, value, offset, num_point,
+                                                                scale_factor, groups)
+        # softmax backward over the point axis, in the accumulation precision
+        a32, g32 = attn.float() if attn.dtype != torch.float64 else attn, grad_attn.float() if attn.dtype != torch.float64 else grad_attn
+        grad_sim = (a32 * (g32 - (a32 * g32).sum(dim=2, keepdim=True))).to(attn.dtype)
+        grad_query, grad_key, goff_qk = deform_qk_backward_raw(grad_sim, query, key, offset, num_point, scale_factor, groups)
+        return grad_query, grad_key, grad_value, goff_av + goff_qk, None, None, None
+
+
+def deform_sapa_fused(query, key, value, offset, num_point=9, scale_factor=2, groups=4):
+    """Fused SAPA-D attention; differentiable with respect to query, key, value and offset."""
+    return DeformSapaFusedFunction.apply(query, key, value, offset, num_point, scale_factor, groups)

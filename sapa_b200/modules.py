@@ -1,0 +1,93 @@
+"""``SAPA`` and ``SAPADeform``: the upsampling modules of the reference with the same constructor arguments
+and parameter names, so that reference checkpoints load unchanged (``norm_y.*``, ``norm_x.*``, ``q.*``,
+``k.*`` and ``offset.*``; sapa_base.py:7-49, sapa_deform.py:7-62).
+
+One extra keyword, ``impl``: ``"fused"`` (default) runs the attention as one kernel, ``"separate"`` keeps the
+reference's three steps ``qk -> F.softmax -> av`` on this library's kernels.
+"""
+from __future__ import annotations
+
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .deform_functions import deform_av, deform_qk, deform_sapa_fused
+from .functions import av, qk, sapa_fused
+
+
+def _init_projection(module: nn.Module) -> None:
+    # 1x1 projections start as N(0, 0.02^2) with zero bias (sapa_base.py:42-46)
+    if isinstance(module, nn.Conv2d):
+        nn.init.normal_(module.weight, std=0.02)
+        if module.bias is not None:
+            nn.init.constant_(module.bias, 0)
+
+
+def _check_impl(impl: str) -> str:
+    if impl not in ("fused", "separate"):
+        raise ValueError(f"impl must be 'fused' or 'separate', got {impl!r}")
+    return impl
+
+
+class SAPA(nn.Module):
+    """Similarity-aware point affiliation upsampler (SAPA-B): x (low-res) is upsampled under guidance of y."""
+
+    def __init__(self, dim_y, dim_x=None, up_factor=2, up_kernel_size=5, embedding_dim=32, qkv_bias=True, norm=True,
+                 impl="fused"):
+        super().__init__()
+        dim_x = dim_y if dim_x is None else dim_x
+        self.up_factor, self.up_kernel_size, self.embedding_dim = up_factor, up_kernel_size, embedding_dim
+        self.norm, self.impl = norm, _check_impl(impl)
+        if norm:
+            self.norm_y = nn.GroupNorm(32, dim_y)
+            self.norm_x = nn.GroupNorm(32, dim_x)
+        self.q = nn.Conv2d(dim_y, embedding_dim, kernel_size=1, bias=qkv_bias)
+        self.k = nn.Conv2d(dim_x, embedding_dim, kernel_size=1, bias=qkv_bias)
+        self.apply(_init_projection)
+
+    def forward(self, y, x):
+        x_normed, y_normed = (self.norm_x(x), self.norm_y(y)) if self.norm else (x, y)
+        # the value is the un-normalised x; only the key is computed from the normalised one
+        return self.attention(self.q(y_normed), self.k(x_normed), x)
+
+    def attention(self, q, k, v):
+        if self.impl == "fused":
+            return sapa_fused(q.contiguous(), k.contiguous(), v.contiguous(), self.up_kernel_size, self.up_factor)
+        attn = F.softmax(qk(q, k, self.up_kernel_size, self.up_factor), dim=1)
+        return av(attn, v, self.up_kernel_size, self.up_factor)
+
+
+class SAPADeform(nn.Module):
+    """Deformable variant (SAPA-D): num_point learned sampling points per group instead of a fixed window."""
+
+    def __init__(self, dim_y, dim_x=None, up_factor=2, num_point=9, groups=4, embedding_dim=32, qkv_bias=True,
+                 high_offset=True, norm=False, impl="fused"):
+        super().__init__()
+        dim_x = dim_y if dim_x is None else dim_x
+        self.up_factor, self.num_point, self.groups = up_factor, num_point, groups
+        self.embedding_dim, self.high_offset = embedding_dim, high_offset
+        self.norm, self.impl = norm, _check_impl(impl)
+        if norm:
+            self.norm_y = nn.GroupNorm(32, dim_y)
+            self.norm_x = nn.GroupNorm(32, dim_x)
+        self.q = nn.Conv2d(dim_y, groups * embedding_dim, kernel_size=1, bias=qkv_bias)
+        self.k = nn.Conv2d(dim_x, groups * embedding_dim, kernel_size=1, bias=qkv_bias)
+        offset_dim = groups * num_point * 2 * (up_factor ** 2 if high_offset else 1)
+        self.offset = nn.Conv2d(dim_x, offset_dim, kernel_size=1, bias=qkv_bias)
+        self.apply(_init_projection)
+
+    def forward(self, y, x):
+        x_normed, y_normed = (self.norm_x(x), self.norm_y(y)) if self.norm else (x, y)
+        q, k = self.q(y_normed), self.k(x_normed)
+        raw = self.offset(x_normed)
+        if self.high_offset:   # one offset per high-res pixel, unpacked from channels
+            offset = F.pixel_shuffle(raw, upscale_factor=self.up_factor)
+        else:                  # every high-res pixel of a parent shares the parent's offset
+            offset = F.interpolate(raw, scale_factor=self.up_factor)
+        return self.attention(q, k, x, offset)
+
+    def attention(self, q, k, x, offset):
+        if self.impl == "fused":
+            return deform_sapa_fused(q.contiguous(), k.contiguous(), x.contiguous(), offset.contiguous(),
+                                     self.num_point, self.up_factor, self.groups)
+        attn = F.softmax(deform_qk(q, k, offset, self.num_point, self.up_factor, self.groups), dim=2)
+        return deform_av(attn, x, offset, self.num_point, self.up_factor, self.groups)
