@@ -1,0 +1,404 @@
+#!/usr/bin/env python
+"""Benchmark of the SAPA upsampling hot path: upsampled Mpix/s and fraction of the HBM roofline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype f32|bf16|f16] [--workload cfg2|cfg5a|cfg5b]
+    python bench.py --impl reference ...      # the CPU path of the reference on the host cores
+
+A step is one fused SAPA-B forward (sim -> softmax -> atn, one kernel launch) over one batch of seeded
+synthetic tensors.  Default workload ``cfg2``: B=8, C=256, 64x64 -> 128x128, d=64, K=5, s=2 per GPU
+(batch-sharded, weak scaling: every rank runs the same per-GPU batch, no collective on the data path).
+One pixel = one high-res output location across all C channels: Mpix = B*sH*sW / 1e6.
+
+Prints ONE JSON line (rank 0).  ``value`` is measured with inputs resident in HBM; ``e2e`` goes through
+the public Python op with pinned host buffers, host->device and device->host copies inside the timed
+region.  ``roofline.achieved`` = algorithmic bytes per launch (every input read once + the output written
+once, the attention map not counted) / measured launch duration.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: per-GPU shapes at N = 1 (cfg5* are split across ranks: strong scaling)
+    "cfg2": dict(B=8, d=64, C=256, H=64, W=64, K=5, s=2, scaling="weak", shard="batch"),
+    "cfg5a": dict(B=64, d=64, C=256, H=128, W=128, K=5, s=2, scaling="strong", shard="batch"),
+    "cfg5b": dict(B=1, d=64, C=256, H=1024, W=1024, K=5, s=2, scaling="strong", shard="rows"),
+}
+DTYPES = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_HBM_GBS = 6650.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused-forward launch at cfg2, from the ncu capture
+# summarised under profiles/ (null until a capture exists for that dtype).
+NCU_TRAFFIC_BYTES = {"f32": None, "bf16": None, "f16": None}
+
+
+def algorithmic_bytes(w, esize):
+    hi, lo = w["s"] * w["H"] * w["s"] * w["W"], w["H"] * w["W"]
+    return (w["B"] * w["d"] * hi + w["B"] * w["d"] * lo + w["B"] * w["C"] * lo + w["B"] * w["C"] * hi) * esize
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Polls SM clock and throttle reasons through NVML (read-only) while the GPU is under load."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag, self.max_mhz, self.error = index, [], threading.Event(), None, None
+
+    def run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:      # NVML order can differ from CUDA order: look the device up by UUID
+                h = pynvml.nvmlDeviceGetHandleByUUID("GPU-" + str(torch.cuda.get_device_properties(self.index).uuid))
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            while not self.stop_flag.is_set():
+                try:
+                    reasons = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    reasons = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append((time.perf_counter(), pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM), reasons))
+                time.sleep(0.005)
+        except Exception as exc:  # NVML missing: report it, do not fail the run
+            self.error = repr(exc)
+
+    def summary(self, t0, t1):
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        window = "timed region"
+        if len(inside) < 3:
+            inside, window = list(self.samples), "warm-up + timed region + identical trailing load"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0, "error": self.error}
+        mhz = sorted(s[1] for s in inside)
+        seen = set()
+        for s in inside:
+            for bit, name in self.REASONS.items():
+                if s[2] & bit:
+                    seen.add(name)
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(seen),
+                "samples": len(inside), "window": window}
+
+
+def make_inputs(w, dtype, device, seed, pinned=False):
+    g = torch.Generator().manual_seed(seed)
+    s = w["s"]
+    shapes = dict(q=(w["B"], w["d"], s * w["H"], s * w["W"]), k=(w["B"], w["d"], w["H"], w["W"]),
+                  v=(w["B"], w["C"], w["H"], w["W"]))
+    out = {}
+    for name, shape in shapes.items():
+        t = torch.randn(*shape, generator=g, dtype=torch.float32).to(dtype)
+        out[name] = t.pin_memory() if pinned else t.to(device)
+    return out
+
+
+# ------------------------------------------------------------------ CPU path of the reference (oracle port)
+
+def cpu_pass(w, nb, which, tensors):
+    """One forward of the reference's CPU formulation on ``nb`` images; returns seconds."""
+    from oracle import c_oracle, unfold_port
+    q, k, v = (tensors[n][:nb] for n in ("q", "k", "v"))
+    t0 = time.perf_counter()
+    if which == "unfold":
+        with torch.no_grad():
+            unfold_port.sapa(q, k, v, w["K"], w["s"])
+    else:
+        c_oracle.sapa_forward(q.numpy(), k.numpy(), v.numpy(), w["K"], w["s"])
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(w, budget_s=12.0):
+    """Times both CPU restatements on the full per-GPU batch for about ``budget_s`` seconds each at most and
+    reports the faster one.  float32, all host threads."""
+    from oracle import c_oracle
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    c_oracle.set_num_threads(cores)
+    tensors = make_inputs(w, torch.float32, "cpu", 0)
+    nb = min(w["B"], 8)
+    best = {}
+    for which in ("unfold", "c"):
+        cpu_pass(w, 1, which, tensors)                      # warm-up on one image
+        times, spent = [], 0.0
+        while spent < budget_s / 2 and len(times) < 5:
+            t = cpu_pass(w, nb, which, tensors)
+            times.append(t)
+            spent += t
+        best[which] = min(times)
+    which = min(best, key=best.get)
+    pix = nb * w["s"] * w["H"] * w["s"] * w["W"]
+    threads = torch.get_num_threads() if which == "unfold" else c_oracle.num_threads()
+    return {"value": pix / best[which] / 1e6, "unit": "Mpix/s", "cores": threads, "kind": "port",
+            "sample": f"{nb} of {w['B']} images of the workload, float32, best of {len(times)} passes; "
+                      f"unfold/einsum port {best['unfold'] * 1e3:.0f} ms, scalar C port (OpenMP) {best['c'] * 1e3:.0f} ms, "
+                      f"faster one reported ({which}); host has {cores} logical cores"}
+
+
+def run_reference(args, w):
+    """--impl reference: the reference's CPU path (oracle port) on the host cores; rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from oracle import c_oracle
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    c_oracle.set_num_threads(cores)
+    tensors = make_inputs(w, torch.float32, "cpu", 0)
+    # pick the faster restatement and a per-step sample that keeps the whole run within ~2 minutes
+    t1 = {which: min(cpu_pass(w, 1, which, tensors) for _ in range(2)) for which in ("unfold", "c")}
+    which = min(t1, key=t1.get)
+    total_steps = args.steps + args.warmup
+    nb = max(1, min(w["B"], int(120.0 / max(t1[which] * total_steps, 1e-9))))
+    for _ in range(args.warmup):
+        cpu_pass(w, nb, which, tensors)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_pass(w, nb, which, tensors)
+    dt = time.perf_counter() - t0
+    pix = nb * w["s"] * w["H"] * w["s"] * w["W"]
+    value = pix * args.steps / dt / 1e6
+    threads = torch.get_num_threads() if which == "unfold" else c_oracle.num_threads()
+    line = {
+        "impl": "reference", "metric": "upsampled Mpix/s (SAPA-B forward: sim -> softmax -> atn)", "value": value,
+        "unit": "Mpix/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": config_dict(args, w, note="CPU path of the reference (F.unfold/einsum formulation or scalar C port, "
+                                            "whichever is faster on this host)"),
+        "cpu_baseline": {"value": value, "unit": "Mpix/s", "cores": threads, "kind": "port",
+                         "sample": f"each step = {nb} of {w['B']} images, float32, restatement '{which}'"},
+        "e2e": {"value": value, "unit": "Mpix/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args, w, note=None):
+    c = {"workload": f"{args.workload}: SAPA-B fused forward, B={w['B']} per GPU" if w["scaling"] == "weak"
+         else f"{args.workload}: SAPA-B fused forward, B={w['B']} total ({w['shard']}-sharded)",
+         "B": w["B"], "C": w["C"], "d": w["d"], "low_res": [w["H"], w["W"]],
+         "high_res": [w["s"] * w["H"], w["s"] * w["W"]], "kernel_size": w["K"], "scale": w["s"],
+         "sharding": w["shard"]}
+    if note:
+        c["note"] = note
+    return c
+
+
+# ------------------------------------------------------------------ GPU arm
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=200)
+    ap.add_argument("--impl", default="sapa_b200", choices=["sapa_b200", "reference"])
+    ap.add_argument("--dtype", default="f32", choices=list(DTYPES))
+    ap.add_argument("--workload", default="cfg2", choices=list(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the additional (non-headline) measurements")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    w = dict(WORKLOADS[args.workload])
+
+    if args.impl == "reference":
+        run_reference(args, w)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the SAPA kernels have no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    import sapa_b200
+    from sapa_b200 import sharding
+    from sapa_b200.functions import fused_forward_raw
+
+    dtype = DTYPES[args.dtype]
+    esize = torch.empty((), dtype=dtype).element_size()
+    K, s = w["K"], w["s"]
+
+    # per-rank share of the workload
+    wl = dict(w)
+    halo = (0, 0)
+    if w["scaling"] == "strong" and world > 1:
+        if w["shard"] == "batch":
+            sl = sharding.batch_slice(w["B"], world, rank)
+            wl["B"] = sl.stop - sl.start
+        else:
+            sl = sharding.row_slice(w["H"], world, rank)
+            wl["H"] = sl.stop - sl.start
+    bytes_per_launch = algorithmic_bytes(wl, esize)
+    pix_per_step_rank = wl["B"] * s * wl["H"] * s * wl["W"]
+
+    # rotating buffer sets so that no input is L2-resident from the previous iteration
+    nsets = max(2, min(8, -(-3 * L2_BYTES // bytes_per_launch) + 1))
+    sets = []
+    for i in range(nsets):
+        t = make_inputs(wl, dtype, device, seed=rank * 1000 + i)
+        t["out"] = torch.empty((wl["B"], wl["C"], s * wl["H"], s * wl["W"]), dtype=dtype, device=device)
+        sets.append(t)
+
+    row_sharded = w["shard"] == "rows" and world > 1
+    r = (K - 1) // 2
+
+    def step(i):
+        t = sets[i % nsets]
+        if row_sharded:   # halo exchange (NCCL send/recv over NVLink) + slab kernel, every step
+            kp, vp = sharding.exchange_row_halo([t["k"], t["v"]], r)
+            sapa_b200._lib.call("sapa_fused_forward_slab", device, t["q"], kp, vp, t["out"], None, wl["B"], wl["d"],
+                                wl["C"], wl["H"], wl["W"], r, r, K, s, sapa_b200._lib.dtype_code(t["q"]))
+        else:
+            sapa_b200._lib.call("sapa_fused_forward", device, t["q"], t["k"], t["v"], t["out"], None, wl["B"], wl["d"],
+                                wl["C"], wl["H"], wl["W"], K, s, sapa_b200._lib.dtype_code(t["q"]))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.perf_counter()
+    start.record()
+    for i in range(args.steps):
+        step(i)
+    end.record()
+    barrier()
+    t_wall1 = time.perf_counter()
+    elapsed_ms = start.elapsed_time(end)
+    if len([x for x in sampler.samples if t_wall0 <= x[0] <= t_wall1]) < 3:
+        t_end = time.perf_counter() + 0.3      # identical load, untimed, only so that the clocks can be sampled
+        i = 0
+        while time.perf_counter() < t_end:
+            step(i)
+            i += 1
+            if i % 64 == 0:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+    clocks = sampler.summary(t_wall0, t_wall1)
+
+    if world > 1:
+        tt = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(tt.item())
+        pp = torch.tensor([pix_per_step_rank], device=device, dtype=torch.float64)
+        dist.all_reduce(pp, op=dist.ReduceOp.SUM)
+        pix_per_step = float(pp.item())
+    else:
+        pix_per_step = float(pix_per_step_rank)
+    ms_per_step = elapsed_ms / args.steps
+    value = pix_per_step / (ms_per_step * 1e-3) / 1e6
+
+    # ---- end to end: public op, pinned host buffers in and out, copies inside the timed region ----
+    e2e_steps = max(3, min(args.steps, 30))
+    host_in = [make_inputs(wl, dtype, device, seed=7 + i, pinned=True) for i in range(2)]
+    host_out = [torch.empty((wl["B"], wl["C"], s * wl["H"], s * wl["W"]), dtype=dtype).pin_memory() for _ in range(2)]
+    s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+    dev_in = [None, None]
+    dev_out = [None, None]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_k = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_loop(n):
+        for i in range(n):
+            b = i % 2
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_k[b])                 # the kernel that last read this slot is done
+                dev_in[b] = {k: v.to(device, non_blocking=True) for k, v in host_in[b].items()}
+                ev_in[b].record(s_in)
+            s_main.wait_event(ev_in[b])
+            s_main.wait_event(ev_out[b])                 # the copy-out that last read this slot is done
+            if row_sharded:
+                dev_out[b] = sharding.sapa_fused_row_sharded(dev_in[b]["q"], dev_in[b]["k"], dev_in[b]["v"], K, s)
+            else:
+                dev_out[b] = sapa_b200.sapa_fused(dev_in[b]["q"], dev_in[b]["k"], dev_in[b]["v"], K, s)
+            ev_k[b].record(s_main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_k[b])
+                host_out[b].copy_(dev_out[b], non_blocking=True)
+                dev_out[b].record_stream(s_out)
+                ev_out[b].record(s_out)
+        s_main.wait_stream(s_in)
+        s_main.wait_stream(s_out)
+
+    e2e_loop(3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    e2e_loop(e2e_steps)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        tt = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item())
+    e2e_value = pix_per_step / (e2e_ms / e2e_steps * 1e-3) / 1e6
+    h2d = sum(v.numel() * v.element_size() for v in host_in[0].values())
+    d2h = host_out[0].numel() * host_out[0].element_size()
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        achieved = bytes_per_launch / (ms_per_step * 1e-3) / 1e9
+        traffic = NCU_TRAFFIC_BYTES.get(args.dtype) if args.workload == "cfg2" and world == 1 else None
+        line = {
+            "metric": "upsampled Mpix/s (SAPA-B fused forward: sim -> softmax -> atn)", "value": value, "unit": "Mpix/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None, "dtype": args.dtype,
+            "data": "synthetic",
+            "config": dict(config_dict(args, w), l2=f"{nsets} rotating input/output sets "
+                           f"({nsets * bytes_per_launch / 1e6:.0f} MB) > 126 MB L2"),
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "Mpix/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "how": "sapa_b200.sapa_fused on pinned host tensors, double-buffered "
+                                               "H2D / kernel / D2H on three streams"},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": traffic, "peak_source": f"of {peak_kind}",
+                         "algorithmic_bytes_per_launch": bytes_per_launch,
+                         "frac_of_8000_nominal": achieved / 8000.0},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(w)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
