@@ -10,7 +10,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsapa_b200.so")
+# SAPA_B200_LIB points at another build of the same library (for example one compiled with extra flags)
+LIB_PATH = os.environ.get("SAPA_B200_LIB") or os.path.join(_HERE, "libsapa_b200.so")
 
 SAPA_F32, SAPA_F16, SAPA_BF16, SAPA_F64 = 0, 1, 2, 3
 _DTYPE_CODE = {torch.float32: SAPA_F32, torch.float16: SAPA_F16, torch.bfloat16: SAPA_BF16, torch.float64: SAPA_F64}

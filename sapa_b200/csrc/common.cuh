@@ -29,26 +29,35 @@ template <> __device__ __forceinline__ __half from_acc<__half>(float x) { return
 template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 template <> __device__ __forceinline__ double from_acc<double>(double x) { return x; }
 
-// A pair of adjacent elements (the two high-res columns of one low-res parent when s == 2).
-template <typename T> struct Pair;
-template <> struct Pair<float> { using type = float2; };
-template <> struct Pair<__half> { using type = __half2; };
-template <> struct Pair<__nv_bfloat16> { using type = __nv_bfloat162; };
-
-__device__ __forceinline__ float2 pair_to_float2(float2 p) { return p; }
-__device__ __forceinline__ float2 pair_to_float2(__half2 p) { return __half22float2(p); }
-__device__ __forceinline__ float2 pair_to_float2(__nv_bfloat162 p) { return __bfloat1622float2(p); }
-
-template <typename T> __device__ __forceinline__ typename Pair<T>::type float2_to_pair(float a, float b);
-template <> __device__ __forceinline__ float2 float2_to_pair<float>(float a, float b) { return make_float2(a, b); }
-template <> __device__ __forceinline__ __half2 float2_to_pair<__half>(float a, float b) { return __floats2half2_rn(a, b); }
-template <> __device__ __forceinline__ __nv_bfloat162 float2_to_pair<__nv_bfloat16>(float a, float b) {
-    return __floats2bfloat162_rn(a, b);
+// Streaming (evict-first) load / store of two adjacent elements (the two high-res columns of one low-res
+// parent when s == 2) as one 64-bit or 32-bit access.  The 16-bit types go through `unsigned int` builtins:
+// the toolkit's own __stcs overloads for __half2 / __nv_bfloat162 are inline asm with a "memory" clobber,
+// which pins every shared-memory load behind the previous store and serialises the aggregation loop.
+template <typename T> __device__ __forceinline__ float2 load_pair(const T *p);
+template <> __device__ __forceinline__ float2 load_pair<float>(const float *p) {
+    return __ldcs(reinterpret_cast<const float2 *>(p));
+}
+template <> __device__ __forceinline__ float2 load_pair<__half>(const __half *p) {
+    const unsigned int raw = __ldcs(reinterpret_cast<const unsigned int *>(p));
+    return __half22float2(*reinterpret_cast<const __half2 *>(&raw));
+}
+template <> __device__ __forceinline__ float2 load_pair<__nv_bfloat16>(const __nv_bfloat16 *p) {
+    const unsigned int raw = __ldcs(reinterpret_cast<const unsigned int *>(p));
+    return make_float2(__uint_as_float(raw << 16), __uint_as_float(raw & 0xffff0000u));
 }
 
-// Read-only load that bypasses L1 allocation (streamed once) and a streaming store.
-template <typename V> __device__ __forceinline__ V ld_stream(const V *p) { return __ldcs(p); }
-template <typename V> __device__ __forceinline__ void st_stream(V *p, V v) { __stcs(p, v); }
+template <typename T> __device__ __forceinline__ void store_pair(T *p, float a, float b);
+template <> __device__ __forceinline__ void store_pair<float>(float *p, float a, float b) {
+    __stcs(reinterpret_cast<float2 *>(p), make_float2(a, b));
+}
+template <> __device__ __forceinline__ void store_pair<__half>(__half *p, float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    __stcs(reinterpret_cast<unsigned int *>(p), *reinterpret_cast<const unsigned int *>(&h));
+}
+template <> __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloat16 *p, float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    __stcs(reinterpret_cast<unsigned int *>(p), *reinterpret_cast<const unsigned int *>(&h));
+}
 
 __device__ __forceinline__ void atomic_add(float *p, float v) { atomicAdd(p, v); }
 __device__ __forceinline__ void atomic_add(double *p, double v) { atomicAdd(p, v); }

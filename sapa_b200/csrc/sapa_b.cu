@@ -22,6 +22,9 @@
 //   * generic kernels for every other odd K, s >= 1 and for f64: one thread per output element.
 #include "common.cuh"
 
+#include <cstdlib>
+#include <cstring>
+
 namespace sapa {
 
 // ==================================================================================================
@@ -222,10 +225,8 @@ __device__ __forceinline__ void load_group(const T *__restrict__ plane, int sW, 
         return;
     }
     if constexpr (S == 2) {
-        using P = typename Pair<T>::type;
-        const P *r0 = reinterpret_cast<const P *>(plane + (size_t)(2 * y) * sW + 2 * x);
-        const P *r1 = reinterpret_cast<const P *>(plane + (size_t)(2 * y + 1) * sW + 2 * x);
-        const float2 a = pair_to_float2(ld_stream(r0)), b = pair_to_float2(ld_stream(r1));
+        const float2 a = load_pair<T>(plane + (size_t)(2 * y) * sW + 2 * x);
+        const float2 b = load_pair<T>(plane + (size_t)(2 * y + 1) * sW + 2 * x);
         g[0] = a.x; g[1] = a.y; g[2] = b.x; g[3] = b.y;
     } else {
 #pragma unroll
@@ -238,11 +239,8 @@ __device__ __forceinline__ void load_group(const T *__restrict__ plane, int sW, 
 template <typename T, int S>
 __device__ __forceinline__ void store_group(T *__restrict__ plane, int sW, int y, int x, const float (&g)[S * S]) {
     if constexpr (S == 2) {
-        using P = typename Pair<T>::type;
-        P *r0 = reinterpret_cast<P *>(plane + (size_t)(2 * y) * sW + 2 * x);
-        P *r1 = reinterpret_cast<P *>(plane + (size_t)(2 * y + 1) * sW + 2 * x);
-        st_stream(r0, float2_to_pair<T>(g[0], g[1]));
-        st_stream(r1, float2_to_pair<T>(g[2], g[3]));
+        store_pair<T>(plane + (size_t)(2 * y) * sW + 2 * x, g[0], g[1]);
+        store_pair<T>(plane + (size_t)(2 * y + 1) * sW + 2 * x, g[2], g[3]);
     } else {
 #pragma unroll
         for (int sy = 0; sy < S; ++sy)
@@ -536,6 +534,20 @@ static inline int grid_1d(long long total, int threads) {
     return (int)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
 }
 
+// tensor-core fused forward (sapa_mma.cu)
+bool fused_mma_supported(int W, int dtype);
+int launch_fused_mma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
+                     int rows, int ytop0, int dtype, cudaStream_t st);
+
+// SAPA_FUSED_IMPL=tile forces the FP32-pipe tiled kernel (kept for K = 3 and for A/B measurements)
+static bool prefer_mma() {
+    static const bool value = [] {
+        const char *e = getenv("SAPA_FUSED_IMPL");
+        return !(e != nullptr && strcmp(e, "tile") == 0);
+    }();
+    return value;
+}
+
 static bool tiled_supported(int K, int s, int dtype) {
     return dtype != SAPA_F64 && s == 2 && (K == 5 || K == 3);
 }
@@ -693,6 +705,8 @@ int sapa_fused_forward_slab(const void *query, const void *key, const void *valu
     a.hi = query; a.lo1 = key; a.lo2 = value; a.out_hi = out; a.out_slots = attn;
     a.B = B; a.C1 = d; a.C2 = C; a.H = H; a.W = W; a.rows = halo_top + H + halo_bottom; a.ytop0 = halo_top;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (K == 5 && fused_mma_supported(W, dtype) && prefer_mma())
+        return launch_fused_mma(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
     return SAPA_DISPATCH_FAST(dtype, [&] { return launch_tile_ks<scalar_t, MODE_FUSED>(a, K, st); });
 }
 

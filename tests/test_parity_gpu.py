@@ -382,9 +382,10 @@ def test_gradcheck_float64_like_the_reference_scripts(sp):
     assert gradcheck(sp.sapa_fused, (q, k, v, K, s))
     P, G = 5, 4
     o = torch.rand(b, G * P * 2, s * h, s * w, device=DEV, dtype=torch.float64, requires_grad=True)
-    assert gradcheck(sp.deform_qk, (q, k, o, P, s, G))
+    # key / value gradients are scattered with float atomics (as in the reference): summation order varies
+    assert gradcheck(sp.deform_qk, (q, k, o, P, s, G), nondet_tol=1e-10)
     da = torch.randn(b, G, P, s * h, s * w, device=DEV, dtype=torch.float64, requires_grad=True)
-    assert gradcheck(sp.deform_av, (da, v, o, P, s, G))
+    assert gradcheck(sp.deform_av, (da, v, o, P, s, G), nondet_tol=1e-10)
 
 
 def test_forward_check_like_the_reference_scripts(sp):
