@@ -32,15 +32,9 @@ constexpr int HP = 16;               // halo row pitch in cells (12 or 16 of the
 constexpr int CELLS = HH * HP;       // 128 cells per channel plane
 constexpr int QROWS = 2 * ROWS, QCOLS = 2 * COLS;   // high-res query tile 8 x 16
 constexpr int KCH = 16;              // key / query channels per stage
-#ifndef SAPA_NSTAGE
-#define SAPA_NSTAGE 4
-#endif
-constexpr int NSTAGE = SAPA_NSTAGE;
+constexpr int NSTAGE = 4;
 constexpr int NT = ROWS * 32;
 constexpr unsigned TF32_MASK = 0xffffe000u;
-#ifndef SAPA_DBG
-#define SAPA_DBG 0
-#endif
 
 // Shared-memory geometry per element type.  Plane strides are chosen so that the 8 row addresses of an
 // ldmatrix (8 consecutive channels) fall into 8 different 16-byte bank groups (stride == 16 bytes mod 128) and
@@ -352,18 +346,10 @@ __global__ void __launch_bounds__(NT32, 2) sapa_mma_fused_f32_kernel(const Args 
                         al[b][i] = __float_as_uint(__uint_as_float(ah[b][i]) - __uint_as_float(ah[b][i] & TF32_MASK));
                 }
                 // three passes over the independent accumulators: hi*hi, lo*hi, hi*lo
-                if (!(SAPA_DBG & 4)) {
 #pragma unroll
                 for (int b = 0; b < NBLK; ++b)
 #pragma unroll
                     for (int r = 0; r < 2; ++r) mma_tf32(acc[b][r], ah[b], phi[r][dy][0], phi[r][dy][1]);
-                } else {
-#pragma unroll
-                for (int b = 0; b < NBLK; ++b)
-#pragma unroll
-                    for (int r = 0; r < 2; ++r) acc[b][r][0] += __uint_as_float(ah[b][r] ^ al[b][r+1]);
-                }
-                if (!(SAPA_DBG & 1)) {
 #pragma unroll
                 for (int b = 0; b < NBLK; ++b)
 #pragma unroll
@@ -372,10 +358,9 @@ __global__ void __launch_bounds__(NT32, 2) sapa_mma_fused_f32_kernel(const Args 
                 for (int b = 0; b < NBLK; ++b)
 #pragma unroll
                     for (int r = 0; r < 2; ++r) mma_tf32(acc[b][r], ah[b], plo[r][dy][0], plo[r][dy][1]);
-                }
             }
             // D fragment: d0,d1 = Out[ch g][px 2t, 2t+1], d2,d3 = Out[ch g+8][px 2t, 2t+1]
-            if (y < a.H && x0 + 4 * h + t < a.W && (!(SAPA_DBG & 2) || acc[0][0][0] == 123.456f)) {
+            if (y < a.H && x0 + 4 * h + t < a.W) {
                 T *o = static_cast<T *>(a.out) + ((size_t)n * a.C + c0 + g) * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h + t);
                 const bool full = c0 + VCH <= a.C;
 #pragma unroll
