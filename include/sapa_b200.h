@@ -107,6 +107,23 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
                         void *workspace, size_t workspace_bytes,
                         int B, int d, int C, int H, int W, int K, int s, int dtype, void *stream);
 
+/* Same gradients as sapa_fused_backward for callers that cannot allocate device memory where they call it
+ * (engines that run under a memory plan fixed when they were built, plugin hosts whose allocator the op cannot
+ * reach, real-time loops that forbid cudaMalloc after start-up because it synchronises the device).  It has no counterpart in the reference.
+ * The scratch for the logit gradients is a 16 MiB array built into the library, so:
+ *   - every GPU that loads the library holds those 16 MiB until the process exits;
+ *   - problems whose scratch (sapa_fused_backward_workspace) exceeds sapa_fused_backward_static_capacity()
+ *     are refused with SAPA_ERR_WORKSPACE (config 2 in float32, 13.1 MB, fits);
+ *   - the first call on each device looks the array's address up (cudaGetSymbolAddress, with that device
+ *     current); make that first call before any stream capture begins;
+ *   - all calls share the one array, which keeps the previous call's contents (nothing needs clearing: it is
+ *     fully rewritten before it is read), so two calls that overlap on the GPU (different streams) race.
+ * Neither this function nor anything it calls allocates or frees memory. */
+size_t sapa_fused_backward_static_capacity(void);
+int sapa_fused_backward_static(const void *grad_out, const void *query, const void *key, const void *value,
+                               const void *attn, void *grad_query, void *grad_key, void *grad_value,
+                               int B, int d, int C, int H, int W, int K, int s, int dtype, void *stream);
+
 /* ------------------------------------------------------------------ SAPA-D (deformable) -------------- */
 /* offset is [B, G*P*2, sH, sW]; channel 2*(g*P+p) is the x (w) offset and 2*(g*P+p)+1 the y (h) offset,
  * in low-res pixels, added to the integer parent index (qh/s, qw/s) (deform_qk_cuda_kernel.cu:172-183).

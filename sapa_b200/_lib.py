@@ -30,13 +30,15 @@ _SIGNATURES = {
     "sapa_fused_forward": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_fused_forward_slab": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_fused_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_fused_backward_static": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_qk_forward": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_qk_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_av_forward": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_av_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_fused_forward": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
 }
-EXPORTS = sorted(list(_SIGNATURES) + ["sapa_last_error", "sapa_abi_version", "sapa_fused_backward_workspace"])
+EXPORTS = sorted(list(_SIGNATURES) + ["sapa_last_error", "sapa_abi_version", "sapa_fused_backward_workspace",
+                                           "sapa_fused_backward_static_capacity"])
 
 
 def lib() -> ctypes.CDLL:
@@ -64,6 +66,8 @@ def lib() -> ctypes.CDLL:
     handle.sapa_abi_version.restype = ctypes.c_int
     handle.sapa_fused_backward_workspace.argtypes = [_i, _i, _i, _i, _i, _i]
     handle.sapa_fused_backward_workspace.restype = ctypes.c_size_t
+    handle.sapa_fused_backward_static_capacity.argtypes = []
+    handle.sapa_fused_backward_static_capacity.restype = ctypes.c_size_t
     if handle.sapa_abi_version() != ABI_VERSION:
         raise RuntimeError("libsapa_b200.so has a different ABI version than this Python package; rebuild it")
     _lib = handle

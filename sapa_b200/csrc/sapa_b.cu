@@ -24,6 +24,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 namespace sapa {
 
@@ -755,6 +756,57 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
     }
     if (int e = run_gath(query, dS, grad_key, B, d, H, W, K, s, dtype, st)) return e;       // dKey = gath(Q, dS)
     return run_gath(grad_out, attn, grad_value, B, C, H, W, K, s, dtype, st);               // dV = gath(dOut, A)
+}
+
+// ------------------------------------------------------------------ backward without any allocation
+// Some callers cannot hand this library a workspace because they cannot allocate device memory at the point
+// of the call: inference engines that size every buffer when the engine is built and run under that fixed memory
+// plan, plugin hosts whose allocator is not reachable from the op, and real-time loops that forbid cudaMalloc
+// after start-up because it synchronises the device.
+// For them the logit-gradient scratch of the backward pass lives in a file-scope device array that every GPU
+// loading this library holds until the process exits.
+constexpr size_t kStaticScratchBytes = 16u << 20;     // 16 MiB: config-2-sized float32 problems (13.1 MB) fit
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// The array's name is only a host-side handle; kernels need its device address, looked up once per device
+// while that device is current.
+static int static_scratch_address(void **out) {
+    constexpr int kMaxDevices = 64;
+    static void *cache[kMaxDevices] = {};
+    static std::mutex lock;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    SAPA_REQUIRE(e == cudaSuccess, SAPA_ERR_LAUNCH, "sapa_fused_backward_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    SAPA_REQUIRE(dev >= 0 && dev < kMaxDevices, SAPA_ERR_ARGUMENT, "sapa_fused_backward_static: device index %d out of range", dev);
+    std::lock_guard<std::mutex> guard(lock);
+    if (cache[dev] == nullptr) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        SAPA_REQUIRE(e == cudaSuccess && p != nullptr, SAPA_ERR_LAUNCH,
+                     "sapa_fused_backward_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        cache[dev] = p;
+    }
+    *out = cache[dev];
+    return SAPA_OK;
+}
+
+size_t sapa_fused_backward_static_capacity(void) { return kStaticScratchBytes; }
+
+int sapa_fused_backward_static(const void *grad_out, const void *query, const void *key, const void *value, const void *attn,
+                               void *grad_query, void *grad_key, void *grad_value, int B, int d, int C, int H, int W, int K,
+                               int s, int dtype, void *stream) {
+    const size_t need = sapa_fused_backward_workspace(B, H, W, K, s, dtype);
+    SAPA_REQUIRE(need != 0, SAPA_ERR_ARGUMENT, "sapa_fused_backward_static: sizes must be positive and the dtype known");
+    SAPA_REQUIRE(need <= kStaticScratchBytes, SAPA_ERR_WORKSPACE,
+                 "sapa_fused_backward_static: the problem needs %zu bytes of scratch but the built-in buffer holds %zu; "
+                 "use sapa_fused_backward with a caller-provided workspace",
+                 need, kStaticScratchBytes);
+    void *scratch = nullptr;
+    if (int e = static_scratch_address(&scratch)) return e;
+    // The scratch is written in full (gradient of the logits) before any kernel reads it, so nothing has to be
+    // cleared between calls; it simply keeps the last call's values.
+    return sapa_fused_backward(grad_out, query, key, value, attn, grad_query, grad_key, grad_value, scratch,
+                               kStaticScratchBytes, B, d, C, H, W, K, s, dtype, stream);
 }
 
 }  // extern "C"
