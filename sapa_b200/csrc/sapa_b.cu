@@ -537,14 +537,21 @@ static inline int grid_1d(long long total, int threads) {
 
 // tensor-core fused forward (sapa_mma.cu)
 bool fused_mma_supported(int W, int dtype);
+bool fused_tma_supported(int W, int dtype);
+int launch_fused_tma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
+                     int rows, int ytop0, cudaStream_t st);
 int launch_fused_mma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
                      int rows, int ytop0, int dtype, cudaStream_t st);
 
-// SAPA_FUSED_IMPL=tile forces the FP32-pipe tiled kernel (kept for K = 3 and for A/B measurements)
-static bool prefer_mma() {
-    static const bool value = [] {
+// SAPA_FUSED_IMPL selects a fused-forward kernel for A/B measurements: "tile" = FP32-pipe tiled kernel,
+// "mma" = tensor-core kernel with cp.async staging, unset / anything else = the best available
+// (float32 with 16-byte aligned rows: tensor-core kernel with TMA staging).
+static int fused_impl_choice() {
+    static const int value = [] {
         const char *e = getenv("SAPA_FUSED_IMPL");
-        return !(e != nullptr && strcmp(e, "tile") == 0);
+        if (e != nullptr && strcmp(e, "tile") == 0) return 1;
+        if (e != nullptr && strcmp(e, "mma") == 0) return 2;
+        return 0;
     }();
     return value;
 }
@@ -706,7 +713,12 @@ int sapa_fused_forward_slab(const void *query, const void *key, const void *valu
     a.hi = query; a.lo1 = key; a.lo2 = value; a.out_hi = out; a.out_slots = attn;
     a.B = B; a.C1 = d; a.C2 = C; a.H = H; a.W = W; a.rows = halo_top + H + halo_bottom; a.ytop0 = halo_top;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (K == 5 && fused_mma_supported(W, dtype) && prefer_mma())
+    const int impl = fused_impl_choice();
+    if (K == 5 && impl == 0 && fused_tma_supported(W, dtype)) {
+        const int e = launch_fused_tma(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, st);
+        if (e != SAPA_ERR_UNSUPPORTED) return e;
+    }
+    if (K == 5 && impl != 1 && fused_mma_supported(W, dtype))
         return launch_fused_mma(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
     return SAPA_DISPATCH_FAST(dtype, [&] { return launch_tile_ks<scalar_t, MODE_FUSED>(a, K, st); });
 }
