@@ -20,6 +20,8 @@
 
 #include <cuda.h>
 
+#include <atomic>
+
 
 namespace sapa {
 
@@ -35,21 +37,26 @@ constexpr int NT = 2 * ROWS * 32;          // 8 warps: (row, 4-pixel half)
 constexpr int ROWB = HC * 4;               // 64 bytes
 constexpr int K_BYTES = HH * KCH * ROWB;   // 8192: key box [8 rows][16 ch][16 cols]
 constexpr int V_BYTES = HH * VCH * ROWB;   // 16384
-constexpr int SLOT_BYTES = V_BYTES > 2 * K_BYTES ? V_BYTES : 2 * K_BYTES;        // = K_BYTES + the query box [8 hi rows][16 ch][16 hi cols] of 8192 bytes
+constexpr int SLOT_BYTES = V_BYTES > 2 * K_BYTES ? V_BYTES : 2 * K_BYTES;
+constexpr int O_BYTES = 2 * ROWS * VCH * ROWB;   // 16384: output box [8 hi rows][32 ch][16 hi cols], double-buffered        // = K_BYTES + the query box [8 hi rows][16 ch][16 hi cols] of 8192 bytes
 constexpr unsigned TF32_MASK = 0xffffe000u;
 constexpr int CTAS_PER_SM = 2;             // resident CTAs per SM the register budget is tuned for
-// true: a slot is refilled by thread 0 after a CTA barrier; false: by the last warp to finish reading it (no
-// barrier in the loop).  Measured equal within noise at config 2; the barrier form is the simpler one.
-constexpr bool SYNC_REFILL = true;
 constexpr int WAIT_LIMIT = 1 << 22;        // bounded mbarrier wait (each try suspends for a while in hardware)
 
-__device__ int g_wait_timeout = 0;         // set when a bounded wait gave up (read by sapa_tma_error_flag)
+__device__ int g_wait_timeout = 0;         // set when a bounded wait gave up (read by tma_wait_timeout_flag)
+// Dynamic tile scheduler of the persistent grid.  Every launch uses one of SCHED_SLOTS counter pairs (chosen
+// round-robin on the host); the last CTA of a launch to exit resets its pair, so a pair is clean again long
+// before the round-robin comes back to it (that would need SCHED_SLOTS launches resident at the same time).
+constexpr int SCHED_SLOTS = 256;
+__device__ unsigned g_next_tile[SCHED_SLOTS];
+__device__ unsigned g_ctas_done[SCHED_SLOTS];
 
 struct Args {
     float *out, *attn;
     int B, d, C, H, W;
     int rows, ytop0;
     int tiles_x, tiles_y;
+    int sched_slot;        // index into g_next_tile / g_ctas_done
 };
 
 __device__ __forceinline__ void mbar_init(unsigned bar, int count) {
@@ -89,6 +96,14 @@ __device__ __forceinline__ unsigned lds32(unsigned addr) {
     asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ void sts64(unsigned addr, float a, float b) {
+    asm volatile("st.shared.v2.f32 [%0], {%1, %2};\n" ::"r"(addr), "f"(a), "f"(b) : "memory");
+}
+// shared -> global tile store; out-of-range parts of the box (tile overhang, channel tail) are clipped
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, unsigned src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 // low term of the two-term tf32 split (the high term is the register itself: the tensor core reads its top 19 bits)
 __device__ __forceinline__ unsigned tf32_lo(unsigned x) {
     return __float_as_uint(__uint_as_float(x) - __uint_as_float(x & TF32_MASK));
@@ -99,13 +114,13 @@ __device__ __forceinline__ int swz(int col, int channel) { return ((((col >> 2) 
 
 __global__ void __launch_bounds__(NT, CTAS_PER_SM)
 sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-                          const __grid_constant__ CUtensorMap vmap, const Args a) {
+                          const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap, const Args a) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) unsigned long long full_bar[NSTAGE];
-    __shared__ int done_count[NSTAGE];          // warps that have finished reading the slot's current stage
     // the swizzle pattern is a function of the absolute shared-memory address: align the ring to 1024 bytes
     const unsigned ring_addr = ((unsigned)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
     const unsigned bar_addr = (unsigned)__cvta_generic_to_shared(full_bar);
+    const unsigned obuf_addr = ring_addr + NSTAGE * SLOT_BYTES;      // two output staging buffers behind the ring
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wrow = warp >> 1, h = warp & 1;
@@ -113,27 +128,34 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     const int sW = 2 * a.W;
     const size_t hi_plane = (size_t)(2 * a.H) * sW;
     const int nk = (a.d + KCH - 1) / KCH, nv = (a.C + VCH - 1) / VCH, total = nk + nv;
-    // persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ...; their stages form one continuous stream
-    // through the ring, so the first tiles of the next tile are in flight while the current one finishes
+    // Persistent CTA: its first tile is blockIdx.x, further tiles come from a global counter.  The stages of
+    // successive tiles form one continuous stream through the ring, so the first stages of the next tile are in
+    // flight while the current tile finishes.  tile_ids[ti & 3] = tile of the ti-th tile of this CTA, -1 = none.
     const int ntiles = a.B * a.tiles_x * a.tiles_y;
-    const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int total_gs = my_tiles * total;
+    __shared__ int tile_ids[4];
 
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < NSTAGE; ++i) {
             mbar_init(bar_addr + 8 * i, 1);
-            done_count[i] = 0;
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
 
-    // stage gs of this CTA's stream goes to slot gs % NSTAGE; executed by one thread
+    // stage gs of this CTA's stream goes to slot gs % NSTAGE; executed by thread 0 only
+    bool exhausted = false;
     auto issue = [&](int gs) {
-        if (gs >= total_gs) return;
+        if (exhausted) return;
         const int ti = gs / total, it = gs - ti * total;
-        int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        if (it == 0) {     // first stage of a tile: claim the tile
+            int claimed = (int)blockIdx.x;
+            if (ti > 0) claimed = (int)(atomicAdd(&g_next_tile[a.sched_slot], 1u) + gridDim.x);
+            if (claimed >= ntiles) claimed = -1;
+            tile_ids[ti & 3] = claimed;
+            if (claimed < 0) { exhausted = true; return; }
+        }
+        int tile = tile_ids[ti & 3];
         const int tbx = tile % a.tiles_x; tile /= a.tiles_x;
         const int tby = tile % a.tiles_y; tile /= a.tiles_y;
         const int tx0 = tbx * COLS, ty0 = tby * ROWS;
@@ -148,7 +170,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     };
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < (SYNC_REFILL ? NSTAGE - 1 : NSTAGE); ++i) issue(i);
+        for (int i = 0; i < NSTAGE - 1; ++i) issue(i);
     }
 
     // Lane (g,t): high-res pixel 8h+g of the tile's 16 columns (both rows); after the logit MMAs it holds the
@@ -162,14 +184,18 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     const int q_off0 = t * ROWB + swz(8 * h + g, t), q_off1 = (t + 4) * ROWB + swz(8 * h + g, t + 4);
     const int k_off0 = t * ROWB + swz(2 + 4 * h + g, t), k_off1 = (t + 4) * ROWB + swz(2 + 4 * h + g, t + 4);
     const int v_offa = g * ROWB + swz(2 + 4 * h + t, g), v_offb = g * ROWB + swz(6 + 4 * h + t, g);
+    //   output D fragment: channel g (and g+8), pixels 8h+2t, 8h+2t+1 of high-res rows 2*wrow, 2*wrow+1
+    const int o_off = (2 * wrow) * (VCH * ROWB) + g * ROWB + swz(8 * h + 2 * t, g);
 
     float s[2][5][2];                      // logits, then probabilities: [row][dy][cell 2t | 2t+1]
     unsigned phi[2][5][2];                 // B fragments of the aggregation: probabilities of cells (t, t+4); their
                                            // low tf32 terms are derived where they are used (2 ALU ops, 20 registers saved)
 
     int gs = 0;
-    for (int ti = 0; ti < my_tiles; ++ti) {
-    int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+    for (int ti = 0;; ++ti) {
+    // written by thread 0 at least one barrier earlier (tile 0 is known to everybody)
+    int tile = ti == 0 ? (int)blockIdx.x : tile_ids[ti & 3];
+    if (tile < 0) break;
     const int bx = tile % a.tiles_x; tile /= a.tiles_x;
     const int by = tile % a.tiles_y; tile /= a.tiles_y;
     const int n = tile;
@@ -181,9 +207,13 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         for (int dy = 0; dy < 5; ++dy) s[r][dy][0] = s[r][dy][1] = 0.f;
 
     for (int it = 0; it < total; ++it, ++gs) {
-        if (SYNC_REFILL) {
-            __syncthreads();                              // everyone is done with the slot that is refilled next
-            if (tid == 0) issue(gs + NSTAGE - 1);
+        __syncthreads();     // everyone is done with the slot that is refilled next and has written its output fragment
+        if (tid == 0) {
+            if (it > nk) {   // the previous stage was a value stage: its output tile is complete in shared memory
+                tma_store_4d(&omap, obuf_addr + ((it - nk - 1) & 1) * O_BYTES, 2 * x0, (it - nk - 1) * VCH, 2 * y0, n);
+                asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+            }
+            issue(gs + NSTAGE - 1);
         }
         if (!mbar_wait_bounded(bar_addr + 8 * (gs % NSTAGE), (gs / NSTAGE) & 1)) {
             atomicExch(&g_wait_timeout, 1);
@@ -265,7 +295,6 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             }
         } else {
             // ------------------------------------------------------------- aggregation: Out[16 ch][8 px] += V[16 ch][8 cells] P[8 cells][8 px]
-            const int c0 = (it - nk) * VCH;
             const unsigned vb = stage + wrow * (VCH * ROWB);
             float acc[VCH / 16][2][4];
 #pragma unroll
@@ -274,19 +303,30 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 for (int r = 0; r < 2; ++r)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[b][r][i] = 0.f;
+            unsigned an[VCH / 16][4];                     // fragments of the next window row, loaded one row ahead
+            auto load_row = [&](int dy) {
+#pragma unroll
+                for (int b = 0; b < VCH / 16; ++b) {
+                    const unsigned p = vb + dy * (VCH * ROWB) + b * 16 * ROWB;
+                    an[b][0] = lds32(p + v_offa);                 // V[ch g][cell t]
+                    an[b][1] = lds32(p + 8 * ROWB + v_offa);      // V[ch g+8][cell t]
+                    an[b][2] = lds32(p + v_offb);                 // V[ch g][cell t+4]
+                    an[b][3] = lds32(p + 8 * ROWB + v_offb);      // V[ch g+8][cell t+4]
+                }
+            };
+            load_row(0);
 #pragma unroll
             for (int dy = 0; dy < 5; ++dy) {
                 unsigned ah[VCH / 16][4], al[VCH / 16][4];
 #pragma unroll
-                for (int b = 0; b < VCH / 16; ++b) {
-                    const unsigned p = vb + dy * (VCH * ROWB) + b * 16 * ROWB;
-                    ah[b][0] = lds32(p + v_offa);                 // V[ch g][cell t]
-                    ah[b][1] = lds32(p + 8 * ROWB + v_offa);      // V[ch g+8][cell t]
-                    ah[b][2] = lds32(p + v_offb);                 // V[ch g][cell t+4]
-                    ah[b][3] = lds32(p + 8 * ROWB + v_offb);      // V[ch g+8][cell t+4]
+                for (int b = 0; b < VCH / 16; ++b)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) ah[b][i] = an[b][i];
+                if (dy < 4) load_row(dy + 1);
+#pragma unroll
+                for (int b = 0; b < VCH / 16; ++b)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) al[b][i] = tf32_lo(ah[b][i]);
-                }
 #pragma unroll
                 for (int b = 0; b < VCH / 16; ++b)
 #pragma unroll
@@ -300,34 +340,37 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
 #pragma unroll
                     for (int r = 0; r < 2; ++r) mma_tf32(acc[b][r], ah[b], tf32_lo(phi[r][dy][0]), tf32_lo(phi[r][dy][1]));
             }
-            // D fragment: d0,d1 = Out[ch g][px 2t, 2t+1], d2,d3 = Out[ch g+8][px 2t, 2t+1]
-            if (y < a.H && x0 + 4 * h + t < a.W) {
-                float *o = a.out + ((size_t)n * a.C + c0 + g) * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h + t);
-                const bool full = c0 + VCH <= a.C;
+            // D fragment: d0,d1 = Out[ch g][px 2t, 2t+1], d2,d3 = Out[ch g+8][px 2t, 2t+1] -> staging buffer laid out
+            // as the output box [hi row][channel][16 hi cols] (64-byte swizzle), stored by TMA after the next barrier
+            {
+                const unsigned ob = obuf_addr + ((it - nk) & 1) * O_BYTES + o_off;
 #pragma unroll
                 for (int b = 0; b < VCH / 16; ++b)
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        if (full || c0 + 16 * b + 8 * half + g < a.C) {
-                            store_pair<float>(o, acc[b][0][2 * half], acc[b][0][2 * half + 1]);
-                            store_pair<float>(o + sW, acc[b][1][2 * half], acc[b][1][2 * half + 1]);
-                        }
-                        o += 8 * hi_plane;
-                    }
-            }
-        }
-        // this warp is done with the slot; the last of the 8 warps to say so refills it with the stage that
-        // comes NSTAGE later in the stream (no CTA-wide barrier in the loop)
-        __syncwarp();
-        if (!SYNC_REFILL && lane == 0) {
-            const int slot = gs % NSTAGE;
-            if (atomicAdd(&done_count[slot], 1) == NT / 32 - 1) {
-                done_count[slot] = 0;
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                issue(gs + NSTAGE);
+                    for (int half = 0; half < 2; ++half)
+#pragma unroll
+                        for (int r = 0; r < 2; ++r)
+                            sts64(ob + r * (VCH * ROWB) + (16 * b + 8 * half) * ROWB, acc[b][r][2 * half], acc[b][r][2 * half + 1]);
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // make the writes visible to the TMA engine
+                // the buffer written two value stages from now is this one: its store must have finished reading it
+                if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
             }
         }
     }
+    // the tile's last output block
+    __syncthreads();
+    if (tid == 0) {
+        tma_store_4d(&omap, obuf_addr + ((nv - 1) & 1) * O_BYTES, 2 * x0, (nv - 1) * VCH, 2 * y0, n);
+        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+    }
+    }
+    if (tid == 0) {
+        asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // all output tiles are written
+        if (atomicAdd(&g_ctas_done[a.sched_slot], 1u) == gridDim.x - 1) {   // last CTA out: reset the scheduler slot
+            g_next_tile[a.sched_slot] = 0u;
+            g_ctas_done[a.sched_slot] = 0u;
+        }
     }
 }
 
@@ -372,9 +415,9 @@ bool fused_tma_supported(int W, int dtype) { return dtype == SAPA_F32 && W % 4 =
 int launch_fused_tma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
                      int rows, int ytop0, cudaStream_t st) {
     using namespace tma;
-    CUtensorMap qmap, kmap, vmap;
+    CUtensorMap qmap, kmap, vmap, omap;
     if (!make_map(&qmap, q, 2 * W, 2 * H, d, B, KCH) || !make_map(&kmap, k, W, rows, d, B, KCH) ||
-        !make_map(&vmap, v, W, rows, C, B, VCH)) {
+        !make_map(&vmap, v, W, rows, C, B, VCH) || !make_map(&omap, out, 2 * W, 2 * H, C, B, VCH)) {
         set_error("sapa_tma_fused: cuTensorMapEncodeTiled rejected the tensor layout");
         return SAPA_ERR_UNSUPPORTED;
     }
@@ -388,7 +431,7 @@ int launch_fused_tma(const void *q, const void *k, const void *v, void *out, voi
         set_error("too many tiles");
         return SAPA_ERR_ARGUMENT;
     }
-    constexpr int smem = NSTAGE * SLOT_BYTES + 1024;
+    constexpr int smem = NSTAGE * SLOT_BYTES + 2 * O_BYTES + 1024;
     const cudaError_t e = cudaFuncSetAttribute(sapa_tma_fused_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) {
         set_error("sapa_tma_fused: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
@@ -400,11 +443,11 @@ int launch_fused_tma(const void *q, const void *k, const void *v, void *out, voi
         return SAPA_ERR_LAUNCH;
     }
     const long long resident = (long long)CTAS_PER_SM * sms;
-    // One tile per CTA.  The kernel also runs as a persistent grid (grid = resident), but with static tile striding
-    // that was 15 % slower at config 2 (SMs end up with 6 to 8 tiles instead of ~6.9).
-    (void)resident;
-    const unsigned grid = (unsigned)nblocks;
-    sapa_tma_fused_f32_kernel<<<grid, NT, smem, st>>>(qmap, kmap, vmap, a);
+    // persistent grid with dynamic tile claiming (static striding left SMs with 6 to 8 tiles instead of ~6.9)
+    const unsigned grid = (unsigned)(nblocks < resident ? nblocks : resident);
+    static std::atomic<unsigned> next_slot{0};
+    a.sched_slot = (int)(next_slot.fetch_add(1u) % SCHED_SLOTS);
+    sapa_tma_fused_f32_kernel<<<grid, NT, smem, st>>>(qmap, kmap, vmap, omap, a);
     return check_launch("sapa_tma_fused_f32_kernel");
 }
 
