@@ -121,74 +121,78 @@ __global__ void deform_av_fwd_kernel(const T *__restrict__ attn, const T *__rest
 }
 
 // ---------------------------------------------------------------------------------- forward, fused
-// one thread per (b, g, qh, qw): logits of the P points -> softmax over the points -> aggregation of the
-// group's value channels.  The attention never leaves registers unless `attn_out` is given.
+// A block of 32 x FY threads handles 32 consecutive pixels of one (image, group).  Phase 1: thread (x, y) computes
+// the logits of points y, y + FY, ... of pixel x and leaves them, with the sampling positions, in shared memory.
+// Phase 2: every thread normalises the P logits of its pixel (softmax over the points) and aggregates the value
+// channels y*CPT .. of the group, CPT at a time.  The attention reaches HBM only if `attn_out` is given.
+constexpr int FY = 8;
+
 template <typename T, int CPT>
-__global__ void deform_fused_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ value,
-                                        const T *__restrict__ offset, T *__restrict__ out, T *__restrict__ attn_out,
-                                        int B, int Cq, int C, int H, int W, int P, int s, int G) {
+__global__ void __launch_bounds__(32 * FY)
+deform_fused_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ value,
+                        const T *__restrict__ offset, T *__restrict__ out, T *__restrict__ attn_out,
+                        int B, int Cq, int C, int H, int W, int P, int s, int G, int pix_blocks) {
+    __shared__ float s_a[MAXP][32], s_h[MAXP][32], s_w[MAXP][32];
     const int sH = s * H, sW = s * W, AC = G * P, gq = Cq / G, gc = C / G;
     const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
-    const long long total = (long long)B * G * hi;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const size_t pix = (size_t)(i % hi);
-        const int qw = (int)(pix % sW), qh = (int)(pix / sW);
-        const int g = (int)((i / hi) % G);
-        const int b = (int)(i / (hi * G));
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    long long blk = blockIdx.x;
+    const int pb = (int)(blk % pix_blocks); blk /= pix_blocks;
+    const int g = (int)(blk % G);
+    const int b = (int)(blk / G);
+    const size_t pix = (size_t)pb * 32 + tx;
+    const bool live = pix < hi;
+    const int qw = live ? (int)(pix % sW) : 0, qh = live ? (int)(pix / sW) : 0;
+
+    // phase 1: logits
+    if (live) {
         const T *qp = query + ((size_t)b * Cq + (size_t)g * gq) * hi + pix;
         const T *kp = key + ((size_t)b * Cq + (size_t)g * gq) * lo;
         const T *op = offset + ((size_t)b * AC + (size_t)g * P) * 2 * hi + pix;
-        float a[MAXP], oh[MAXP], ow[MAXP];
-        float m = -INFINITY;
-#pragma unroll
-        for (int p = 0; p < MAXP; ++p) {
-            a[p] = 0.f; oh[p] = 0.f; ow[p] = 0.f;
-            if (p < P) {
-                ow[p] = float(qw / s) + to_acc(op[(size_t)(2 * p) * hi]);
-                oh[p] = float(qh / s) + to_acc(op[(size_t)(2 * p + 1) * hi]);
-                Bilinear<float> bl;
-                bl.setup(oh[p], ow[p], H, W);
-                float acc = 0.f;
-                if (bl.inside)
-                    for (int c = 0; c < gq; ++c) acc += bl.sample(kp + (size_t)c * lo) * to_acc(qp[(size_t)c * hi]);
-                a[p] = acc;
-                m = fmaxf(m, acc);
-            }
+        for (int p = ty; p < P; p += FY) {
+            const float w = float(qw / s) + to_acc(op[(size_t)(2 * p) * hi]);
+            const float h = float(qh / s) + to_acc(op[(size_t)(2 * p + 1) * hi]);
+            Bilinear<float> bl;
+            bl.setup(h, w, H, W);
+            float acc = 0.f;
+            if (bl.inside)
+                for (int c = 0; c < gq; ++c) acc += bl.sample(kp + (size_t)c * lo) * to_acc(qp[(size_t)c * hi]);
+            s_a[p][tx] = acc;
+            s_h[p][tx] = h;
+            s_w[p][tx] = w;
         }
-        float z = 0.f;
+    }
+    __syncthreads();
+    if (!live) return;
+
+    // phase 2: softmax over the points (every thread of the pixel's column does the same few operations)
+    float m = -INFINITY;
+    for (int p = 0; p < P; ++p) m = fmaxf(m, s_a[p][tx]);
+    float z = 0.f;
+    for (int p = 0; p < P; ++p) z += expf(s_a[p][tx] - m);
+    const float inv = 1.f / z;
+    if (attn_out != nullptr)
+        for (int p = ty; p < P; p += FY)
+            attn_out[((size_t)b * AC + (size_t)g * P + p) * hi + pix] = from_acc<T>(expf(s_a[p][tx] - m) * inv);
+
+    for (int c0 = ty * CPT; c0 < gc; c0 += FY * CPT) {
+        const T *vp = value + ((size_t)b * C + (size_t)g * gc + c0) * lo;
+        const int nc = min(CPT, gc - c0);
+        float o[CPT];
 #pragma unroll
-        for (int p = 0; p < MAXP; ++p)
-            if (p < P) { a[p] = expf(a[p] - m); z += a[p]; }
-        const float inv = 1.f / z;
-#pragma unroll
-        for (int p = 0; p < MAXP; ++p)
-            if (p < P) {
-                a[p] *= inv;
-                if (attn_out != nullptr) attn_out[((size_t)b * AC + (size_t)g * P + p) * hi + pix] = from_acc<T>(a[p]);
-            }
-        // aggregation, CPT value channels at a time
-        for (int c0 = 0; c0 < gc; c0 += CPT) {
-            const T *vp = value + ((size_t)b * C + (size_t)g * gc + c0) * lo;
-            const int nc = min(CPT, gc - c0);
-            float o[CPT];
-#pragma unroll
-            for (int j = 0; j < CPT; ++j) o[j] = 0.f;
-#pragma unroll
-            for (int p = 0; p < MAXP; ++p)
-                if (p < P) {
-                    Bilinear<float> bl;
-                    bl.setup(oh[p], ow[p], H, W);
-                    if (bl.inside) {
-#pragma unroll
-                        for (int j = 0; j < CPT; ++j)
-                            if (j < nc) o[j] += bl.sample(vp + (size_t)j * lo) * a[p];
-                    }
-                }
+        for (int j = 0; j < CPT; ++j) o[j] = 0.f;
+        for (int p = 0; p < P; ++p) {
+            Bilinear<float> bl;
+            bl.setup(s_h[p][tx], s_w[p][tx], H, W);
+            if (!bl.inside) continue;
+            const float a = expf(s_a[p][tx] - m) * inv;
 #pragma unroll
             for (int j = 0; j < CPT; ++j)
-                if (j < nc) out[((size_t)b * C + (size_t)g * gc + c0 + j) * hi + pix] = from_acc<T>(o[j]);
+                if (j < nc) o[j] += bl.sample(vp + (size_t)j * lo) * a;
         }
+#pragma unroll
+        for (int j = 0; j < CPT; ++j)
+            if (j < nc) out[((size_t)b * C + (size_t)g * gc + c0 + j) * hi + pix] = from_acc<T>(o[j]);
     }
 }
 
@@ -327,11 +331,16 @@ int sapa_deform_fused_forward(const void *query, const void *key, const void *va
                  "%s: no fused kernel for num_point=%d dtype=%d (use the separate ops)", fn, P, dtype);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return SAPA_DISPATCH_FAST(dtype, [&] {
-        const long long total = (long long)B * G * s * H * s * W;
-        deform_fused_fwd_kernel<scalar_t, 8><<<grid_1d(total, 128), 128, 0, st>>>(
+        const int pix_blocks = ceil_div((long long)s * H * s * W, 32);
+        const long long blocks = (long long)B * G * pix_blocks;
+        if (blocks > 0x7fffffffLL) {
+            set_error("too many blocks");
+            return (int)SAPA_ERR_ARGUMENT;
+        }
+        deform_fused_fwd_kernel<scalar_t, 8><<<(unsigned)blocks, dim3(32, FY), 0, st>>>(
             static_cast<const scalar_t *>(query), static_cast<const scalar_t *>(key), static_cast<const scalar_t *>(value),
             static_cast<const scalar_t *>(offset), static_cast<scalar_t *>(out), static_cast<scalar_t *>(attn), B, Cq, C, H,
-            W, P, s, G);
+            W, P, s, G, pix_blocks);
         return check_launch("deform_fused_fwd_kernel");
     });
 }

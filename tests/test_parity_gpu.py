@@ -448,3 +448,32 @@ def test_error_behaviour_on_cuda_tensors(sp):
     # K = 7 still works through the public op (separate kernels behind the same function)
     v = torch.randn(1, 3, 4, 4, device=DEV)
     assert sp.sapa_fused(q, k, v, 7, 2).shape == (1, 3, 8, 8)
+
+
+def test_config4_decoder_pyramid_bf16_forward(sp):
+    """BASELINE config 4 (stand-in wiring, random init): encoder features of 64/128/320/512 channels at
+    128^2/64^2/32^2/16^2 are projected to 256 channels and upsampled 16^2 -> 32^2 -> 64^2 -> 128^2 by three
+    chained SAPA modules (d=32, K=5), bf16, forward only.  Checked against the same modules in float32 on the
+    separate-op path (1e-2 of the output range; batch 2 instead of 16 keeps the test small)."""
+    torch.manual_seed(0)
+    B = 2
+    feats = [torch.randn(B, c, r, r, device=DEV) for c, r in ((64, 128), (128, 64), (320, 32), (512, 16))]
+    proj = [torch.nn.Conv2d(c, 256, 1).to(DEV) for c in (64, 128, 320, 512)]
+    ups = [sp.SAPA(256, embedding_dim=32).to(DEV) for _ in range(3)]
+
+    def run(dtype, impl):
+        with torch.no_grad():
+            ys = [p.to(dtype)(f.to(dtype)) for p, f in zip(proj, feats)]
+            x = ys[3]
+            for level, m in zip((2, 1, 0), ups):
+                m.impl = impl
+                x = m.to(dtype)(ys[level], x)
+            return x
+
+    want = run(torch.float32, "separate")
+    got = run(torch.bfloat16, "fused")
+    for m in ups:
+        m.impl = "fused"
+    assert got.shape == (B, 256, 128, 128) and got.dtype == torch.bfloat16
+    assert rel_err(host64(got), host64(want)) < 2e-2
+    assert rel_err(host64(run(torch.float32, "fused")), host64(want)) < 1e-5
