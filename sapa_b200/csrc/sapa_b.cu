@@ -539,7 +539,7 @@ static inline int grid_1d(long long total, int threads) {
 bool fused_mma_supported(int W, int dtype);
 bool fused_tma_supported(int W, int dtype);
 int launch_fused_tma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
-                     int rows, int ytop0, cudaStream_t st);
+                     int rows, int ytop0, int dtype, cudaStream_t st);
 int launch_fused_mma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
                      int rows, int ytop0, int dtype, cudaStream_t st);
 
@@ -715,7 +715,7 @@ int sapa_fused_forward_slab(const void *query, const void *key, const void *valu
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int impl = fused_impl_choice();
     if (K == 5 && impl == 0 && fused_tma_supported(W, dtype)) {
-        const int e = launch_fused_tma(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, st);
+        const int e = launch_fused_tma(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
     if (K == 5 && impl != 1 && fused_mma_supported(W, dtype))

@@ -52,7 +52,7 @@ __device__ unsigned g_next_tile[SCHED_SLOTS];
 __device__ unsigned g_ctas_done[SCHED_SLOTS];
 
 struct Args {
-    float *out, *attn;
+    void *out, *attn;
     int B, d, C, H, W;
     int rows, ytop0;
     int tiles_x, tiles_y;
@@ -219,7 +219,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             atomicExch(&g_wait_timeout, 1);
             return;
         }
-        const unsigned stage = ring_addr + (it % NSTAGE) * SLOT_BYTES;
+        const unsigned stage = ring_addr + (gs % NSTAGE) * SLOT_BYTES;
 
         if (it < nk) {
             // ------------------------------------------------------------- logits: S[16 px][8 cells] += Qt[16 px][8 ch] K[8 ch][8 cells]
@@ -271,7 +271,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     for (int dy = 0; dy < 5; ++dy) { s[r][dy][0] *= inv; s[r][dy][1] *= inv; }
                 }
                 if (a.attn != nullptr && y < a.H && x0 + 4 * h + l < a.W) {
-                    float *an = a.attn + (size_t)n * 25 * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h) + g;
+                    float *an = static_cast<float *>(a.attn) + (size_t)n * 25 * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h) + g;
 #pragma unroll
                     for (int dy = 0; dy < 5; ++dy)
 #pragma unroll
@@ -374,6 +374,301 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     }
 }
 
+// ---------------------------------------------------------------------------------- float16 / bfloat16
+// Same tile (4 x 8 low-res pixels), ring, barriers and scheduler as the float32 kernel; what differs:
+//   * key / value boxes are 24 columns wide and start at x0 - 8, the nearest 16-byte boundary below the halo
+//     (window cell j of the tile sits in box column j + 6); rows are 48 bytes, unswizzled: eight consecutive
+//     channels start in eight different 16-byte bank groups, so ldmatrix and the per-lane loads are conflict-free;
+//   * query and output boxes are [8 high-res rows][channels][16 pixels] with 32-byte rows and the 32-byte swizzle;
+//   * a warp owns ONE high-res row (16 pixels): warp = (low-res row, upper / lower high-res row);
+//   * logits: m16n8k16 over three 8-column tiles of the box per window row; the probabilities of columns
+//     (6+2t, 7+2t) and (14+2t, 15+2t), which the aggregation's B fragment wants, are held by lane (t+3)&3 of the
+//     same quad, so one quad rotation of the packed pairs re-aligns them.
+namespace h16 {
+constexpr int BC = 24;                          // key / value box columns
+constexpr int KROW = BC * 2;                    // 48 bytes
+constexpr int QROW = 32;                        // 16 high-res pixels
+constexpr int K_BYTES = HH * KCH * KROW;        // 6144
+constexpr int Q_BYTES = 2 * ROWS * KCH * QROW;  // 4096
+constexpr int V_BYTES = HH * VCH * KROW;        // 12288
+constexpr int SLOT_BYTES = V_BYTES > K_BYTES + Q_BYTES ? V_BYTES : K_BYTES + Q_BYTES;
+constexpr int O_BYTES = 2 * ROWS * VCH * QROW;  // 8192
+static_assert(K_BYTES % 256 == 0 && SLOT_BYTES % 256 == 0 && O_BYTES % 256 == 0, "swizzled boxes need 256-byte alignment");
+}  // namespace h16
+
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_trans(unsigned (&r)[2], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma_h16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    if constexpr (std::is_same<T, __half>::value)
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_pair(__half, float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const unsigned *>(&h);
+}
+__device__ __forceinline__ unsigned pack_pair(__nv_bfloat16, float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const unsigned *>(&h);
+}
+__device__ __forceinline__ void sts32(unsigned addr, unsigned v) {
+    asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(addr), "r"(v) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT, CTAS_PER_SM)
+sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                         const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap, const Args a) {
+    using namespace h16;
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) unsigned long long full_bar[NSTAGE];
+    const unsigned ring_addr = ((unsigned)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
+    const unsigned bar_addr = (unsigned)__cvta_generic_to_shared(full_bar);
+    const unsigned obuf_addr = ring_addr + NSTAGE * h16::SLOT_BYTES;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wrow = warp >> 1, r = warp & 1;
+    const int g = lane >> 2, t = lane & 3;
+    const int sW = 2 * a.W;
+    const size_t hi_plane = (size_t)(2 * a.H) * sW;
+    const int nk = (a.d + KCH - 1) / KCH, nv = (a.C + VCH - 1) / VCH, total = nk + nv;
+    const int ntiles = a.B * a.tiles_x * a.tiles_y;
+    __shared__ int tile_ids[4];
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < NSTAGE; ++i) mbar_init(bar_addr + 8 * i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    bool exhausted = false;
+    auto issue = [&](int gs) {     // thread 0 only; see the float32 kernel
+        if (exhausted) return;
+        const int ti = gs / total, it = gs - ti * total;
+        if (it == 0) {
+            int claimed = (int)blockIdx.x;
+            if (ti > 0) claimed = (int)(atomicAdd(&g_next_tile[a.sched_slot], 1u) + gridDim.x);
+            if (claimed >= ntiles) claimed = -1;
+            tile_ids[ti & 3] = claimed;
+            if (claimed < 0) { exhausted = true; return; }
+        }
+        int tile = tile_ids[ti & 3];
+        const int tbx = tile % a.tiles_x; tile /= a.tiles_x;
+        const int tby = tile % a.tiles_y; tile /= a.tiles_y;
+        const int tx0 = tbx * COLS, ty0 = tby * ROWS;
+        const unsigned slot = ring_addr + (gs % NSTAGE) * h16::SLOT_BYTES, bar = bar_addr + 8 * (gs % NSTAGE);
+        mbar_expect_tx(bar, it < nk ? h16::K_BYTES + Q_BYTES : h16::V_BYTES);
+        if (it < nk) {
+            tma_load_4d(slot, &kmap, bar, tx0 - 8, it * KCH, a.ytop0 + ty0 - 2, tile);
+            tma_load_4d(slot + h16::K_BYTES, &qmap, bar, 2 * tx0, it * KCH, 2 * ty0, tile);
+        } else {
+            tma_load_4d(slot, &vmap, bar, tx0 - 8, (it - nk) * VCH, a.ytop0 + ty0 - 2, tile);
+        }
+    };
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < NSTAGE - 1; ++i) issue(i);
+    }
+
+    // Lane (g,t) holds, for the pixels g and g+8 of its row, the box columns 8*tile + 2t, +1 (tile = 0..2).  The
+    // parent of pixel px is l = px/2 and its window covers box columns l+6 .. l+10.
+    bool ok[2][3][2];
+#pragma unroll
+    for (int p = 0; p < 2; ++p)
+#pragma unroll
+        for (int c = 0; c < 3; ++c)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int col = 8 * c + 2 * t + i, l = (g >> 1) + 4 * p;
+                ok[p][c][i] = (col >= l + 6) && (col <= l + 10);
+            }
+
+    // ldmatrix row addresses: query matrices (ch 0-7 | 8-15) x (px 0-7 | 8-15), key matrices (ch 0-7 | 8-15) x 8 columns
+    const int qch = (lane & 7) + 8 * (lane >> 4);
+    const int q_off = h16::K_BYTES + (2 * wrow + r) * (KCH * QROW) + qch * QROW + (((((lane >> 3) & 1) ^ (qch >> 2)) & 1) << 4);
+    const int kch = (lane & 7) + 8 * ((lane >> 3) & 1);
+    const int k_off = wrow * (KCH * KROW) + kch * KROW + (lane >> 4) * 16;
+    const int k_off2 = wrow * (KCH * KROW) + kch * KROW + 32;
+    // value A fragment: channel g (and g+8), box columns 6+2t, 7+2t (and +8)
+    const int v_off = wrow * (VCH * KROW) + g * KROW + (6 + 2 * t) * 2;
+    // output D fragment: channel g (and g+8), pixels 8p + 2t, +1
+    const int o_off = (2 * wrow + r) * (VCH * QROW) + g * QROW + 4 * t;
+    const int o_sw = (g >> 2) & 1;
+
+    float s[2][5][3][2];          // logits, then probabilities: [pixel g | g+8][dy][column tile][column 2t | 2t+1]
+    unsigned pb[2][5][2];         // B fragments of the aggregation
+
+    int gs = 0;
+    for (int ti = 0;; ++ti) {
+    int tile = ti == 0 ? (int)blockIdx.x : tile_ids[ti & 3];
+    if (tile < 0) break;
+    const int bx = tile % a.tiles_x; tile /= a.tiles_x;
+    const int by = tile % a.tiles_y; tile /= a.tiles_y;
+    const int n = tile;
+    const int x0 = bx * COLS, y0 = by * ROWS;
+    const int y = y0 + wrow;
+#pragma unroll
+    for (int p = 0; p < 2; ++p)
+#pragma unroll
+        for (int dy = 0; dy < 5; ++dy)
+#pragma unroll
+            for (int c = 0; c < 3; ++c) s[p][dy][c][0] = s[p][dy][c][1] = 0.f;
+
+    for (int it = 0; it < total; ++it, ++gs) {
+        __syncthreads();
+        if (tid == 0) {
+            if (it > nk) {
+                tma_store_4d(&omap, obuf_addr + ((it - nk - 1) & 1) * h16::O_BYTES, 2 * x0, (it - nk - 1) * VCH, 2 * y0, n);
+                asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+            }
+            issue(gs + NSTAGE - 1);
+        }
+        if (!mbar_wait_bounded(bar_addr + 8 * (gs % NSTAGE), (gs / NSTAGE) & 1)) {
+            atomicExch(&g_wait_timeout, 1);
+            return;
+        }
+        const unsigned stage = ring_addr + (gs % NSTAGE) * h16::SLOT_BYTES;
+
+        if (it < nk) {
+            // ------------------------------------------------------------- logits: S[16 px][24 cols] += Qt[16 px][16 ch] K[16 ch][24 cols]
+            unsigned qa[4];
+            ldsm_x4_trans(qa, stage + q_off);
+#pragma unroll
+            for (int dy = 0; dy < 5; ++dy) {
+                unsigned kb[4], kc[2];
+                ldsm_x4_trans(kb, stage + k_off + dy * (KCH * KROW));
+                ldsm_x2_trans(kc, stage + k_off2 + dy * (KCH * KROW));
+                float d0[4] = {s[0][dy][0][0], s[0][dy][0][1], s[1][dy][0][0], s[1][dy][0][1]};
+                float d1[4] = {s[0][dy][1][0], s[0][dy][1][1], s[1][dy][1][0], s[1][dy][1][1]};
+                float d2[4] = {s[0][dy][2][0], s[0][dy][2][1], s[1][dy][2][0], s[1][dy][2][1]};
+                mma_h16<T>(d0, qa, kb[0], kb[1]);
+                mma_h16<T>(d1, qa, kb[2], kb[3]);
+                mma_h16<T>(d2, qa, kc[0], kc[1]);
+                s[0][dy][0][0] = d0[0]; s[0][dy][0][1] = d0[1]; s[1][dy][0][0] = d0[2]; s[1][dy][0][1] = d0[3];
+                s[0][dy][1][0] = d1[0]; s[0][dy][1][1] = d1[1]; s[1][dy][1][0] = d1[2]; s[1][dy][1][1] = d1[3];
+                s[0][dy][2][0] = d2[0]; s[0][dy][2][1] = d2[1]; s[1][dy][2][0] = d2[2]; s[1][dy][2][1] = d2[3];
+            }
+            if (it == nk - 1) {
+#pragma unroll
+                for (int p = 0; p < 2; ++p) {
+                    float m = -INFINITY;
+#pragma unroll
+                    for (int dy = 0; dy < 5; ++dy)
+#pragma unroll
+                        for (int c = 0; c < 3; ++c)
+#pragma unroll
+                            for (int i = 0; i < 2; ++i)
+                                if (ok[p][c][i]) m = fmaxf(m, s[p][dy][c][i]);
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                    float z = 0.f;
+#pragma unroll
+                    for (int dy = 0; dy < 5; ++dy)
+#pragma unroll
+                        for (int c = 0; c < 3; ++c)
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                s[p][dy][c][i] = ok[p][c][i] ? expf(s[p][dy][c][i] - m) : 0.f;
+                                z += s[p][dy][c][i];
+                            }
+                    z += __shfl_xor_sync(0xffffffffu, z, 1);
+                    z += __shfl_xor_sync(0xffffffffu, z, 2);
+                    const float inv = 1.f / z;
+#pragma unroll
+                    for (int dy = 0; dy < 5; ++dy)
+#pragma unroll
+                        for (int c = 0; c < 3; ++c) { s[p][dy][c][0] *= inv; s[p][dy][c][1] *= inv; }
+                }
+                if (a.attn != nullptr && y < a.H) {
+                    T *an = static_cast<T *>(a.attn) + (size_t)n * 25 * hi_plane + (size_t)(2 * y + r) * sW + 2 * x0 + g;
+#pragma unroll
+                    for (int p = 0; p < 2; ++p) {
+                        const int l = (g >> 1) + 4 * p;
+                        if (x0 + l < a.W) {
+#pragma unroll
+                            for (int dy = 0; dy < 5; ++dy)
+#pragma unroll
+                                for (int c = 0; c < 3; ++c)
+#pragma unroll
+                                    for (int i = 0; i < 2; ++i)
+                                        if (ok[p][c][i])
+                                            an[(size_t)(dy * 5 + 8 * c + 2 * t + i - 6 - l) * hi_plane + 8 * p] = from_acc<T>(s[p][dy][c][i]);
+                        }
+                    }
+                }
+                // quad rotation: lane t takes the packed pairs of lane (t+3)&3; columns 6+2t.. are that lane's tile
+                // (t+3)>>2 and columns 14+2t.. its tile (t+7)>>2
+                const int src = (lane & ~3) | ((t + 3) & 3);
+#pragma unroll
+                for (int p = 0; p < 2; ++p)
+#pragma unroll
+                    for (int dy = 0; dy < 5; ++dy) {
+                        const unsigned v0 = __shfl_sync(0xffffffffu, pack_pair(T(), s[p][dy][0][0], s[p][dy][0][1]), src);
+                        const unsigned v1 = __shfl_sync(0xffffffffu, pack_pair(T(), s[p][dy][1][0], s[p][dy][1][1]), src);
+                        const unsigned v2 = __shfl_sync(0xffffffffu, pack_pair(T(), s[p][dy][2][0], s[p][dy][2][1]), src);
+                        pb[p][dy][0] = t == 0 ? v0 : v1;
+                        pb[p][dy][1] = t == 0 ? v1 : v2;
+                    }
+            }
+        } else {
+            // ------------------------------------------------------------- aggregation: Out[16 ch][8 px] += V[16 ch][16 cols] P[16 cols][8 px]
+            float acc[VCH / 16][2][4];
+#pragma unroll
+            for (int b = 0; b < VCH / 16; ++b)
+#pragma unroll
+                for (int p = 0; p < 2; ++p)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[b][p][i] = 0.f;
+#pragma unroll
+            for (int dy = 0; dy < 5; ++dy)
+#pragma unroll
+                for (int b = 0; b < VCH / 16; ++b) {
+                    const unsigned vp = stage + v_off + dy * (VCH * KROW) + b * 16 * KROW;
+                    const unsigned av[4] = {lds32(vp), lds32(vp + 8 * KROW), lds32(vp + 16), lds32(vp + 8 * KROW + 16)};
+#pragma unroll
+                    for (int p = 0; p < 2; ++p) mma_h16<T>(acc[b][p], av, pb[p][dy][0], pb[p][dy][1]);
+                }
+            const unsigned ob = obuf_addr + ((it - nk) & 1) * h16::O_BYTES + o_off;
+#pragma unroll
+            for (int b = 0; b < VCH / 16; ++b)
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+#pragma unroll
+                    for (int p = 0; p < 2; ++p)
+                        sts32(ob + (16 * b + 8 * half) * QROW + ((p ^ o_sw) << 4),
+                              pack_pair(T(), acc[b][p][2 * half], acc[b][p][2 * half + 1]));
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        tma_store_4d(&omap, obuf_addr + ((nv - 1) & 1) * h16::O_BYTES, 2 * x0, (nv - 1) * VCH, 2 * y0, n);
+        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+    }
+    }
+    if (tid == 0) {
+        asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+        if (atomicAdd(&g_ctas_done[a.sched_slot], 1u) == gridDim.x - 1) {
+            g_next_tile[a.sched_slot] = 0u;
+            g_ctas_done[a.sched_slot] = 0u;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------- host side
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -393,53 +688,36 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// 4-D map over an NCHW float32 tensor seen as (x, channel, y, image); box = 16 columns x box_ch channels x 8 rows
-static bool make_map(CUtensorMap *map, const void *base, int width, int height, int channels, int images, int box_ch) {
+// 4-D map over a dense NCHW tensor seen as (x, channel, y, image); box = box_w columns x box_ch channels x 8 rows
+static bool make_map(CUtensorMap *map, const void *base, int width, int height, int channels, int images, int box_ch,
+                     CUtensorMapDataType type, int esize, int box_w, CUtensorMapSwizzle swizzle) {
     EncodeTiledFn encode = encode_tiled_fn();
     if (encode == nullptr) return false;
     const cuuint64_t dims[4] = {(cuuint64_t)width, (cuuint64_t)channels, (cuuint64_t)height, (cuuint64_t)images};
-    const cuuint64_t strides[3] = {(cuuint64_t)height * width * 4, (cuuint64_t)width * 4, (cuuint64_t)channels * height * width * 4};
-    const cuuint32_t box[4] = {16u, (cuuint32_t)box_ch, 8u, 1u};
+    const cuuint64_t strides[3] = {(cuuint64_t)height * width * esize, (cuuint64_t)width * esize,
+                                   (cuuint64_t)channels * height * width * esize};
+    const cuuint32_t box[4] = {(cuuint32_t)box_w, (cuuint32_t)box_ch, 8u, 1u};
     const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void *>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return encode(map, type, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-}  // namespace tma
-
-// float32, K = 5, s = 2 and every row of every tensor on a 16-byte boundary
-bool fused_tma_supported(int W, int dtype) { return dtype == SAPA_F32 && W % 4 == 0 && tma::encode_tiled_fn() != nullptr; }
-
-// Returns SAPA_ERR_UNSUPPORTED when a tensor map cannot be built (the caller then uses the cp.async kernel).
-int launch_fused_tma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
-                     int rows, int ytop0, cudaStream_t st) {
-    using namespace tma;
-    CUtensorMap qmap, kmap, vmap, omap;
-    if (!make_map(&qmap, q, 2 * W, 2 * H, d, B, KCH) || !make_map(&kmap, k, W, rows, d, B, KCH) ||
-        !make_map(&vmap, v, W, rows, C, B, VCH) || !make_map(&omap, out, 2 * W, 2 * H, C, B, VCH)) {
-        set_error("sapa_tma_fused: cuTensorMapEncodeTiled rejected the tensor layout");
-        return SAPA_ERR_UNSUPPORTED;
-    }
-    Args a{};
-    a.out = static_cast<float *>(out); a.attn = static_cast<float *>(attn);
-    a.B = B; a.d = d; a.C = C; a.H = H; a.W = W; a.rows = rows; a.ytop0 = ytop0;
-    a.tiles_x = ceil_div(W, COLS);
-    a.tiles_y = ceil_div(H, ROWS);
-    const long long nblocks = (long long)B * a.tiles_x * a.tiles_y;
+template <typename Kernel>
+static int launch_persistent(Kernel kernel, const char *name, int smem, const CUtensorMap &qmap, const CUtensorMap &kmap,
+                             const CUtensorMap &vmap, const CUtensorMap &omap, Args &a, cudaStream_t st) {
+    const long long nblocks = (long long)a.B * a.tiles_x * a.tiles_y;
     if (nblocks > 0x7fffffffLL) {
         set_error("too many tiles");
         return SAPA_ERR_ARGUMENT;
     }
-    constexpr int smem = NSTAGE * SLOT_BYTES + 2 * O_BYTES + 1024;
-    const cudaError_t e = cudaFuncSetAttribute(sapa_tma_fused_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) {
-        set_error("sapa_tma_fused: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+        set_error("%s: cudaFuncSetAttribute failed: %s", name, cudaGetErrorString(e));
         return SAPA_ERR_LAUNCH;
     }
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
-        set_error("sapa_tma_fused: cannot query the SM count");
+        set_error("%s: cannot query the SM count", name);
         return SAPA_ERR_LAUNCH;
     }
     const long long resident = (long long)CTAS_PER_SM * sms;
@@ -447,8 +725,53 @@ int launch_fused_tma(const void *q, const void *k, const void *v, void *out, voi
     const unsigned grid = (unsigned)(nblocks < resident ? nblocks : resident);
     static std::atomic<unsigned> next_slot{0};
     a.sched_slot = (int)(next_slot.fetch_add(1u) % SCHED_SLOTS);
-    sapa_tma_fused_f32_kernel<<<grid, NT, smem, st>>>(qmap, kmap, vmap, omap, a);
-    return check_launch("sapa_tma_fused_f32_kernel");
+    kernel<<<grid, NT, smem, st>>>(qmap, kmap, vmap, omap, a);
+    return check_launch(name);
+}
+
+}  // namespace tma
+
+// K = 5, s = 2 and every row of every tensor on a 16-byte boundary
+bool fused_tma_supported(int W, int dtype) {
+    if (tma::encode_tiled_fn() == nullptr) return false;
+    if (dtype == SAPA_F32) return W % 4 == 0;
+    if (dtype == SAPA_F16 || dtype == SAPA_BF16) return W % 8 == 0;
+    return false;
+}
+
+// Returns SAPA_ERR_UNSUPPORTED when a tensor map cannot be built (the caller then uses the cp.async kernel).
+int launch_fused_tma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
+                     int rows, int ytop0, int dtype, cudaStream_t st) {
+    using namespace tma;
+    CUtensorMap qmap, kmap, vmap, omap;
+    bool ok;
+    if (dtype == SAPA_F32) {
+        const auto ty = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+        const auto sw = CU_TENSOR_MAP_SWIZZLE_64B;
+        ok = make_map(&qmap, q, 2 * W, 2 * H, d, B, KCH, ty, 4, HC, sw) && make_map(&kmap, k, W, rows, d, B, KCH, ty, 4, HC, sw) &&
+             make_map(&vmap, v, W, rows, C, B, VCH, ty, 4, HC, sw) && make_map(&omap, out, 2 * W, 2 * H, C, B, VCH, ty, 4, HC, sw);
+    } else {
+        const auto ty = dtype == SAPA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        const auto none = CU_TENSOR_MAP_SWIZZLE_NONE, sw = CU_TENSOR_MAP_SWIZZLE_32B;
+        ok = make_map(&qmap, q, 2 * W, 2 * H, d, B, KCH, ty, 2, 16, sw) && make_map(&kmap, k, W, rows, d, B, KCH, ty, 2, h16::BC, none) &&
+             make_map(&vmap, v, W, rows, C, B, VCH, ty, 2, h16::BC, none) && make_map(&omap, out, 2 * W, 2 * H, C, B, VCH, ty, 2, 16, sw);
+    }
+    if (!ok) {
+        set_error("sapa_tma_fused: cuTensorMapEncodeTiled rejected the tensor layout");
+        return SAPA_ERR_UNSUPPORTED;
+    }
+    Args a{};
+    a.out = out; a.attn = attn;
+    a.B = B; a.d = d; a.C = C; a.H = H; a.W = W; a.rows = rows; a.ytop0 = ytop0;
+    a.tiles_x = ceil_div(W, COLS);
+    a.tiles_y = ceil_div(H, ROWS);
+    constexpr int smem32 = NSTAGE * SLOT_BYTES + 2 * O_BYTES + 1024;
+    constexpr int smem16 = NSTAGE * h16::SLOT_BYTES + 2 * h16::O_BYTES + 1024;
+    if (dtype == SAPA_F32)
+        return launch_persistent(sapa_tma_fused_f32_kernel, "sapa_tma_fused_f32_kernel", smem32, qmap, kmap, vmap, omap, a, st);
+    if (dtype == SAPA_F16)
+        return launch_persistent(sapa_tma_fused_16_kernel<__half>, "sapa_tma_fused_16_kernel", smem16, qmap, kmap, vmap, omap, a, st);
+    return launch_persistent(sapa_tma_fused_16_kernel<__nv_bfloat16>, "sapa_tma_fused_16_kernel", smem16, qmap, kmap, vmap, omap, a, st);
 }
 
 // 1 if a bounded mbarrier wait of the TMA kernel ever gave up on the current device (synchronises the device).

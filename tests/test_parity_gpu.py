@@ -152,6 +152,7 @@ def test_sapa_d_half_precision(sp, oracle, name, dtype):
 
 SHAPES_B = [  # B, d, C, H, W: tile overhang in both directions, channel-chunk tails, a single pixel
     (2, 64, 48, 9, 40), (1, 7, 5, 4, 33), (3, 2, 1, 1, 1), (1, 13, 9, 17, 3), (1, 32, 256, 8, 64),
+    (4, 16, 40, 64, 64),   # 512 tiles: persistent CTAs take several tiles, 3 stages per tile against a ring of 4
 ]
 
 
@@ -176,6 +177,24 @@ def test_sapa_b_seeded_vs_oracle(sp, oracle, shape, K):
     prob = torch.softmax(sp.qk(qd.detach(), kd.detach(), K, s), dim=1)
     assert rel_err(host64(prob), want_p) < 1e-5
     assert rel_err(host64(sp.av(prob, vd.detach(), K, s)), want) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(2, 64, 48, 9, 40), (4, 16, 40, 64, 64), (1, 24, 72, 7, 8), (1, 8, 16, 5, 12)])
+def test_sapa_b_half_precision_fused_forward_vs_oracle(sp, oracle, shape, dtype):
+    """16-bit fused forward (rows of 16 bytes: tensor-map kernel; W=12: cp.async kernel) against the float64 oracle
+    evaluated on the same rounded inputs; tolerance 1e-2 (16-bit probabilities and outputs)."""
+    from sapa_b200.functions import fused_forward_raw
+    B, d, C, H, W = shape
+    K, s = 5, 2
+    g = torch.Generator().manual_seed(77 + H * W)
+    q, k, v = (torch.randn(*sh, generator=g).to(dtype) for sh in ((B, d, s * H, s * W), (B, d, H, W), (B, C, H, W)))
+    want, want_p = oracle.sapa_forward(q.double().numpy(), k.double().numpy(), v.double().numpy(), K, s, return_attn=True)
+    out, attn = fused_forward_raw(q.to(DEV), k.to(DEV), v.to(DEV), K, s, True)
+    assert rel_err(host64(out), want) < 1e-2
+    assert rel_err(host64(attn), want_p) < 1e-2
+    out2, _ = fused_forward_raw(q.to(DEV), k.to(DEV), v.to(DEV), K, s, False)
+    assert torch.equal(out, out2)
 
 
 def test_sapa_b_config2_full_size_vs_oracle_float32(sp, oracle):
@@ -471,9 +490,8 @@ def test_config4_decoder_pyramid_bf16_forward(sp):
             return x
 
     want = run(torch.float32, "separate")
-    got = run(torch.bfloat16, "fused")
-    for m in ups:
-        m.impl = "fused"
+    fused32 = run(torch.float32, "fused")
+    got = run(torch.bfloat16, "fused")           # last: .to(bfloat16) rounds the modules' weights in place
     assert got.shape == (B, 256, 128, 128) and got.dtype == torch.bfloat16
     assert rel_err(host64(got), host64(want)) < 2e-2
-    assert rel_err(host64(run(torch.float32, "fused")), host64(want)) < 1e-5
+    assert rel_err(host64(fused32), host64(want)) < 1e-5
