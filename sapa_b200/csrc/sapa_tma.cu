@@ -187,7 +187,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     //   output D fragment: channel g (and g+8), pixels 8h+2t, 8h+2t+1 of high-res rows 2*wrow, 2*wrow+1
     const int o_off = (2 * wrow) * (VCH * ROWB) + g * ROWB + swz(8 * h + 2 * t, g);
 
-    float s[2][5][2];                      // logits, then probabilities: [row][dy][cell 2t | 2t+1]
+    float s[5][4];                         // logits, then probabilities: [dy][2 * row + (cell 2t | 2t+1)], the MMA's D fragment
     unsigned phi[2][5][2];                 // B fragments of the aggregation: probabilities of cells (t, t+4); their
                                            // low tf32 terms are derived where they are used (2 ALU ops, 20 registers saved)
 
@@ -204,7 +204,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
 #pragma unroll
     for (int r = 0; r < 2; ++r)
 #pragma unroll
-        for (int dy = 0; dy < 5; ++dy) s[r][dy][0] = s[r][dy][1] = 0.f;
+        for (int dy = 0; dy < 5; ++dy) s[dy][2 * r] = s[dy][2 * r + 1] = 0.f;
 
     for (int it = 0; it < total; ++it, ++gs) {
         __syncthreads();     // everyone is done with the slot that is refilled next and has written its output fragment
@@ -238,11 +238,9 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 for (int dy = 0; dy < 5; ++dy) {
                     const unsigned b0 = lds32(kb + dy * (KCH * ROWB) + ks * 8 * ROWB + k_off0);
                     const unsigned b1 = lds32(kb + dy * (KCH * ROWB) + ks * 8 * ROWB + k_off1);
-                    float dacc[4] = {s[0][dy][0], s[0][dy][1], s[1][dy][0], s[1][dy][1]};
-                    mma_tf32(dacc, ah, b0, b1);
-                    mma_tf32(dacc, al, b0, b1);
-                    mma_tf32(dacc, ah, tf32_lo(b0), tf32_lo(b1));
-                    s[0][dy][0] = dacc[0]; s[0][dy][1] = dacc[1]; s[1][dy][0] = dacc[2]; s[1][dy][1] = dacc[3];
+                    mma_tf32(s[dy], ah, b0, b1);
+                    mma_tf32(s[dy], al, b0, b1);
+                    mma_tf32(s[dy], ah, tf32_lo(b0), tf32_lo(b1));
                 }
             }
             if (it == nk - 1) {
@@ -252,23 +250,23 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     float m = -INFINITY;
 #pragma unroll
                     for (int dy = 0; dy < 5; ++dy) {
-                        if (ok0) m = fmaxf(m, s[r][dy][0]);
-                        if (ok1) m = fmaxf(m, s[r][dy][1]);
+                        if (ok0) m = fmaxf(m, s[dy][2 * r]);
+                        if (ok1) m = fmaxf(m, s[dy][2 * r + 1]);
                     }
                     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
                     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
                     float z = 0.f;
 #pragma unroll
                     for (int dy = 0; dy < 5; ++dy) {
-                        s[r][dy][0] = ok0 ? expf(s[r][dy][0] - m) : 0.f;
-                        s[r][dy][1] = ok1 ? expf(s[r][dy][1] - m) : 0.f;
-                        z += s[r][dy][0] + s[r][dy][1];
+                        s[dy][2 * r] = ok0 ? expf(s[dy][2 * r] - m) : 0.f;
+                        s[dy][2 * r + 1] = ok1 ? expf(s[dy][2 * r + 1] - m) : 0.f;
+                        z += s[dy][2 * r] + s[dy][2 * r + 1];
                     }
                     z += __shfl_xor_sync(0xffffffffu, z, 1);
                     z += __shfl_xor_sync(0xffffffffu, z, 2);
                     const float inv = 1.f / z;
 #pragma unroll
-                    for (int dy = 0; dy < 5; ++dy) { s[r][dy][0] *= inv; s[r][dy][1] *= inv; }
+                    for (int dy = 0; dy < 5; ++dy) { s[dy][2 * r] *= inv; s[dy][2 * r + 1] *= inv; }
                 }
                 if (a.attn != nullptr && y < a.H && x0 + 4 * h + l < a.W) {
                     float *an = static_cast<float *>(a.attn) + (size_t)n * 25 * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h) + g;
@@ -276,8 +274,8 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     for (int dy = 0; dy < 5; ++dy)
 #pragma unroll
                         for (int r = 0; r < 2; ++r) {
-                            if (ok0) an[(size_t)(dy * 5 + 2 * t - l) * hi_plane + (size_t)r * sW] = s[r][dy][0];
-                            if (ok1) an[(size_t)(dy * 5 + 2 * t + 1 - l) * hi_plane + (size_t)r * sW] = s[r][dy][1];
+                            if (ok0) an[(size_t)(dy * 5 + 2 * t - l) * hi_plane + (size_t)r * sW] = s[dy][2 * r];
+                            if (ok1) an[(size_t)(dy * 5 + 2 * t + 1 - l) * hi_plane + (size_t)r * sW] = s[dy][2 * r + 1];
                         }
                 }
                 // cells (2t, 2t+1) -> cells (t, t+4), the k order of the value fragments; split into tf32 hi / lo
@@ -287,8 +285,8 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 for (int r = 0; r < 2; ++r)
 #pragma unroll
                     for (int dy = 0; dy < 5; ++dy) {
-                        const float a0 = __shfl_sync(0xffffffffu, s[r][dy][0], src_a), a1 = __shfl_sync(0xffffffffu, s[r][dy][1], src_a);
-                        const float b0 = __shfl_sync(0xffffffffu, s[r][dy][0], src_b), b1 = __shfl_sync(0xffffffffu, s[r][dy][1], src_b);
+                        const float a0 = __shfl_sync(0xffffffffu, s[dy][2 * r], src_a), a1 = __shfl_sync(0xffffffffu, s[dy][2 * r + 1], src_a);
+                        const float b0 = __shfl_sync(0xffffffffu, s[dy][2 * r], src_b), b1 = __shfl_sync(0xffffffffu, s[dy][2 * r + 1], src_b);
                         const unsigned ua = __float_as_uint(odd ? a1 : a0), ub = __float_as_uint(odd ? b1 : b0);
                         phi[r][dy][0] = ua; phi[r][dy][1] = ub;
                     }
@@ -331,6 +329,8 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 for (int b = 0; b < VCH / 16; ++b)
 #pragma unroll
                     for (int r = 0; r < 2; ++r) mma_tf32(acc[b][r], ah[b], phi[r][dy][0], phi[r][dy][1]);
+                // (Folding the two correction terms into one bfloat16 m16n8k16 MMA was tried: the four extra
+                // float -> bfloat16 packs per fragment cost as much as the MMA they save, and the error grew to 4e-6.)
 #pragma unroll
                 for (int b = 0; b < VCH / 16; ++b)
 #pragma unroll
@@ -374,17 +374,42 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     }
 }
 
+__device__ __forceinline__ bool mbar_test_wait(unsigned bar, unsigned parity) {     // never suspends
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
 // ---------------------------------------------------------------------------------- float16 / bfloat16
-// Same tile (4 x 8 low-res pixels), ring, barriers and scheduler as the float32 kernel; what differs:
+// Same tile (4 x 8 low-res pixels) and scheduler as the float32 kernel; what differs:
 //   * key / value boxes are 24 columns wide and start at x0 - 8, the nearest 16-byte boundary below the halo
 //     (window cell j of the tile sits in box column j + 6); rows are 48 bytes, unswizzled: eight consecutive
-//     channels start in eight different 16-byte bank groups, so ldmatrix and the per-lane loads are conflict-free;
-//   * query and output boxes are [8 high-res rows][channels][16 pixels] with 32-byte rows and the 32-byte swizzle;
-//   * a warp owns ONE high-res row (16 pixels): warp = (low-res row, upper / lower high-res row);
-//   * logits: m16n8k16 over three 8-column tiles of the box per window row; the probabilities of columns
-//     (6+2t, 7+2t) and (14+2t, 15+2t), which the aggregation's B fragment wants, are held by lane (t+3)&3 of the
-//     same quad, so one quad rotation of the packed pairs re-aligns them.
+//     channels start in eight different 16-byte bank groups, so every ldmatrix is conflict-free;
+//   * query boxes are [8 high-res rows][channels][16 pixels] with 32-byte rows and the 32-byte swizzle;
+//   * a warp owns ONE high-res row (16 pixels = two groups of 8): warp = (low-res row, upper / lower high-res row);
+//   * logits are computed TRANSPOSED, S^T[16 box columns][8 pixels] = K^T[16 columns][16 ch] Q[16 ch][8 pixels]
+//     (m16n8k16; columns 0-15 for the left pixel group, 8-23 for the right one), so that the same 16 columns are
+//     the k dimension of the aggregation Out[16 ch][8 px] += V[16 ch][16 columns] P^T[16 columns][8 px]; the
+//     accumulator fragment of S^T becomes the B fragment of that product with one movmatrix (8x8 transpose) per
+//     packed register;
+//   * all fragments come from ldmatrix: K^T and Q with .trans, V without;
+//   * no CTA-wide barrier in the steady state: ring slots are handed back on "empty" mbarriers (one arrival per
+//     warp) and refilled by lane 0 of warp 0 whenever it finds one free; outputs go from registers to global memory.
 namespace h16 {
+constexpr int COLS = 8;                         // low-res columns of a CTA tile
+#ifndef SAPA_H16_NSTAGE
+#define SAPA_H16_NSTAGE 6                       // ring slots (a build-time tuning knob)
+#endif
+constexpr int NSTAGE = SAPA_H16_NSTAGE;
+constexpr int NW = 2 * ROWS;                    // 8 warps
+constexpr int NT = NW * 32;
+constexpr int CTAS_PER_SM = 2;                  // resident CTAs per SM the register budget is tuned for
+static_assert(KCH == 16 && VCH == 32, "one k step of m16n8k16 per key stage, two m blocks per value stage");
 constexpr int BC = 24;                          // key / value box columns
 constexpr int KROW = BC * 2;                    // 48 bytes
 constexpr int QROW = 32;                        // 16 high-res pixels
@@ -392,27 +417,38 @@ constexpr int K_BYTES = HH * KCH * KROW;        // 6144
 constexpr int Q_BYTES = 2 * ROWS * KCH * QROW;  // 4096
 constexpr int V_BYTES = HH * VCH * KROW;        // 12288
 constexpr int SLOT_BYTES = V_BYTES > K_BYTES + Q_BYTES ? V_BYTES : K_BYTES + Q_BYTES;
-constexpr int O_BYTES = 2 * ROWS * VCH * QROW;  // 8192
-static_assert(K_BYTES % 256 == 0 && SLOT_BYTES % 256 == 0 && O_BYTES % 256 == 0, "swizzled boxes need 256-byte alignment");
+constexpr int SMEM_BYTES = NSTAGE * SLOT_BYTES + 1024;
+static_assert(K_BYTES % 256 == 0 && SLOT_BYTES % 256 == 0, "the swizzled query box needs 256-byte alignment");
 }  // namespace h16
 
-__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], unsigned addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(unsigned (&r)[2], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
 __device__ __forceinline__ void ldsm_x2_trans(unsigned (&r)[2], unsigned addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// 8x8 transpose of a matrix of 16-bit elements held one row-pair per lane
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned v) {
+    unsigned r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(v));
+    return r;
+}
 template <typename T>
-__device__ __forceinline__ void mma_h16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+__device__ __forceinline__ void mma_h16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
     if constexpr (std::is_same<T, __half>::value)
         asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
     else
         asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ unsigned pack_pair(__half, float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
@@ -422,20 +458,22 @@ __device__ __forceinline__ unsigned pack_pair(__nv_bfloat16, float a, float b) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<const unsigned *>(&h);
 }
-__device__ __forceinline__ void sts32(unsigned addr, unsigned v) {
-    asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(addr), "r"(v) : "memory");
+__device__ __forceinline__ float ex2_ftz(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(NT, CTAS_PER_SM)
+__global__ void __launch_bounds__(h16::NT, h16::CTAS_PER_SM)
 sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-                         const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap, const Args a) {
+                         const __grid_constant__ CUtensorMap vmap, const Args a) {
     using namespace h16;
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) unsigned long long full_bar[NSTAGE];
+    __shared__ __align__(8) unsigned long long bars[2 * h16::NSTAGE];      // full[NSTAGE], empty[NSTAGE]
+    __shared__ int tile_ids[4];       // tile_ids[ti & 3] = tile of the ti-th tile of this CTA, -1 = no more tiles
     const unsigned ring_addr = ((unsigned)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
-    const unsigned bar_addr = (unsigned)__cvta_generic_to_shared(full_bar);
-    const unsigned obuf_addr = ring_addr + NSTAGE * h16::SLOT_BYTES;
+    const unsigned full_addr = (unsigned)__cvta_generic_to_shared(bars), empty_addr = full_addr + 8 * h16::NSTAGE;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wrow = warp >> 1, r = warp & 1;
@@ -444,186 +482,214 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
     const size_t hi_plane = (size_t)(2 * a.H) * sW;
     const int nk = (a.d + KCH - 1) / KCH, nv = (a.C + VCH - 1) / VCH, total = nk + nv;
     const int ntiles = a.B * a.tiles_x * a.tiles_y;
-    __shared__ int tile_ids[4];
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < NSTAGE; ++i) mbar_init(bar_addr + 8 * i, 1);
+        for (int i = 0; i < h16::NSTAGE; ++i) {
+            mbar_init(full_addr + 8 * i, 1);
+            mbar_init(empty_addr + 8 * i, NW);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
 
-    bool exhausted = false;
-    auto issue = [&](int gs) {     // thread 0 only; see the float32 kernel
-        if (exhausted) return;
-        const int ti = gs / total, it = gs - ti * total;
-        if (it == 0) {
-            int claimed = (int)blockIdx.x;
-            if (ti > 0) claimed = (int)(atomicAdd(&g_next_tile[a.sched_slot], 1u) + gridDim.x);
-            if (claimed >= ntiles) claimed = -1;
-            tile_ids[ti & 3] = claimed;
-            if (claimed < 0) { exhausted = true; return; }
-        }
-        int tile = tile_ids[ti & 3];
-        const int tbx = tile % a.tiles_x; tile /= a.tiles_x;
-        const int tby = tile % a.tiles_y; tile /= a.tiles_y;
-        const int tx0 = tbx * COLS, ty0 = tby * ROWS;
-        const unsigned slot = ring_addr + (gs % NSTAGE) * h16::SLOT_BYTES, bar = bar_addr + 8 * (gs % NSTAGE);
-        mbar_expect_tx(bar, it < nk ? h16::K_BYTES + Q_BYTES : h16::V_BYTES);
-        if (it < nk) {
-            tma_load_4d(slot, &kmap, bar, tx0 - 8, it * KCH, a.ytop0 + ty0 - 2, tile);
-            tma_load_4d(slot + h16::K_BYTES, &qmap, bar, 2 * tx0, it * KCH, 2 * ty0, tile);
-        } else {
-            tma_load_4d(slot, &vmap, bar, tx0 - 8, (it - nk) * VCH, a.ytop0 + ty0 - 2, tile);
+    // ---- producer state (lane 0 of warp 0).  The stages of successive tiles form one continuous stream through
+    // the ring; the first tile of a CTA is blockIdx.x, further tiles come from a global counter.
+    int p_issued = 0, p_slot = 0, p_phase = 0, p_it = 0, p_ti = 0, p_n = 0, p_x0 = 0, p_y0 = 0;
+    bool p_done = false;
+    // Issues every stage whose slot is free; when the stage `need` (the one the warp is about to wait for) has not
+    // been issued yet it waits for that slot.  A slot is free when all NW warps have released its previous use; on
+    // a fresh barrier the wait for the parity of the "previous" phase succeeds at once.
+    auto produce = [&](int need) {
+        while (!p_done) {
+            const unsigned ebar = empty_addr + 8 * p_slot;
+            if (!mbar_test_wait(ebar, p_phase ^ 1)) {
+                if (p_issued > need) return;
+                if (!mbar_wait_bounded(ebar, p_phase ^ 1)) {
+                    atomicExch(&g_wait_timeout, 1);
+                    p_done = true;
+                    return;
+                }
+            }
+            const unsigned bar = full_addr + 8 * p_slot;
+            if (p_it == 0) {
+                int claimed = (int)blockIdx.x;
+                if (p_ti > 0) claimed = (int)(atomicAdd(&g_next_tile[a.sched_slot], 1u) + gridDim.x);
+                if (claimed >= ntiles) claimed = -1;
+                tile_ids[p_ti & 3] = claimed;
+                if (claimed < 0) {
+                    mbar_arrive(bar);          // completes the phase without data: the warps read -1 and stop
+                    if (atomicAdd(&g_ctas_done[a.sched_slot], 1u) == gridDim.x - 1) {   // last CTA out: reset the scheduler slot
+                        g_next_tile[a.sched_slot] = 0u;
+                        g_ctas_done[a.sched_slot] = 0u;
+                    }
+                    p_done = true;
+                    return;
+                }
+                p_x0 = (claimed % a.tiles_x) * h16::COLS; claimed /= a.tiles_x;
+                p_y0 = (claimed % a.tiles_y) * ROWS; claimed /= a.tiles_y;
+                p_n = claimed;
+            }
+            const unsigned dst = ring_addr + p_slot * h16::SLOT_BYTES;
+            if (p_it < nk) {
+                mbar_expect_tx(bar, h16::K_BYTES + Q_BYTES);
+                tma_load_4d(dst, &kmap, bar, p_x0 - 8, p_it * KCH, a.ytop0 + p_y0 - 2, p_n);
+                tma_load_4d(dst + h16::K_BYTES, &qmap, bar, 2 * p_x0, p_it * KCH, 2 * p_y0, p_n);
+            } else {
+                mbar_expect_tx(bar, h16::V_BYTES);
+                tma_load_4d(dst, &vmap, bar, p_x0 - 8, (p_it - nk) * VCH, a.ytop0 + p_y0 - 2, p_n);
+            }
+            ++p_issued;
+            if (++p_it == total) { p_it = 0; ++p_ti; }
+            if (++p_slot == h16::NSTAGE) { p_slot = 0; p_phase ^= 1; }
         }
     };
-    if (tid == 0) {
+
+    // ---- per-lane constants
+    // ldmatrix row addresses.  "A-type" lane order: matrices (rows 0-7 | 8-15) x (chunk 0 | 1) as m0..m3 =
+    // (lo,0) (hi,0) (lo,1) (hi,1); "T-type": (lo,0) (lo,1) (hi,0) (hi,1).
+    const int row_a = (lane & 7) + 8 * ((lane >> 3) & 1), chunk_a = lane >> 4;
+    const int row_t = (lane & 7) + 8 * (lane >> 4), chunk_t = (lane >> 3) & 1;
+    // query (B of the logits): m0..m3 = (ch 0-7, px 0-7) (ch 8-15, px 0-7) (ch 0-7, px 8-15) (ch 8-15, px 8-15)
+    const int q_off = h16::K_BYTES + (2 * wrow + r) * (KCH * QROW) + row_a * QROW + (((chunk_a ^ (row_a >> 2)) & 1) << 4);
+    // key (A of the logits, transposed): m0..m3 = (ch 0-7, col 0-7) (ch 0-7, col 8-15) (ch 8-15, col 0-7) (ch 8-15, col 8-15),
+    // then m4, m5 = (ch 0-7, col 16-23) (ch 8-15, col 16-23).  The right pixel group's fragment is assembled from
+    // m1, m4, m3, m5: loading the shared middle columns a second time instead was measured slower (the kernel is
+    // short of shared-memory bandwidth, not of issue slots).
+    const int k_off = wrow * (KCH * KROW) + row_t * KROW + chunk_t * 16;
+    const int k_off2 = wrow * (KCH * KROW) + row_a * KROW + 32;
+    // value (A of the aggregation): m0..m3 = (ch 0-7, col 0-7) (ch 8-15, col 0-7) (ch 0-7, col 8-15) (ch 8-15, col 8-15),
+    // then m4, m5 = (ch 0-7, col 16-23) (ch 8-15, col 16-23)
+    const int v_off = wrow * (VCH * KROW) + row_a * KROW + chunk_a * 16;
+    const int v_off2 = wrow * (VCH * KROW) + row_a * KROW + 32;
+    // Lane (g,t) of pixel group p (pixels 8p .. 8p+7 of the row) holds, for the pixels 8p+2t and 8p+2t+1 (parent
+    // column l = 4p + t, window = box columns l+6 .. l+10), the box columns 8p+g ("lo") and 8p+g+8 ("hi").
+    bool ok_lo[2], ok_hi[2];
+    int dx_lo[2];                 // window column of the lo cell (hi = lo + 8)
 #pragma unroll
-        for (int i = 0; i < NSTAGE - 1; ++i) issue(i);
+    for (int p = 0; p < 2; ++p) {
+        dx_lo[p] = 4 * p + g - t - 6;
+        ok_lo[p] = dx_lo[p] >= 0 && dx_lo[p] <= 4;
+        ok_hi[p] = dx_lo[p] + 8 >= 0 && dx_lo[p] + 8 <= 4;
     }
 
-    // Lane (g,t) holds, for the pixels g and g+8 of its row, the box columns 8*tile + 2t, +1 (tile = 0..2).  The
-    // parent of pixel px is l = px/2 and its window covers box columns l+6 .. l+10.
-    bool ok[2][3][2];
-#pragma unroll
-    for (int p = 0; p < 2; ++p)
-#pragma unroll
-        for (int c = 0; c < 3; ++c)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int col = 8 * c + 2 * t + i, l = (g >> 1) + 4 * p;
-                ok[p][c][i] = (col >= l + 6) && (col <= l + 10);
-            }
-
-    // ldmatrix row addresses: query matrices (ch 0-7 | 8-15) x (px 0-7 | 8-15), key matrices (ch 0-7 | 8-15) x 8 columns
-    const int qch = (lane & 7) + 8 * (lane >> 4);
-    const int q_off = h16::K_BYTES + (2 * wrow + r) * (KCH * QROW) + qch * QROW + (((((lane >> 3) & 1) ^ (qch >> 2)) & 1) << 4);
-    const int kch = (lane & 7) + 8 * ((lane >> 3) & 1);
-    const int k_off = wrow * (KCH * KROW) + kch * KROW + (lane >> 4) * 16;
-    const int k_off2 = wrow * (KCH * KROW) + kch * KROW + 32;
-    // value A fragment: channel g (and g+8), box columns 6+2t, 7+2t (and +8)
-    const int v_off = wrow * (VCH * KROW) + g * KROW + (6 + 2 * t) * 2;
-    // output D fragment: channel g (and g+8), pixels 8p + 2t, +1
-    const int o_off = (2 * wrow + r) * (VCH * QROW) + g * QROW + 4 * t;
-    const int o_sw = (g >> 2) & 1;
-
-    float s[2][5][3][2];          // logits, then probabilities: [pixel g | g+8][dy][column tile][column 2t | 2t+1]
+    float s[2][5][4];             // logits, then probabilities: [group][dy][(lo,px0) (lo,px1) (hi,px0) (hi,px1)]
     unsigned pb[2][5][2];         // B fragments of the aggregation
 
-    int gs = 0;
-    for (int ti = 0;; ++ti) {
-    int tile = ti == 0 ? (int)blockIdx.x : tile_ids[ti & 3];
-    if (tile < 0) break;
-    const int bx = tile % a.tiles_x; tile /= a.tiles_x;
-    const int by = tile % a.tiles_y; tile /= a.tiles_y;
-    const int n = tile;
-    const int x0 = bx * COLS, y0 = by * ROWS;
-    const int y = y0 + wrow;
-#pragma unroll
-    for (int p = 0; p < 2; ++p)
-#pragma unroll
-        for (int dy = 0; dy < 5; ++dy)
-#pragma unroll
-            for (int c = 0; c < 3; ++c) s[p][dy][c][0] = s[p][dy][c][1] = 0.f;
-
-    for (int it = 0; it < total; ++it, ++gs) {
-        __syncthreads();
-        if (tid == 0) {
-            if (it > nk) {
-                tma_store_4d(&omap, obuf_addr + ((it - nk - 1) & 1) * h16::O_BYTES, 2 * x0, (it - nk - 1) * VCH, 2 * y0, n);
-                asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
-            }
-            issue(gs + NSTAGE - 1);
+    int slot = 0, phase = 0, it = 0, ti = 0, gs = 0;
+    int n = 0, x0 = 0, y = 0;
+    // kernel-wide strides in 32-bit words of the 16-bit output / attention tensors (two elements per word)
+    const size_t plane_w = hi_plane >> 1;
+    const int C = a.C, Wlo = a.W, Hlo = a.H;
+    unsigned *o_ptr = nullptr;            // this lane's output word for the first channel of the current value stage
+    bool row_ok = false, col_ok0 = false, col_ok1 = false;
+    constexpr float LOG2E = 1.4426950408889634f;
+    for (;; ++gs) {
+        if (warp == 0) {
+            if (lane == 0) produce(gs);
+            __syncwarp();
         }
-        if (!mbar_wait_bounded(bar_addr + 8 * (gs % NSTAGE), (gs / NSTAGE) & 1)) {
+        if (!mbar_wait_bounded(full_addr + 8 * slot, phase)) {
             atomicExch(&g_wait_timeout, 1);
             return;
         }
-        const unsigned stage = ring_addr + (gs % NSTAGE) * h16::SLOT_BYTES;
+        if (it == 0) {
+            int tile = tile_ids[ti & 3];      // published by the producer before the barrier's phase completed
+            if (tile < 0) break;
+            x0 = (tile % a.tiles_x) * h16::COLS; tile /= a.tiles_x;
+            y = (tile % a.tiles_y) * ROWS + wrow; tile /= a.tiles_y;
+            n = tile;
+            row_ok = y < Hlo; col_ok0 = x0 + t < Wlo; col_ok1 = x0 + 4 + t < Wlo;
+            o_ptr = reinterpret_cast<unsigned *>(static_cast<T *>(a.out) + ((size_t)n * C + g) * hi_plane +
+                                                 (size_t)(2 * y + r) * sW + 2 * x0 + 2 * t);
+#pragma unroll
+            for (int p = 0; p < 2; ++p)
+#pragma unroll
+                for (int dy = 0; dy < 5; ++dy)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s[p][dy][i] = 0.f;
+        }
+        const unsigned stage = ring_addr + slot * h16::SLOT_BYTES;
 
         if (it < nk) {
-            // ------------------------------------------------------------- logits: S[16 px][24 cols] += Qt[16 px][16 ch] K[16 ch][24 cols]
-            unsigned qa[4];
-            ldsm_x4_trans(qa, stage + q_off);
+            // ------------------------------------------------------------- logits
+            unsigned qb[4];
+            ldsm_x4_trans(qb, stage + q_off);
+            const unsigned ka_addr = stage + k_off, kc_addr = stage + k_off2;
 #pragma unroll
             for (int dy = 0; dy < 5; ++dy) {
-                unsigned kb[4], kc[2];
-                ldsm_x4_trans(kb, stage + k_off + dy * (KCH * KROW));
-                ldsm_x2_trans(kc, stage + k_off2 + dy * (KCH * KROW));
-                float d0[4] = {s[0][dy][0][0], s[0][dy][0][1], s[1][dy][0][0], s[1][dy][0][1]};
-                float d1[4] = {s[0][dy][1][0], s[0][dy][1][1], s[1][dy][1][0], s[1][dy][1][1]};
-                float d2[4] = {s[0][dy][2][0], s[0][dy][2][1], s[1][dy][2][0], s[1][dy][2][1]};
-                mma_h16<T>(d0, qa, kb[0], kb[1]);
-                mma_h16<T>(d1, qa, kb[2], kb[3]);
-                mma_h16<T>(d2, qa, kc[0], kc[1]);
-                s[0][dy][0][0] = d0[0]; s[0][dy][0][1] = d0[1]; s[1][dy][0][0] = d0[2]; s[1][dy][0][1] = d0[3];
-                s[0][dy][1][0] = d1[0]; s[0][dy][1][1] = d1[1]; s[1][dy][1][0] = d1[2]; s[1][dy][1][1] = d1[3];
-                s[0][dy][2][0] = d2[0]; s[0][dy][2][1] = d2[1]; s[1][dy][2][0] = d2[2]; s[1][dy][2][1] = d2[3];
+                unsigned ka[4], kc[2];
+                ldsm_x4_trans(ka, ka_addr + dy * (KCH * KROW));
+                ldsm_x2_trans(kc, kc_addr + dy * (KCH * KROW));
+                mma_h16<T>(s[0][dy], ka[0], ka[1], ka[2], ka[3], qb[0], qb[1]);
+                mma_h16<T>(s[1][dy], ka[1], kc[0], ka[3], kc[1], qb[2], qb[3]);
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_addr + 8 * slot);
             if (it == nk - 1) {
+                // softmax over the 25 window slots of each pixel: 5 rows here x the lanes with the same t.
+                // exp(x - m) = 2^(x * log2(e) - m * log2(e)): one FMA and one ex2 per element.
 #pragma unroll
                 for (int p = 0; p < 2; ++p) {
-                    float m = -INFINITY;
+                    float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
-                    for (int dy = 0; dy < 5; ++dy)
+                    for (int dy = 0; dy < 5; ++dy) {
+                        if (ok_lo[p]) { m0 = fmaxf(m0, s[p][dy][0]); m1 = fmaxf(m1, s[p][dy][1]); }
+                        if (ok_hi[p]) { m0 = fmaxf(m0, s[p][dy][2]); m1 = fmaxf(m1, s[p][dy][3]); }
+                    }
 #pragma unroll
-                        for (int c = 0; c < 3; ++c)
+                    for (int sh = 4; sh < 32; sh <<= 1) {
+                        m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, sh));
+                        m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, sh));
+                    }
+                    m0 *= LOG2E; m1 *= LOG2E;
+                    float z0 = 0.f, z1 = 0.f;
 #pragma unroll
-                            for (int i = 0; i < 2; ++i)
-                                if (ok[p][c][i]) m = fmaxf(m, s[p][dy][c][i]);
-                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-                    float z = 0.f;
+                    for (int dy = 0; dy < 5; ++dy) {
+                        s[p][dy][0] = ok_lo[p] ? ex2_ftz(fmaf(s[p][dy][0], LOG2E, -m0)) : 0.f;
+                        s[p][dy][1] = ok_lo[p] ? ex2_ftz(fmaf(s[p][dy][1], LOG2E, -m1)) : 0.f;
+                        s[p][dy][2] = ok_hi[p] ? ex2_ftz(fmaf(s[p][dy][2], LOG2E, -m0)) : 0.f;
+                        s[p][dy][3] = ok_hi[p] ? ex2_ftz(fmaf(s[p][dy][3], LOG2E, -m1)) : 0.f;
+                        z0 += s[p][dy][0] + s[p][dy][2];
+                        z1 += s[p][dy][1] + s[p][dy][3];
+                    }
 #pragma unroll
-                    for (int dy = 0; dy < 5; ++dy)
+                    for (int sh = 4; sh < 32; sh <<= 1) {
+                        z0 += __shfl_xor_sync(0xffffffffu, z0, sh);
+                        z1 += __shfl_xor_sync(0xffffffffu, z1, sh);
+                    }
+                    const float i0 = __frcp_rn(z0), i1 = __frcp_rn(z1);
 #pragma unroll
-                        for (int c = 0; c < 3; ++c)
-#pragma unroll
-                            for (int i = 0; i < 2; ++i) {
-                                s[p][dy][c][i] = ok[p][c][i] ? expf(s[p][dy][c][i] - m) : 0.f;
-                                z += s[p][dy][c][i];
-                            }
-                    z += __shfl_xor_sync(0xffffffffu, z, 1);
-                    z += __shfl_xor_sync(0xffffffffu, z, 2);
-                    const float inv = 1.f / z;
-#pragma unroll
-                    for (int dy = 0; dy < 5; ++dy)
-#pragma unroll
-                        for (int c = 0; c < 3; ++c) { s[p][dy][c][0] *= inv; s[p][dy][c][1] *= inv; }
-                }
-                if (a.attn != nullptr && y < a.H) {
-                    T *an = static_cast<T *>(a.attn) + (size_t)n * 25 * hi_plane + (size_t)(2 * y + r) * sW + 2 * x0 + g;
-#pragma unroll
-                    for (int p = 0; p < 2; ++p) {
-                        const int l = (g >> 1) + 4 * p;
-                        if (x0 + l < a.W) {
-#pragma unroll
-                            for (int dy = 0; dy < 5; ++dy)
-#pragma unroll
-                                for (int c = 0; c < 3; ++c)
-#pragma unroll
-                                    for (int i = 0; i < 2; ++i)
-                                        if (ok[p][c][i])
-                                            an[(size_t)(dy * 5 + 8 * c + 2 * t + i - 6 - l) * hi_plane + 8 * p] = from_acc<T>(s[p][dy][c][i]);
-                        }
+                    for (int dy = 0; dy < 5; ++dy) {
+                        pb[p][dy][0] = pack_pair(T(), s[p][dy][0] * i0, s[p][dy][1] * i1);
+                        pb[p][dy][1] = pack_pair(T(), s[p][dy][2] * i0, s[p][dy][3] * i1);
                     }
                 }
-                // quad rotation: lane t takes the packed pairs of lane (t+3)&3; columns 6+2t.. are that lane's tile
-                // (t+3)>>2 and columns 14+2t.. its tile (t+7)>>2
-                const int src = (lane & ~3) | ((t + 3) & 3);
+                if (a.attn != nullptr && row_ok) {
+                    // the two pixels of a pair are neighbours in memory: one 32-bit store per (window slot, pair)
+                    unsigned *an = reinterpret_cast<unsigned *>(static_cast<T *>(a.attn) + (size_t)n * 25 * hi_plane +
+                                                                (size_t)(2 * y + r) * sW + 2 * x0 + 2 * t);
+#pragma unroll
+                    for (int p = 0; p < 2; ++p)
+                        if (p == 0 ? col_ok0 : col_ok1) {
+#pragma unroll
+                            for (int dy = 0; dy < 5; ++dy) {
+                                if (ok_lo[p]) an[(size_t)(dy * 5 + dx_lo[p]) * plane_w + 4 * p] = pb[p][dy][0];
+                                if (ok_hi[p]) an[(size_t)(dy * 5 + dx_lo[p] + 8) * plane_w + 4 * p] = pb[p][dy][1];
+                            }
+                        }
+                }
+                // S^T accumulator fragments -> B fragments of the aggregation
 #pragma unroll
                 for (int p = 0; p < 2; ++p)
 #pragma unroll
                     for (int dy = 0; dy < 5; ++dy) {
-                        const unsigned v0 = __shfl_sync(0xffffffffu, pack_pair(T(), s[p][dy][0][0], s[p][dy][0][1]), src);
-                        const unsigned v1 = __shfl_sync(0xffffffffu, pack_pair(T(), s[p][dy][1][0], s[p][dy][1][1]), src);
-                        const unsigned v2 = __shfl_sync(0xffffffffu, pack_pair(T(), s[p][dy][2][0], s[p][dy][2][1]), src);
-                        pb[p][dy][0] = t == 0 ? v0 : v1;
-                        pb[p][dy][1] = t == 0 ? v1 : v2;
+                        pb[p][dy][0] = movmatrix_trans(pb[p][dy][0]);
+                        pb[p][dy][1] = movmatrix_trans(pb[p][dy][1]);
                     }
             }
         } else {
-            // ------------------------------------------------------------- aggregation: Out[16 ch][8 px] += V[16 ch][16 cols] P[16 cols][8 px]
+            // ------------------------------------------------------------- aggregation
             float acc[VCH / 16][2][4];
 #pragma unroll
             for (int b = 0; b < VCH / 16; ++b)
@@ -631,41 +697,46 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
                 for (int p = 0; p < 2; ++p)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[b][p][i] = 0.f;
+            const unsigned va_addr = stage + v_off, vc_addr = stage + v_off2;
 #pragma unroll
             for (int dy = 0; dy < 5; ++dy)
 #pragma unroll
                 for (int b = 0; b < VCH / 16; ++b) {
-                    const unsigned vp = stage + v_off + dy * (VCH * KROW) + b * 16 * KROW;
-                    const unsigned av[4] = {lds32(vp), lds32(vp + 8 * KROW), lds32(vp + 16), lds32(vp + 8 * KROW + 16)};
-#pragma unroll
-                    for (int p = 0; p < 2; ++p) mma_h16<T>(acc[b][p], av, pb[p][dy][0], pb[p][dy][1]);
+                    unsigned va[4], vc[2];
+                    ldsm_x4(va, va_addr + dy * (VCH * KROW) + b * 16 * KROW);
+                    ldsm_x2(vc, vc_addr + dy * (VCH * KROW) + b * 16 * KROW);
+                    mma_h16<T>(acc[b][0], va[0], va[1], va[2], va[3], pb[0][dy][0], pb[0][dy][1]);
+                    mma_h16<T>(acc[b][1], va[2], va[3], vc[0], vc[1], pb[1][dy][0], pb[1][dy][1]);
                 }
-            const unsigned ob = obuf_addr + ((it - nk) & 1) * h16::O_BYTES + o_off;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_addr + 8 * slot);
+            // D fragment of group p: d0,d1 = Out[ch g][px 8p+2t, +1], d2,d3 = Out[ch g+8][same]; the 4 lanes of a quad
+            // write 16 consecutive bytes, the two groups the two halves of a 32-byte sector
+            const int c0 = (it - nk) * VCH;
+            unsigned *o = o_ptr;
+            o_ptr += (size_t)VCH * plane_w;
+            if (row_ok) {
+                if (c0 + VCH <= C && col_ok1) {        // whole block inside the tensor (col_ok1 implies col_ok0)
 #pragma unroll
-            for (int b = 0; b < VCH / 16; ++b)
+                    for (int j = 0; j < VCH / 8; ++j) {       // channel g + 8j: block j/2, half j%2
+                        __stcs(o, pack_pair(T(), acc[j >> 1][0][2 * (j & 1)], acc[j >> 1][0][2 * (j & 1) + 1]));
+                        __stcs(o + 4, pack_pair(T(), acc[j >> 1][1][2 * (j & 1)], acc[j >> 1][1][2 * (j & 1) + 1]));
+                        o += 8 * plane_w;
+                    }
+                } else {
 #pragma unroll
-                for (int half = 0; half < 2; ++half)
-#pragma unroll
-                    for (int p = 0; p < 2; ++p)
-                        sts32(ob + (16 * b + 8 * half) * QROW + ((p ^ o_sw) << 4),
-                              pack_pair(T(), acc[b][p][2 * half], acc[b][p][2 * half + 1]));
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+                    for (int j = 0; j < VCH / 8; ++j) {
+                        if (c0 + 8 * j + g < C) {
+                            if (col_ok0) __stcs(o, pack_pair(T(), acc[j >> 1][0][2 * (j & 1)], acc[j >> 1][0][2 * (j & 1) + 1]));
+                            if (col_ok1) __stcs(o + 4, pack_pair(T(), acc[j >> 1][1][2 * (j & 1)], acc[j >> 1][1][2 * (j & 1) + 1]));
+                        }
+                        o += 8 * plane_w;
+                    }
+                }
+            }
         }
-    }
-    __syncthreads();
-    if (tid == 0) {
-        tma_store_4d(&omap, obuf_addr + ((nv - 1) & 1) * h16::O_BYTES, 2 * x0, (nv - 1) * VCH, 2 * y0, n);
-        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
-        asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
-    }
-    }
-    if (tid == 0) {
-        asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
-        if (atomicAdd(&g_ctas_done[a.sched_slot], 1u) == gridDim.x - 1) {
-            g_next_tile[a.sched_slot] = 0u;
-            g_ctas_done[a.sched_slot] = 0u;
-        }
+        if (++slot == h16::NSTAGE) { slot = 0; phase ^= 1; }
+        if (++it == total) { it = 0; ++ti; }
     }
 }
 
@@ -702,9 +773,9 @@ static bool make_map(CUtensorMap *map, const void *base, int width, int height, 
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename Kernel>
-static int launch_persistent(Kernel kernel, const char *name, int smem, const CUtensorMap &qmap, const CUtensorMap &kmap,
-                             const CUtensorMap &vmap, const CUtensorMap &omap, Args &a, cudaStream_t st) {
+// Opts in to the dynamic shared memory, sizes the persistent grid, picks a scheduler slot and launches.
+template <typename Kernel, typename... Maps>
+static int launch_persistent(Kernel kernel, const char *name, int threads, int smem, Args &a, cudaStream_t st, const Maps &...maps) {
     const long long nblocks = (long long)a.B * a.tiles_x * a.tiles_y;
     if (nblocks > 0x7fffffffLL) {
         set_error("too many tiles");
@@ -725,7 +796,7 @@ static int launch_persistent(Kernel kernel, const char *name, int smem, const CU
     const unsigned grid = (unsigned)(nblocks < resident ? nblocks : resident);
     static std::atomic<unsigned> next_slot{0};
     a.sched_slot = (int)(next_slot.fetch_add(1u) % SCHED_SLOTS);
-    kernel<<<grid, NT, smem, st>>>(qmap, kmap, vmap, omap, a);
+    kernel<<<grid, threads, smem, st>>>(maps..., a);
     return check_launch(name);
 }
 
@@ -752,9 +823,9 @@ int launch_fused_tma(const void *q, const void *k, const void *v, void *out, voi
              make_map(&vmap, v, W, rows, C, B, VCH, ty, 4, HC, sw) && make_map(&omap, out, 2 * W, 2 * H, C, B, VCH, ty, 4, HC, sw);
     } else {
         const auto ty = dtype == SAPA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-        const auto none = CU_TENSOR_MAP_SWIZZLE_NONE, sw = CU_TENSOR_MAP_SWIZZLE_32B;
-        ok = make_map(&qmap, q, 2 * W, 2 * H, d, B, KCH, ty, 2, 16, sw) && make_map(&kmap, k, W, rows, d, B, KCH, ty, 2, h16::BC, none) &&
-             make_map(&vmap, v, W, rows, C, B, VCH, ty, 2, h16::BC, none) && make_map(&omap, out, 2 * W, 2 * H, C, B, VCH, ty, 2, 16, sw);
+        ok = make_map(&qmap, q, 2 * W, 2 * H, d, B, KCH, ty, 2, 16, CU_TENSOR_MAP_SWIZZLE_32B) &&
+             make_map(&kmap, k, W, rows, d, B, KCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+             make_map(&vmap, v, W, rows, C, B, VCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (!ok) {
         set_error("sapa_tma_fused: cuTensorMapEncodeTiled rejected the tensor layout");
@@ -763,15 +834,15 @@ int launch_fused_tma(const void *q, const void *k, const void *v, void *out, voi
     Args a{};
     a.out = out; a.attn = attn;
     a.B = B; a.d = d; a.C = C; a.H = H; a.W = W; a.rows = rows; a.ytop0 = ytop0;
+    static_assert(h16::COLS == COLS && h16::CTAS_PER_SM == CTAS_PER_SM, "both kernels use the same tile and residency");
     a.tiles_x = ceil_div(W, COLS);
     a.tiles_y = ceil_div(H, ROWS);
     constexpr int smem32 = NSTAGE * SLOT_BYTES + 2 * O_BYTES + 1024;
-    constexpr int smem16 = NSTAGE * h16::SLOT_BYTES + 2 * h16::O_BYTES + 1024;
     if (dtype == SAPA_F32)
-        return launch_persistent(sapa_tma_fused_f32_kernel, "sapa_tma_fused_f32_kernel", smem32, qmap, kmap, vmap, omap, a, st);
+        return launch_persistent(sapa_tma_fused_f32_kernel, "sapa_tma_fused_f32_kernel", NT, smem32, a, st, qmap, kmap, vmap, omap);
     if (dtype == SAPA_F16)
-        return launch_persistent(sapa_tma_fused_16_kernel<__half>, "sapa_tma_fused_16_kernel", smem16, qmap, kmap, vmap, omap, a, st);
-    return launch_persistent(sapa_tma_fused_16_kernel<__nv_bfloat16>, "sapa_tma_fused_16_kernel", smem16, qmap, kmap, vmap, omap, a, st);
+        return launch_persistent(sapa_tma_fused_16_kernel<__half>, "sapa_tma_fused_16_kernel", h16::NT, h16::SMEM_BYTES, a, st, qmap, kmap, vmap);
+    return launch_persistent(sapa_tma_fused_16_kernel<__nv_bfloat16>, "sapa_tma_fused_16_kernel", h16::NT, h16::SMEM_BYTES, a, st, qmap, kmap, vmap);
 }
 
 // 1 if a bounded mbarrier wait of the TMA kernel ever gave up on the current device (synchronises the device).
