@@ -322,6 +322,92 @@ def main():
     ms_per_step = elapsed_ms / args.steps
     value = pix_per_step / (ms_per_step * 1e-3) / 1e6
 
+    # ---- the same kernel-only measurement for the other element types of config 2 (not the headline; N = 1 only) ----
+    other = {}
+    if world == 1 and not args.no_extra and args.workload == "cfg2":
+        for name in [n for n in DTYPES if n != args.dtype]:
+            odt = DTYPES[name]
+            osize = torch.empty((), dtype=odt).element_size()
+            obytes = algorithmic_bytes(wl, osize)
+            on = max(2, min(8, -(-3 * L2_BYTES // obytes) + 1))
+            osets = []
+            for i in range(on):
+                t = make_inputs(wl, odt, device, seed=500 + i)
+                t["out"] = torch.empty((wl["B"], wl["C"], s * wl["H"], s * wl["W"]), dtype=odt, device=device)
+                osets.append(t)
+            code = sapa_b200._lib.dtype_code(osets[0]["q"])
+
+            def ostep(i):
+                t = osets[i % on]
+                sapa_b200._lib.call("sapa_fused_forward", device, t["q"], t["k"], t["v"], t["out"], None, wl["B"], wl["d"],
+                                    wl["C"], wl["H"], wl["W"], K, s, code)
+            osteps = max(3, min(args.steps, 300))
+            for i in range(max(3, min(args.warmup, 20))):
+                ostep(i)
+            torch.cuda.synchronize()
+            o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            o0.record()
+            for i in range(osteps):
+                ostep(i)
+            o1.record()
+            torch.cuda.synchronize()
+            oms = o0.elapsed_time(o1) / osteps
+            other[name] = {"value": pix_per_step_rank / (oms * 1e-3) / 1e6, "unit": "Mpix/s", "ms_per_step": oms, "steps": osteps,
+                           "roofline_frac": obytes / (oms * 1e-3) / 1e9 / measured_peak()[0],
+                           "algorithmic_bytes_per_launch": obytes}
+            del osets
+
+    # ---- the rest of the path at the same shapes: SAPA-B fused backward and SAPA-D fused forward (kernel time only) ----
+    paths = {}
+    if world == 1 and not args.no_extra and args.workload == "cfg2":
+        peak_gbs = measured_peak()[0]
+
+        def time_path(fn, steps):
+            for _ in range(5):
+                fn()
+            torch.cuda.synchronize()
+            flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)   # L2 flushed between iterations
+            times = []
+            for _ in range(steps):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+            times.sort()
+            return times[len(times) // 2]
+
+        t = make_inputs(wl, dtype, device, seed=900)
+        B_, d_, C_, H_, W_ = wl["B"], wl["d"], wl["C"], wl["H"], wl["W"]
+        hi = s * H_ * s * W_
+        g_out = torch.randn(B_, C_, s * H_, s * W_, device=device).to(dtype)
+        out_b, attn_b = fused_forward_raw(t["q"], t["k"], t["v"], K, s, True)
+        code = sapa_b200._lib.dtype_code(t["q"])
+        gq, gk, gv = torch.empty_like(t["q"]), torch.empty_like(t["k"]), torch.empty_like(t["v"])
+        nb = sapa_b200._lib.fused_backward_workspace(B_, H_, W_, K, s, code)
+        ws = torch.empty(nb, dtype=torch.uint8, device=device)
+        ms_b = time_path(lambda: sapa_b200._lib.call("sapa_fused_backward", device, g_out, t["q"], t["k"], t["v"], attn_b, gq, gk, gv,
+                                                     ws, nb, B_, d_, C_, H_, W_, K, s, code), 20)
+        # reads dOut, V, Q, K and the saved attention map; writes dV, dQ, dK
+        bytes_b = (B_ * C_ * hi + B_ * C_ * H_ * W_ + B_ * d_ * hi + B_ * d_ * H_ * W_ + B_ * K * K * hi
+                   + B_ * C_ * H_ * W_ + B_ * d_ * hi + B_ * d_ * H_ * W_) * esize
+        paths["sapa_b_fused_backward"] = {"ms": ms_b, "launches": 3, "algorithmic_bytes": bytes_b,
+                                          "achieved_gbs": bytes_b / (ms_b * 1e-3) / 1e9, "roofline_frac": bytes_b / (ms_b * 1e-3) / 1e9 / peak_gbs,
+                                          "mpix_per_s": pix_per_step_rank / (ms_b * 1e-3) / 1e6}
+        del out_b, gq, gk, gv, ws
+        # SAPA-D, config 3: 4 groups, 9 points, offsets ~ N(0, 0.5^2), q/k channels = d in total
+        G_, P_ = 4, 9
+        off = (torch.randn(B_, G_ * P_ * 2, s * H_, s * W_, device=device) * 0.5).to(dtype)
+        ms_d = time_path(lambda: sapa_b200.deform_sapa_fused(t["q"], t["k"], t["v"], off, P_, s, G_), 10)
+        bytes_d = (B_ * d_ * hi + B_ * d_ * H_ * W_ + 2 * B_ * G_ * P_ * hi + B_ * C_ * H_ * W_ + B_ * C_ * hi) * esize
+        paths["sapa_d_fused_forward"] = {"ms": ms_d, "launches": 1, "algorithmic_bytes": bytes_d,
+                                         "achieved_gbs": bytes_d / (ms_d * 1e-3) / 1e9, "roofline_frac": bytes_d / (ms_d * 1e-3) / 1e9 / peak_gbs,
+                                         "mpix_per_s": pix_per_step_rank / (ms_d * 1e-3) / 1e6,
+                                         "config": {"groups": G_, "points": P_, "offset_sigma": 0.5}}
+        del t, off, g_out, attn_b
+
     # ---- end to end: public op, pinned host buffers in and out, copies inside the timed region ----
     e2e_steps = max(3, min(args.steps, 30))
     host_in = [make_inputs(wl, dtype, device, seed=7 + i, pinned=True) for i in range(2)]
@@ -392,6 +478,9 @@ def main():
                          "algorithmic_bytes_per_launch": bytes_per_launch,
                          "frac_of_8000_nominal": achieved / 8000.0},
         }
+        if world == 1 and not args.no_extra and args.workload == "cfg2":
+            line["other_dtypes"] = other
+            line["other_paths"] = paths
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(line), flush=True)

@@ -30,17 +30,27 @@ namespace tma {
 constexpr int ROWS = 4, COLS = 8;          // low-res tile of a CTA
 constexpr int HH = ROWS + 4;               // halo rows
 constexpr int HC = 16;                     // halo columns x0-4 .. x0+11 = one 64-byte row
-constexpr int KCH = 16;                    // key / query channels per stage
-constexpr int VCH = 32;                    // value channels per stage
+// float32 kernel: channels per stage and resident CTAs per SM are build-time tuning knobs
+#ifndef SAPA_F32_KCH
+#define SAPA_F32_KCH 16
+#endif
+#ifndef SAPA_F32_VCH
+#define SAPA_F32_VCH 32
+#endif
+#ifndef SAPA_F32_CTAS
+#define SAPA_F32_CTAS 2
+#endif
+constexpr int F_KCH = SAPA_F32_KCH;        // key / query channels per stage (multiple of 8)
+constexpr int F_VCH = SAPA_F32_VCH;        // value channels per stage (multiple of 16)
 constexpr int NSTAGE = 4;
 constexpr int NT = 2 * ROWS * 32;          // 8 warps: (row, 4-pixel half)
 constexpr int ROWB = HC * 4;               // 64 bytes
-constexpr int K_BYTES = HH * KCH * ROWB;   // 8192: key box [8 rows][16 ch][16 cols]
-constexpr int V_BYTES = HH * VCH * ROWB;   // 16384
+constexpr int K_BYTES = HH * F_KCH * ROWB;   // 8192: key box [8 rows][16 ch][16 cols]
+constexpr int V_BYTES = HH * F_VCH * ROWB;   // 16384
 constexpr int SLOT_BYTES = V_BYTES > 2 * K_BYTES ? V_BYTES : 2 * K_BYTES;
-constexpr int O_BYTES = 2 * ROWS * VCH * ROWB;   // 16384: output box [8 hi rows][32 ch][16 hi cols], double-buffered        // = K_BYTES + the query box [8 hi rows][16 ch][16 hi cols] of 8192 bytes
+constexpr int O_BYTES = 2 * ROWS * F_VCH * ROWB;   // 16384: output box [8 hi rows][32 ch][16 hi cols], double-buffered        // = K_BYTES + the query box [8 hi rows][16 ch][16 hi cols] of 8192 bytes
 constexpr unsigned TF32_MASK = 0xffffe000u;
-constexpr int CTAS_PER_SM = 2;             // resident CTAs per SM the register budget is tuned for
+constexpr int CTAS_PER_SM = SAPA_F32_CTAS;  // resident CTAs per SM the register budget is tuned for
 constexpr int WAIT_LIMIT = 1 << 22;        // bounded mbarrier wait (each try suspends for a while in hardware)
 
 __device__ int g_wait_timeout = 0;         // set when a bounded wait gave up (read by tma_wait_timeout_flag)
@@ -127,7 +137,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     const int g = lane >> 2, t = lane & 3;
     const int sW = 2 * a.W;
     const size_t hi_plane = (size_t)(2 * a.H) * sW;
-    const int nk = (a.d + KCH - 1) / KCH, nv = (a.C + VCH - 1) / VCH, total = nk + nv;
+    const int nk = (a.d + F_KCH - 1) / F_KCH, nv = (a.C + F_VCH - 1) / F_VCH, total = nk + nv;
     // Persistent CTA: its first tile is blockIdx.x, further tiles come from a global counter.  The stages of
     // successive tiles form one continuous stream through the ring, so the first stages of the next tile are in
     // flight while the current tile finishes.  tile_ids[ti & 3] = tile of the ti-th tile of this CTA, -1 = none.
@@ -143,30 +153,34 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     }
     __syncthreads();
 
-    // stage gs of this CTA's stream goes to slot gs % NSTAGE; executed by thread 0 only
+    // Stages are issued in stream order (stage gs goes to slot gs % NSTAGE) by thread 0 only.  The producer keeps its
+    // position incrementally: per stage it costs a handful of instructions, which matters because the other seven
+    // warps wait for warp 0 at the next barrier.
     bool exhausted = false;
-    auto issue = [&](int gs) {
+    int p_it = 0, p_ti = 0, p_slot = 0, p_n = 0, p_x0 = 0, p_y0 = 0;
+    auto issue = [&](int) {
         if (exhausted) return;
-        const int ti = gs / total, it = gs - ti * total;
-        if (it == 0) {     // first stage of a tile: claim the tile
+        if (p_it == 0) {     // first stage of a tile: claim the tile
             int claimed = (int)blockIdx.x;
-            if (ti > 0) claimed = (int)(atomicAdd(&g_next_tile[a.sched_slot], 1u) + gridDim.x);
+            if (p_ti > 0) claimed = (int)(atomicAdd(&g_next_tile[a.sched_slot], 1u) + gridDim.x);
             if (claimed >= ntiles) claimed = -1;
-            tile_ids[ti & 3] = claimed;
+            tile_ids[p_ti & 3] = claimed;
             if (claimed < 0) { exhausted = true; return; }
+            p_x0 = (claimed % a.tiles_x) * COLS; claimed /= a.tiles_x;
+            p_y0 = (claimed % a.tiles_y) * ROWS; claimed /= a.tiles_y;
+            p_n = claimed;
         }
-        int tile = tile_ids[ti & 3];
-        const int tbx = tile % a.tiles_x; tile /= a.tiles_x;
-        const int tby = tile % a.tiles_y; tile /= a.tiles_y;
-        const int tx0 = tbx * COLS, ty0 = tby * ROWS;
-        const unsigned slot = ring_addr + (gs % NSTAGE) * SLOT_BYTES, bar = bar_addr + 8 * (gs % NSTAGE);
-        mbar_expect_tx(bar, it < nk ? 2 * K_BYTES : V_BYTES);
-        if (it < nk) {
-            tma_load_4d(slot, &kmap, bar, tx0 - 4, it * KCH, a.ytop0 + ty0 - 2, tile);
-            tma_load_4d(slot + K_BYTES, &qmap, bar, 2 * tx0, it * KCH, 2 * ty0, tile);
+        const unsigned slot = ring_addr + p_slot * SLOT_BYTES, bar = bar_addr + 8 * p_slot;
+        if (p_it < nk) {
+            mbar_expect_tx(bar, 2 * K_BYTES);
+            tma_load_4d(slot, &kmap, bar, p_x0 - 4, p_it * F_KCH, a.ytop0 + p_y0 - 2, p_n);
+            tma_load_4d(slot + K_BYTES, &qmap, bar, 2 * p_x0, p_it * F_KCH, 2 * p_y0, p_n);
         } else {
-            tma_load_4d(slot, &vmap, bar, tx0 - 4, (it - nk) * VCH, a.ytop0 + ty0 - 2, tile);
+            mbar_expect_tx(bar, V_BYTES);
+            tma_load_4d(slot, &vmap, bar, p_x0 - 4, (p_it - nk) * F_VCH, a.ytop0 + p_y0 - 2, p_n);
         }
+        if (++p_it == total) { p_it = 0; ++p_ti; }
+        p_slot = (p_slot + 1) % NSTAGE;
     };
     if (tid == 0) {
 #pragma unroll
@@ -185,7 +199,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     const int k_off0 = t * ROWB + swz(2 + 4 * h + g, t), k_off1 = (t + 4) * ROWB + swz(2 + 4 * h + g, t + 4);
     const int v_offa = g * ROWB + swz(2 + 4 * h + t, g), v_offb = g * ROWB + swz(6 + 4 * h + t, g);
     //   output D fragment: channel g (and g+8), pixels 8h+2t, 8h+2t+1 of high-res rows 2*wrow, 2*wrow+1
-    const int o_off = (2 * wrow) * (VCH * ROWB) + g * ROWB + swz(8 * h + 2 * t, g);
+    const int o_off = (2 * wrow) * (F_VCH * ROWB) + g * ROWB + swz(8 * h + 2 * t, g);
 
     float s[5][4];                         // logits, then probabilities: [dy][2 * row + (cell 2t | 2t+1)], the MMA's D fragment
     unsigned phi[2][5][2];                 // B fragments of the aggregation: probabilities of cells (t, t+4); their
@@ -210,7 +224,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         __syncthreads();     // everyone is done with the slot that is refilled next and has written its output fragment
         if (tid == 0) {
             if (it > nk) {   // the previous stage was a value stage: its output tile is complete in shared memory
-                tma_store_4d(&omap, obuf_addr + ((it - nk - 1) & 1) * O_BYTES, 2 * x0, (it - nk - 1) * VCH, 2 * y0, n);
+                tma_store_4d(&omap, obuf_addr + ((it - nk - 1) & 1) * O_BYTES, 2 * x0, (it - nk - 1) * F_VCH, 2 * y0, n);
                 asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
             }
             issue(gs + NSTAGE - 1);
@@ -223,21 +237,21 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
 
         if (it < nk) {
             // ------------------------------------------------------------- logits: S[16 px][8 cells] += Qt[16 px][8 ch] K[8 ch][8 cells]
-            const unsigned kb = stage + wrow * (KCH * ROWB);
-            const unsigned qb = stage + K_BYTES + (2 * wrow) * (KCH * ROWB);
+            const unsigned kb = stage + wrow * (F_KCH * ROWB);
+            const unsigned qb = stage + K_BYTES + (2 * wrow) * (F_KCH * ROWB);
 #pragma unroll
-            for (int ks = 0; ks < KCH / 8; ++ks) {
+            for (int ks = 0; ks < F_KCH / 8; ++ks) {
                 unsigned ah[4], al[4];
                 ah[0] = lds32(qb + ks * 8 * ROWB + q_off0);                  // Q[ch t][row 0][px g]
-                ah[1] = lds32(qb + KCH * ROWB + ks * 8 * ROWB + q_off0);     // Q[ch t][row 1][px g]
+                ah[1] = lds32(qb + F_KCH * ROWB + ks * 8 * ROWB + q_off0);     // Q[ch t][row 1][px g]
                 ah[2] = lds32(qb + ks * 8 * ROWB + q_off1);                  // Q[ch t+4][row 0]
-                ah[3] = lds32(qb + KCH * ROWB + ks * 8 * ROWB + q_off1);     // Q[ch t+4][row 1]
+                ah[3] = lds32(qb + F_KCH * ROWB + ks * 8 * ROWB + q_off1);     // Q[ch t+4][row 1]
 #pragma unroll
                 for (int i = 0; i < 4; ++i) al[i] = tf32_lo(ah[i]);
 #pragma unroll
                 for (int dy = 0; dy < 5; ++dy) {
-                    const unsigned b0 = lds32(kb + dy * (KCH * ROWB) + ks * 8 * ROWB + k_off0);
-                    const unsigned b1 = lds32(kb + dy * (KCH * ROWB) + ks * 8 * ROWB + k_off1);
+                    const unsigned b0 = lds32(kb + dy * (F_KCH * ROWB) + ks * 8 * ROWB + k_off0);
+                    const unsigned b1 = lds32(kb + dy * (F_KCH * ROWB) + ks * 8 * ROWB + k_off1);
                     mma_tf32(s[dy], ah, b0, b1);
                     mma_tf32(s[dy], al, b0, b1);
                     mma_tf32(s[dy], ah, tf32_lo(b0), tf32_lo(b1));
@@ -293,19 +307,19 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             }
         } else {
             // ------------------------------------------------------------- aggregation: Out[16 ch][8 px] += V[16 ch][8 cells] P[8 cells][8 px]
-            const unsigned vb = stage + wrow * (VCH * ROWB);
-            float acc[VCH / 16][2][4];
+            const unsigned vb = stage + wrow * (F_VCH * ROWB);
+            float acc[F_VCH / 16][2][4];
 #pragma unroll
-            for (int b = 0; b < VCH / 16; ++b)
+            for (int b = 0; b < F_VCH / 16; ++b)
 #pragma unroll
                 for (int r = 0; r < 2; ++r)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[b][r][i] = 0.f;
-            unsigned an[VCH / 16][4];                     // fragments of the next window row, loaded one row ahead
+            unsigned an[F_VCH / 16][4];                     // fragments of the next window row, loaded one row ahead
             auto load_row = [&](int dy) {
 #pragma unroll
-                for (int b = 0; b < VCH / 16; ++b) {
-                    const unsigned p = vb + dy * (VCH * ROWB) + b * 16 * ROWB;
+                for (int b = 0; b < F_VCH / 16; ++b) {
+                    const unsigned p = vb + dy * (F_VCH * ROWB) + b * 16 * ROWB;
                     an[b][0] = lds32(p + v_offa);                 // V[ch g][cell t]
                     an[b][1] = lds32(p + 8 * ROWB + v_offa);      // V[ch g+8][cell t]
                     an[b][2] = lds32(p + v_offb);                 // V[ch g][cell t+4]
@@ -315,28 +329,28 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             load_row(0);
 #pragma unroll
             for (int dy = 0; dy < 5; ++dy) {
-                unsigned ah[VCH / 16][4], al[VCH / 16][4];
+                unsigned ah[F_VCH / 16][4], al[F_VCH / 16][4];
 #pragma unroll
-                for (int b = 0; b < VCH / 16; ++b)
+                for (int b = 0; b < F_VCH / 16; ++b)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) ah[b][i] = an[b][i];
                 if (dy < 4) load_row(dy + 1);
 #pragma unroll
-                for (int b = 0; b < VCH / 16; ++b)
+                for (int b = 0; b < F_VCH / 16; ++b)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) al[b][i] = tf32_lo(ah[b][i]);
 #pragma unroll
-                for (int b = 0; b < VCH / 16; ++b)
+                for (int b = 0; b < F_VCH / 16; ++b)
 #pragma unroll
                     for (int r = 0; r < 2; ++r) mma_tf32(acc[b][r], ah[b], phi[r][dy][0], phi[r][dy][1]);
                 // (Folding the two correction terms into one bfloat16 m16n8k16 MMA was tried: the four extra
                 // float -> bfloat16 packs per fragment cost as much as the MMA they save, and the error grew to 4e-6.)
 #pragma unroll
-                for (int b = 0; b < VCH / 16; ++b)
+                for (int b = 0; b < F_VCH / 16; ++b)
 #pragma unroll
                     for (int r = 0; r < 2; ++r) mma_tf32(acc[b][r], al[b], phi[r][dy][0], phi[r][dy][1]);
 #pragma unroll
-                for (int b = 0; b < VCH / 16; ++b)
+                for (int b = 0; b < F_VCH / 16; ++b)
 #pragma unroll
                     for (int r = 0; r < 2; ++r) mma_tf32(acc[b][r], ah[b], tf32_lo(phi[r][dy][0]), tf32_lo(phi[r][dy][1]));
             }
@@ -345,12 +359,12 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             {
                 const unsigned ob = obuf_addr + ((it - nk) & 1) * O_BYTES + o_off;
 #pragma unroll
-                for (int b = 0; b < VCH / 16; ++b)
+                for (int b = 0; b < F_VCH / 16; ++b)
 #pragma unroll
                     for (int half = 0; half < 2; ++half)
 #pragma unroll
                         for (int r = 0; r < 2; ++r)
-                            sts64(ob + r * (VCH * ROWB) + (16 * b + 8 * half) * ROWB, acc[b][r][2 * half], acc[b][r][2 * half + 1]);
+                            sts64(ob + r * (F_VCH * ROWB) + (16 * b + 8 * half) * ROWB, acc[b][r][2 * half], acc[b][r][2 * half + 1]);
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // make the writes visible to the TMA engine
                 // the buffer written two value stages from now is this one: its store must have finished reading it
                 if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
@@ -360,7 +374,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     // the tile's last output block
     __syncthreads();
     if (tid == 0) {
-        tma_store_4d(&omap, obuf_addr + ((nv - 1) & 1) * O_BYTES, 2 * x0, (nv - 1) * VCH, 2 * y0, n);
+        tma_store_4d(&omap, obuf_addr + ((nv - 1) & 1) * O_BYTES, 2 * x0, (nv - 1) * F_VCH, 2 * y0, n);
         asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
         asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
     }
@@ -409,7 +423,8 @@ constexpr int NSTAGE = SAPA_H16_NSTAGE;
 constexpr int NW = 2 * ROWS;                    // 8 warps
 constexpr int NT = NW * 32;
 constexpr int CTAS_PER_SM = 2;                  // resident CTAs per SM the register budget is tuned for
-static_assert(KCH == 16 && VCH == 32, "one k step of m16n8k16 per key stage, two m blocks per value stage");
+constexpr int KCH = 16;                         // key / query channels per stage (one k step of m16n8k16)
+constexpr int VCH = 32;                         // value channels per stage
 constexpr int BC = 24;                          // key / value box columns
 constexpr int KROW = BC * 2;                    // 48 bytes
 constexpr int QROW = 32;                        // 16 high-res pixels
@@ -775,7 +790,8 @@ static bool make_map(CUtensorMap *map, const void *base, int width, int height, 
 
 // Opts in to the dynamic shared memory, sizes the persistent grid, picks a scheduler slot and launches.
 template <typename Kernel, typename... Maps>
-static int launch_persistent(Kernel kernel, const char *name, int threads, int smem, Args &a, cudaStream_t st, const Maps &...maps) {
+static int launch_persistent(Kernel kernel, const char *name, int threads, int smem, int ctas_per_sm, Args &a, cudaStream_t st,
+                             const Maps &...maps) {
     const long long nblocks = (long long)a.B * a.tiles_x * a.tiles_y;
     if (nblocks > 0x7fffffffLL) {
         set_error("too many tiles");
@@ -791,7 +807,7 @@ static int launch_persistent(Kernel kernel, const char *name, int threads, int s
         set_error("%s: cannot query the SM count", name);
         return SAPA_ERR_LAUNCH;
     }
-    const long long resident = (long long)CTAS_PER_SM * sms;
+    const long long resident = (long long)ctas_per_sm * sms;
     // persistent grid with dynamic tile claiming (static striding left SMs with 6 to 8 tiles instead of ~6.9)
     const unsigned grid = (unsigned)(nblocks < resident ? nblocks : resident);
     static std::atomic<unsigned> next_slot{0};
@@ -819,13 +835,13 @@ int launch_fused_tma(const void *q, const void *k, const void *v, void *out, voi
     if (dtype == SAPA_F32) {
         const auto ty = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
         const auto sw = CU_TENSOR_MAP_SWIZZLE_64B;
-        ok = make_map(&qmap, q, 2 * W, 2 * H, d, B, KCH, ty, 4, HC, sw) && make_map(&kmap, k, W, rows, d, B, KCH, ty, 4, HC, sw) &&
-             make_map(&vmap, v, W, rows, C, B, VCH, ty, 4, HC, sw) && make_map(&omap, out, 2 * W, 2 * H, C, B, VCH, ty, 4, HC, sw);
+        ok = make_map(&qmap, q, 2 * W, 2 * H, d, B, F_KCH, ty, 4, HC, sw) && make_map(&kmap, k, W, rows, d, B, F_KCH, ty, 4, HC, sw) &&
+             make_map(&vmap, v, W, rows, C, B, F_VCH, ty, 4, HC, sw) && make_map(&omap, out, 2 * W, 2 * H, C, B, F_VCH, ty, 4, HC, sw);
     } else {
         const auto ty = dtype == SAPA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-        ok = make_map(&qmap, q, 2 * W, 2 * H, d, B, KCH, ty, 2, 16, CU_TENSOR_MAP_SWIZZLE_32B) &&
-             make_map(&kmap, k, W, rows, d, B, KCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE) &&
-             make_map(&vmap, v, W, rows, C, B, VCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE);
+        ok = make_map(&qmap, q, 2 * W, 2 * H, d, B, h16::KCH, ty, 2, 16, CU_TENSOR_MAP_SWIZZLE_32B) &&
+             make_map(&kmap, k, W, rows, d, B, h16::KCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+             make_map(&vmap, v, W, rows, C, B, h16::VCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (!ok) {
         set_error("sapa_tma_fused: cuTensorMapEncodeTiled rejected the tensor layout");
@@ -834,15 +850,15 @@ int launch_fused_tma(const void *q, const void *k, const void *v, void *out, voi
     Args a{};
     a.out = out; a.attn = attn;
     a.B = B; a.d = d; a.C = C; a.H = H; a.W = W; a.rows = rows; a.ytop0 = ytop0;
-    static_assert(h16::COLS == COLS && h16::CTAS_PER_SM == CTAS_PER_SM, "both kernels use the same tile and residency");
+    static_assert(h16::COLS == COLS, "both kernels use the same tile");
     a.tiles_x = ceil_div(W, COLS);
     a.tiles_y = ceil_div(H, ROWS);
     constexpr int smem32 = NSTAGE * SLOT_BYTES + 2 * O_BYTES + 1024;
     if (dtype == SAPA_F32)
-        return launch_persistent(sapa_tma_fused_f32_kernel, "sapa_tma_fused_f32_kernel", NT, smem32, a, st, qmap, kmap, vmap, omap);
+        return launch_persistent(sapa_tma_fused_f32_kernel, "sapa_tma_fused_f32_kernel", NT, smem32, CTAS_PER_SM, a, st, qmap, kmap, vmap, omap);
     if (dtype == SAPA_F16)
-        return launch_persistent(sapa_tma_fused_16_kernel<__half>, "sapa_tma_fused_16_kernel", h16::NT, h16::SMEM_BYTES, a, st, qmap, kmap, vmap);
-    return launch_persistent(sapa_tma_fused_16_kernel<__nv_bfloat16>, "sapa_tma_fused_16_kernel", h16::NT, h16::SMEM_BYTES, a, st, qmap, kmap, vmap);
+        return launch_persistent(sapa_tma_fused_16_kernel<__half>, "sapa_tma_fused_16_kernel", h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
+    return launch_persistent(sapa_tma_fused_16_kernel<__nv_bfloat16>, "sapa_tma_fused_16_kernel", h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
 }
 
 // 1 if a bounded mbarrier wait of the TMA kernel ever gave up on the current device (synchronises the device).
