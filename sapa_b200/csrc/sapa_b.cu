@@ -543,6 +543,19 @@ int launch_fused_tma(const void *q, const void *k, const void *v, void *out, voi
 int launch_fused_mma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
                      int rows, int ytop0, int dtype, cudaStream_t st);
 
+// tensor-core transposed aggregation (sapa_gath_mma.cu)
+bool gath_mma_supported(int W, int dtype);
+int launch_gath_mma(const void *hi, const void *wt, void *out, int B, int C, int H, int W, int dtype, cudaStream_t st);
+
+// SAPA_GATH_IMPL=tile selects the FP32-pipe gather kernel for A/B measurements
+static int gath_impl_choice() {
+    static const int value = [] {
+        const char *e = getenv("SAPA_GATH_IMPL");
+        return (e != nullptr && strcmp(e, "tile") == 0) ? 1 : 0;
+    }();
+    return value;
+}
+
 // SAPA_FUSED_IMPL selects a fused-forward kernel for A/B measurements: "tile" = FP32-pipe tiled kernel,
 // "mma" = tensor-core kernel with cp.async staging, unset / anything else = the best available
 // (float32 with 16-byte aligned rows: tensor-core kernel with TMA staging).
@@ -641,6 +654,10 @@ static int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int
 
 static int run_gath(const void *hi, const void *wt, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
                     cudaStream_t st) {
+    if (K == 5 && s == 2 && gath_impl_choice() == 0 && gath_mma_supported(W, dtype)) {
+        const int e = launch_gath_mma(hi, wt, out, B, Cc, H, W, dtype, st);
+        if (e != SAPA_ERR_UNSUPPORTED) return e;
+    }
     if (tiled_supported(K, s, dtype)) {
         return SAPA_DISPATCH_FAST(dtype, [&] {
             return launch_gath<scalar_t>(static_cast<const scalar_t *>(hi), static_cast<const scalar_t *>(wt),
