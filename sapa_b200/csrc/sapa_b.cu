@@ -538,8 +538,8 @@ static inline int grid_1d(long long total, int threads) {
 // tensor-core fused forward (sapa_mma.cu)
 bool fused_mma_supported(int W, int dtype);
 bool fused_tma_supported(int W, int dtype);
-int launch_fused_tma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
-                     int rows, int ytop0, int dtype, cudaStream_t st);
+int launch_fused_tma(bool bwd, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d, int C,
+                     int H, int W, int rows, int ytop0, int dtype, cudaStream_t st);
 int launch_fused_mma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
                      int rows, int ytop0, int dtype, cudaStream_t st);
 
@@ -732,7 +732,7 @@ int sapa_fused_forward_slab(const void *query, const void *key, const void *valu
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int impl = fused_impl_choice();
     if (K == 5 && impl == 0 && fused_tma_supported(W, dtype)) {
-        const int e = launch_fused_tma(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
+        const int e = launch_fused_tma(false, query, key, value, out, attn, nullptr, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
     if (K == 5 && impl != 1 && fused_mma_supported(W, dtype))
@@ -764,7 +764,16 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
     SAPA_REQUIRE(aligned16(workspace), SAPA_ERR_ALIGNMENT, "%s: workspace is not 16-byte aligned", fn);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     void *dS = workspace;
-    if (tiled_supported(K, s, dtype)) {
+    bool stage1_done = false;
+    if (K == 5 && s == 2 && fused_impl_choice() == 0 && fused_tma_supported(W, dtype)) {
+        // tensor-core kernel (the fused forward's data flow with the softmax backward in the middle)
+        const int e = launch_fused_tma(true, grad_out, value, key, grad_query, const_cast<void *>(attn), dS, B, C, d, H, W, H, 0,
+                                       dtype, st);
+        if (e != SAPA_OK && e != SAPA_ERR_UNSUPPORTED) return e;
+        stage1_done = e == SAPA_OK;
+    }
+    if (stage1_done) {
+    } else if (tiled_supported(K, s, dtype)) {
         // one kernel: dA = sim(dOut, V) -> softmax backward with the saved A -> dS (workspace), dQ = agg(dS, Key)
         TileArgs a{};
         a.hi = grad_out; a.lo1 = value; a.slots_in = attn; a.lo2 = key; a.out_slots = dS; a.out_hi = grad_query;

@@ -62,7 +62,8 @@ __device__ unsigned g_next_tile[SCHED_SLOTS];
 __device__ unsigned g_ctas_done[SCHED_SLOTS];
 
 struct Args {
-    void *out, *attn;
+    void *out, *attn;      // attn: forward = optional output (softmax), backward = input (saved softmax)
+    void *ws;              // backward only: logit gradients [B, 25, 2H, 2W], written for the key-gradient gather
     int B, d, C, H, W;
     int rows, ytop0;
     int tiles_x, tiles_y;
@@ -122,6 +123,12 @@ __device__ __forceinline__ unsigned tf32_lo(unsigned x) {
 // bits 7..8 of the row's byte offset, which for channel-minor rows of 64 bytes is (channel >> 1) & 3
 __device__ __forceinline__ int swz(int col, int channel) { return ((((col >> 2) ^ (channel >> 1)) & 3) << 4) | ((col & 3) << 2); }
 
+// BWD = false: out = atn(softmax(sim(query, key)), value).
+// BWD = true : the first half of the backward pass with the same data flow.  The "query" map is grad_out and the
+//              "key" map the value tensor (logits = dA = sim(grad_out, value) over C channels); the middle step is the
+//              softmax backward dS = A * (dA - sum_k A_k dA_k) with the saved attention map, stored to `ws`; the
+//              "value" map is the key tensor and the output is grad_query = agg(dS, key).
+template <bool BWD>
 __global__ void __launch_bounds__(NT, CTAS_PER_SM)
 sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                           const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap, const Args a) {
@@ -257,7 +264,44 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     mma_tf32(s[dy], ah, tf32_lo(b0), tf32_lo(b1));
                 }
             }
-            if (it == nk - 1) {
+            if (it == nk - 1 && BWD) {
+                // softmax backward over the 25 window slots of each pixel (spread over the 4 lanes of a quad)
+                const bool pix_ok = y < a.H && x0 + 4 * h + l < a.W;
+                const size_t poff = (size_t)n * 25 * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h) + g;
+                const float *ap = static_cast<const float *>(a.attn) + poff;
+                float *wp = static_cast<float *>(a.ws) + poff;
+                float av[5][4];
+#pragma unroll
+                for (int dy = 0; dy < 5; ++dy)
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        av[dy][2 * r] = (pix_ok && ok0) ? __ldg(ap + (size_t)(dy * 5 + 2 * t - l) * hi_plane + (size_t)r * sW) : 0.f;
+                        av[dy][2 * r + 1] = (pix_ok && ok1) ? __ldg(ap + (size_t)(dy * 5 + 2 * t + 1 - l) * hi_plane + (size_t)r * sW) : 0.f;
+                    }
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    float dot = 0.f;
+#pragma unroll
+                    for (int dy = 0; dy < 5; ++dy) dot += av[dy][2 * r] * s[dy][2 * r] + av[dy][2 * r + 1] * s[dy][2 * r + 1];
+                    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+#pragma unroll
+                    for (int dy = 0; dy < 5; ++dy) {
+                        s[dy][2 * r] = av[dy][2 * r] * (s[dy][2 * r] - dot);
+                        s[dy][2 * r + 1] = av[dy][2 * r + 1] * (s[dy][2 * r + 1] - dot);
+                    }
+                }
+                if (pix_ok) {
+#pragma unroll
+                    for (int dy = 0; dy < 5; ++dy)
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            if (ok0) wp[(size_t)(dy * 5 + 2 * t - l) * hi_plane + (size_t)r * sW] = s[dy][2 * r];
+                            if (ok1) wp[(size_t)(dy * 5 + 2 * t + 1 - l) * hi_plane + (size_t)r * sW] = s[dy][2 * r + 1];
+                        }
+                }
+            }
+            if (it == nk - 1 && !BWD) {
                 // softmax over the 25 window slots of each pixel (spread over the 4 lanes of a quad)
 #pragma unroll
                 for (int r = 0; r < 2; ++r) {
@@ -292,6 +336,8 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                             if (ok1) an[(size_t)(dy * 5 + 2 * t + 1 - l) * hi_plane + (size_t)r * sW] = s[dy][2 * r + 1];
                         }
                 }
+            }
+            if (it == nk - 1) {
                 // cells (2t, 2t+1) -> cells (t, t+4), the k order of the value fragments; split into tf32 hi / lo
                 const int src_a = (lane & ~3) | (t >> 1), src_b = src_a + 2;
                 const bool odd = t & 1;
@@ -473,13 +519,17 @@ __device__ __forceinline__ unsigned pack_pair(__nv_bfloat16, float a, float b) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<const unsigned *>(&h);
 }
+__device__ __forceinline__ float2 unpack_pair(__half, unsigned u) { return __half22float2(*reinterpret_cast<const __half2 *>(&u)); }
+__device__ __forceinline__ float2 unpack_pair(__nv_bfloat16, unsigned u) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u));
+}
 __device__ __forceinline__ float ex2_ftz(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
 
-template <typename T>
+template <typename T, bool BWD>     // BWD: see the float32 kernel
 __global__ void __launch_bounds__(h16::NT, h16::CTAS_PER_SM)
 sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                          const __grid_constant__ CUtensorMap vmap, const Args a) {
@@ -641,7 +691,42 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_addr + 8 * slot);
-            if (it == nk - 1) {
+            if (it == nk - 1 && BWD) {
+                // softmax backward; the saved attention map is read and the logit gradients are written as 32-bit
+                // pairs (the two pixels of a lane are neighbours in memory)
+                const size_t poff = ((size_t)n * 25 * hi_plane + (size_t)(2 * y + r) * sW + 2 * x0 + 2 * t) >> 1;
+                const unsigned *ap = static_cast<const unsigned *>(a.attn) + poff;
+                unsigned *wp = static_cast<unsigned *>(a.ws) + poff;
+#pragma unroll
+                for (int p = 0; p < 2; ++p) {
+                    const bool pix = row_ok && (p == 0 ? col_ok0 : col_ok1);
+                    float av[5][4];
+                    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+                    for (int dy = 0; dy < 5; ++dy) {
+                        unsigned ulo = 0u, uhi = 0u;
+                        if (pix && ok_lo[p]) ulo = __ldg(ap + (size_t)(dy * 5 + dx_lo[p]) * plane_w + 4 * p);
+                        if (pix && ok_hi[p]) uhi = __ldg(ap + (size_t)(dy * 5 + dx_lo[p] + 8) * plane_w + 4 * p);
+                        const float2 flo = unpack_pair(T(), ulo), fhi = unpack_pair(T(), uhi);
+                        av[dy][0] = flo.x; av[dy][1] = flo.y; av[dy][2] = fhi.x; av[dy][3] = fhi.y;
+                        d0 += av[dy][0] * s[p][dy][0] + av[dy][2] * s[p][dy][2];
+                        d1 += av[dy][1] * s[p][dy][1] + av[dy][3] * s[p][dy][3];
+                    }
+#pragma unroll
+                    for (int sh = 4; sh < 32; sh <<= 1) {
+                        d0 += __shfl_xor_sync(0xffffffffu, d0, sh);
+                        d1 += __shfl_xor_sync(0xffffffffu, d1, sh);
+                    }
+#pragma unroll
+                    for (int dy = 0; dy < 5; ++dy) {
+                        pb[p][dy][0] = pack_pair(T(), av[dy][0] * (s[p][dy][0] - d0), av[dy][1] * (s[p][dy][1] - d1));
+                        pb[p][dy][1] = pack_pair(T(), av[dy][2] * (s[p][dy][2] - d0), av[dy][3] * (s[p][dy][3] - d1));
+                        if (pix && ok_lo[p]) wp[(size_t)(dy * 5 + dx_lo[p]) * plane_w + 4 * p] = pb[p][dy][0];
+                        if (pix && ok_hi[p]) wp[(size_t)(dy * 5 + dx_lo[p] + 8) * plane_w + 4 * p] = pb[p][dy][1];
+                    }
+                }
+            }
+            if (it == nk - 1 && !BWD) {
                 // softmax over the 25 window slots of each pixel: 5 rows here x the lanes with the same t.
                 // exp(x - m) = 2^(x * log2(e) - m * log2(e)): one FMA and one ex2 per element.
 #pragma unroll
@@ -694,6 +779,8 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
                             }
                         }
                 }
+            }
+            if (it == nk - 1) {
                 // S^T accumulator fragments -> B fragments of the aggregation
 #pragma unroll
                 for (int p = 0; p < 2; ++p)
@@ -826,9 +913,12 @@ bool fused_tma_supported(int W, int dtype) {
     return false;
 }
 
-// Returns SAPA_ERR_UNSUPPORTED when a tensor map cannot be built (the caller then uses the cp.async kernel).
-int launch_fused_tma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
-                     int rows, int ytop0, int dtype, cudaStream_t st) {
+// Returns SAPA_ERR_UNSUPPORTED when a tensor map cannot be built (the caller then uses another kernel).
+// bwd = false: out = atn(softmax(sim(q, k)), v), attn = optional output.
+// bwd = true : q = grad_out [B,d,2H,2W], k = value [B,d,H,W] (d = value channels), v = key [B,C,H,W] (C = key channels),
+//              attn = saved attention map (input), ws = logit gradients (output), out = grad_query [B,C,2H,2W].
+int launch_fused_tma(bool bwd, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d, int C,
+                     int H, int W, int rows, int ytop0, int dtype, cudaStream_t st) {
     using namespace tma;
     CUtensorMap qmap, kmap, vmap, omap;
     bool ok;
@@ -848,17 +938,23 @@ int launch_fused_tma(const void *q, const void *k, const void *v, void *out, voi
         return SAPA_ERR_UNSUPPORTED;
     }
     Args a{};
-    a.out = out; a.attn = attn;
+    a.out = out; a.attn = attn; a.ws = ws;
     a.B = B; a.d = d; a.C = C; a.H = H; a.W = W; a.rows = rows; a.ytop0 = ytop0;
     static_assert(h16::COLS == COLS, "both kernels use the same tile");
     a.tiles_x = ceil_div(W, COLS);
     a.tiles_y = ceil_div(H, ROWS);
     constexpr int smem32 = NSTAGE * SLOT_BYTES + 2 * O_BYTES + 1024;
-    if (dtype == SAPA_F32)
-        return launch_persistent(sapa_tma_fused_f32_kernel, "sapa_tma_fused_f32_kernel", NT, smem32, CTAS_PER_SM, a, st, qmap, kmap, vmap, omap);
-    if (dtype == SAPA_F16)
-        return launch_persistent(sapa_tma_fused_16_kernel<__half>, "sapa_tma_fused_16_kernel", h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
-    return launch_persistent(sapa_tma_fused_16_kernel<__nv_bfloat16>, "sapa_tma_fused_16_kernel", h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
+    const char *n32 = "sapa_tma_fused_f32_kernel", *n16 = "sapa_tma_fused_16_kernel";
+    if (dtype == SAPA_F32) {
+        if (bwd) return launch_persistent(sapa_tma_fused_f32_kernel<true>, n32, NT, smem32, CTAS_PER_SM, a, st, qmap, kmap, vmap, omap);
+        return launch_persistent(sapa_tma_fused_f32_kernel<false>, n32, NT, smem32, CTAS_PER_SM, a, st, qmap, kmap, vmap, omap);
+    }
+    if (dtype == SAPA_F16) {
+        if (bwd) return launch_persistent(sapa_tma_fused_16_kernel<__half, true>, n16, h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
+        return launch_persistent(sapa_tma_fused_16_kernel<__half, false>, n16, h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
+    }
+    if (bwd) return launch_persistent(sapa_tma_fused_16_kernel<__nv_bfloat16, true>, n16, h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
+    return launch_persistent(sapa_tma_fused_16_kernel<__nv_bfloat16, false>, n16, h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
 }
 
 // 1 if a bounded mbarrier wait of the TMA kernel ever gave up on the current device (synchronises the device).
