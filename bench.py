@@ -217,6 +217,9 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the additional (non-headline) measurements")
+    ap.add_argument("--only-path", default=None, choices=["backward", "deform"],
+                    help="N = 1: run only the SAPA-B fused backward or the SAPA-D fused forward at the cfg2 shapes "
+                         "(warm-up + --steps launches) and print a short JSON line; meant for profiler captures")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     w = dict(WORKLOADS[args.workload])
@@ -256,6 +259,43 @@ def main():
             wl["H"] = sl.stop - sl.start
     bytes_per_launch = algorithmic_bytes(wl, esize)
     pix_per_step_rank = wl["B"] * s * wl["H"] * s * wl["W"]
+
+    if args.only_path is not None:
+        assert world == 1, "--only-path is a single-GPU run"
+        t = make_inputs(wl, dtype, device, seed=900)
+        hi_px = s * wl["H"] * s * wl["W"]
+        if args.only_path == "backward":
+            g_out = torch.randn(wl["B"], wl["C"], s * wl["H"], s * wl["W"], device=device).to(dtype)
+            _, attn_b = fused_forward_raw(t["q"], t["k"], t["v"], K, s, True)
+            code = sapa_b200._lib.dtype_code(t["q"])
+            gq, gk, gv = torch.empty_like(t["q"]), torch.empty_like(t["k"]), torch.empty_like(t["v"])
+            nb = sapa_b200._lib.fused_backward_workspace(wl["B"], wl["H"], wl["W"], K, s, code)
+            ws = torch.empty(nb, dtype=torch.uint8, device=device)
+
+            def run_path():
+                sapa_b200._lib.call("sapa_fused_backward", device, g_out, t["q"], t["k"], t["v"], attn_b, gq, gk, gv, ws, nb,
+                                    wl["B"], wl["d"], wl["C"], wl["H"], wl["W"], K, s, code)
+            launches = 3
+        else:
+            off = (torch.randn(wl["B"], 4 * 9 * 2, s * wl["H"], s * wl["W"], device=device) * 0.5).to(dtype)
+
+            def run_path():
+                sapa_b200.deform_sapa_fused(t["q"], t["k"], t["v"], off, 9, s, 4)
+            launches = 1
+        for _ in range(max(3, args.warmup)):
+            run_path()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            run_path()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        print(json.dumps({"path": args.only_path, "dtype": args.dtype, "ms_per_step": ms, "steps": args.steps,
+                          "mpix_per_s": wl["B"] * hi_px / (ms * 1e-3) / 1e6, "gpu_launches": launches * args.steps,
+                          "l2": "same buffers every step (not flushed): for profiler captures, not a bench value"}), flush=True)
+        return
 
     # rotating buffer sets so that no input is L2-resident from the previous iteration
     nsets = max(2, min(8, -(-3 * L2_BYTES // bytes_per_launch) + 1))

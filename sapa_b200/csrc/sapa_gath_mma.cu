@@ -33,7 +33,7 @@ constexpr int ROWS = 4, COLS = 8;          // low-res output tile of a CTA
 constexpr int NCH = 16;                    // channels per stage = one m block
 constexpr int HR = 2 * (ROWS + 4);         // high-res rows per box
 constexpr int BPX = 32;                    // high-res pixels per box row: 2*x0-8 .. 2*x0+23 (used: 4 .. 27)
-constexpr int NSTAGE = 3;
+constexpr int MAX_STAGE = 6;                // ring slots: 3 boxes of 32 KB (float32) or 6 of 16 KB (16-bit types)
 constexpr int NW = 2 * ROWS;               // 8 warps
 constexpr int NT = NW * 32;
 constexpr int CTAS_PER_SM = 2;
@@ -121,6 +121,7 @@ template <typename T> struct Geo {
     static constexpr int ES = (int)sizeof(T);
     static constexpr int ROWB = BPX * ES;                    // 128 bytes (float32, 128-byte swizzle) or 64 (64-byte swizzle)
     static constexpr int BOX_BYTES = HR * NCH * ROWB;        // 32768 or 16384
+    static constexpr int NSTAGE = ES == 4 ? 3 : MAX_STAGE;
     static constexpr int SMEM_BYTES = NSTAGE * BOX_BYTES + 1024;
 };
 // byte offset of pixel `px` in the row of channel `ch` (rows are channel-minor: the row index modulo 8 is ch & 7)
@@ -134,10 +135,11 @@ __global__ void __launch_bounds__(NT, CTAS_PER_SM)
 sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
     using G = Geo<T>;
     constexpr bool F32 = sizeof(T) == 4;
+    constexpr int NSTAGE = G::NSTAGE;
     extern __shared__ unsigned char smem_dyn[];
     constexpr int NX = NSTAGE + 1;    // exchange buffers: a warp can run at most NSTAGE stages ahead of its partner
     __shared__ __align__(8) unsigned long long bars[2 * NSTAGE + ROWS * NX];   // full[NSTAGE], empty[NSTAGE], pair[ROWS][NX]
-    __shared__ int tile_ids[4];
+    __shared__ int tile_ids[8];      // ring of claimed tiles: the producer is at most MAX_STAGE (< 8) tiles ahead
     __shared__ __align__(16) float xch[NX][ROWS][32][4];               // partial sums of the odd-row warps
     const unsigned ring_addr = ((unsigned)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
     const unsigned full_addr = (unsigned)__cvta_generic_to_shared(bars), empty_addr = full_addr + 8 * NSTAGE;
@@ -182,7 +184,7 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
                 int claimed = (int)blockIdx.x;
                 if (p_ti > 0) claimed = (int)(atomicAdd(&g_next_tile[a.sched_slot], 1u) + gridDim.x);
                 if (claimed >= ntiles) claimed = -1;
-                tile_ids[p_ti & 3] = claimed;
+                tile_ids[p_ti & 7] = claimed;
                 if (claimed < 0) {
                     mbar_arrive(bar);          // completes the phase without data: the warps read -1 and stop
                     if (atomicAdd(&g_ctas_done[a.sched_slot], 1u) == gridDim.x - 1) {
@@ -237,7 +239,7 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
             return;
         }
         if (it == 0) {
-            int tile = tile_ids[ti & 3];      // published by the producer before the barrier's phase completed
+            int tile = tile_ids[ti & 7];      // published by the producer before the barrier's phase completed
             if (tile < 0) break;
             x0 = (tile % a.tiles_x) * COLS; tile /= a.tiles_x;
             const int y0 = (tile % a.tiles_y) * ROWS; tile /= a.tiles_y;

@@ -195,6 +195,14 @@ def test_sapa_b_half_precision_fused_forward_vs_oracle(sp, oracle, shape, dtype)
     assert rel_err(host64(attn), want_p) < 1e-2
     out2, _ = fused_forward_raw(q.to(DEV), k.to(DEV), v.to(DEV), K, s, False)
     assert torch.equal(out, out2)
+    # backward through the public op: tensor-core stage 1 (dS, dQ) and the gather kernels (dKey, dV); the oracle
+    # differentiates the exact function, the kernels work with 16-bit probabilities and logit gradients
+    go = torch.randn(B, C, s * H, s * W, generator=g).to(dtype)
+    wq, wk, wv = oracle.sapa_backward(go.double().numpy(), q.double().numpy(), k.double().numpy(), v.double().numpy(), K, s)
+    qd, kd, vd = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    fq, fk, fv = grads(sp.sapa_fused(qd, kd, vd, K, s), (qd, kd, vd), go.to(DEV))
+    for got, want_g in ((fq, wq), (fk, wk), (fv, wv)):
+        assert rel_err(host64(got), want_g) < 3e-2
 
 
 def test_sapa_b_config2_full_size_vs_oracle_float32(sp, oracle):
