@@ -812,28 +812,21 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
                 }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_addr + 8 * slot);
-            // D fragment of group p: d0,d1 = Out[ch g][px 8p+2t, +1], d2,d3 = Out[ch g+8][same]; the 4 lanes of a quad
-            // write 16 consecutive bytes, the two groups the two halves of a 32-byte sector
+            // D fragment of group p: d0,d1 = Out[ch g][px 8p+2t, +1], d2,d3 = Out[ch g+8][same].  Neighbouring lanes swap one
+            // pair so that even lanes hold pixels 2t .. 2t+3 of the left group and odd lanes 2(t-1) .. 2(t-1)+3 of the right
+            // group: a quad then writes one full 32-byte sector per store instruction (half sectors cost an L1 tag cycle each).
             const int c0 = (it - nk) * VCH;
-            unsigned *o = o_ptr;
+            unsigned *o = o_ptr + ((t & 1) ? 3 : 0);
             o_ptr += (size_t)VCH * plane_w;
-            if (row_ok) {
-                if (c0 + VCH <= C && col_ok1) {        // whole block inside the tensor (col_ok1 implies col_ok0)
+            if (row_ok) {          // warp-uniform; columns are always inside (W is a multiple of the tile width here)
+                const bool odd = t & 1;
 #pragma unroll
-                    for (int j = 0; j < VCH / 8; ++j) {       // channel g + 8j: block j/2, half j%2
-                        __stcs(o, pack_pair(T(), acc[j >> 1][0][2 * (j & 1)], acc[j >> 1][0][2 * (j & 1) + 1]));
-                        __stcs(o + 4, pack_pair(T(), acc[j >> 1][1][2 * (j & 1)], acc[j >> 1][1][2 * (j & 1) + 1]));
-                        o += 8 * plane_w;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < VCH / 8; ++j) {
-                        if (c0 + 8 * j + g < C) {
-                            if (col_ok0) __stcs(o, pack_pair(T(), acc[j >> 1][0][2 * (j & 1)], acc[j >> 1][0][2 * (j & 1) + 1]));
-                            if (col_ok1) __stcs(o + 4, pack_pair(T(), acc[j >> 1][1][2 * (j & 1)], acc[j >> 1][1][2 * (j & 1) + 1]));
-                        }
-                        o += 8 * plane_w;
-                    }
+                for (int j = 0; j < VCH / 8; ++j) {       // channel g + 8j: block j/2, half j%2
+                    const unsigned v0 = pack_pair(T(), acc[j >> 1][0][2 * (j & 1)], acc[j >> 1][0][2 * (j & 1) + 1]);
+                    const unsigned v1 = pack_pair(T(), acc[j >> 1][1][2 * (j & 1)], acc[j >> 1][1][2 * (j & 1) + 1]);
+                    const unsigned got = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);
+                    if (c0 + 8 * j + g < C) __stcs(reinterpret_cast<uint2 *>(o), odd ? make_uint2(got, v1) : make_uint2(v0, got));
+                    o += 8 * plane_w;
                 }
             }
         }
