@@ -11,12 +11,17 @@
 // split into two tf32 terms (hi = top 19 bits, which is what the tensor core reads of a float32 register;
 // lo = x - hi) and use three MMAs (hi*hi + lo*hi + hi*lo), which keeps float32 accuracy.
 //
-// CTA = 4 warps = 4 low-res rows x 8 columns; a warp owns the 8 low-res pixels (16 x 2 high-res) of one row.
-// Everything a stage needs arrives by cp.async into a 4-deep ring of shared-memory slots: first 16 channels of
-// the key halo tile (8 rows x 12 cells, zero outside the image) together with the same 16 channels of the
-// query tile (8 x 16 high-res pixels) per stage, then 32 (f32) or 64 (16-bit) channels of the value halo per
-// stage.  Fragments come out of shared memory with ldmatrix (no register shuffling); no thread waits on a
-// global load inside the compute loops.
+// These kernels stage their tiles with per-lane cp.async copies.  They are the fall-back of the TMA kernels in
+// sapa_tma.cu (same mathematics, tensor maps instead of cp.async) for tensors whose rows are not 16-byte aligned
+// (float32: W % 4 != 0, 16-bit: W % 8 != 0), and remain selectable with SAPA_FUSED_IMPL=mma.
+//
+// CTA = 4 low-res rows x 8 columns.  16-bit kernel: 4 warps, a warp owns the 8 low-res pixels (16 x 2 high-res) of
+// one row and takes all fragments with ldmatrix.  float32 kernel: 8 warps = (row, 4-pixel half); logits on the
+// FP32 pipe with packed FMAs, value fragments with per-lane 32-bit shared loads (the window starts 8 bytes off a
+// 16-byte boundary, so ldmatrix cannot be used).  Everything a stage needs arrives by cp.async into a 4-deep ring
+// of shared-memory slots: first 16 channels of the key halo tile (8 rows, zero outside the image) together with
+// the same 16 channels of the query tile (8 x 16 high-res pixels) per stage, then 32 (f32) or 64 (16-bit) channels
+// of the value halo per stage; no thread waits on a global load inside the compute loops.
 #include "common.cuh"
 
 #include <type_traits>

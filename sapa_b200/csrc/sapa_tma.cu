@@ -468,7 +468,10 @@ constexpr int COLS = 8;                         // low-res columns of a CTA tile
 constexpr int NSTAGE = SAPA_H16_NSTAGE;
 constexpr int NW = 2 * ROWS;                    // 8 warps
 constexpr int NT = NW * 32;
-constexpr int CTAS_PER_SM = 2;                  // resident CTAs per SM the register budget is tuned for
+#ifndef SAPA_H16_CTAS
+#define SAPA_H16_CTAS 2
+#endif
+constexpr int CTAS_PER_SM = SAPA_H16_CTAS;      // resident CTAs per SM the register budget is tuned for
 constexpr int KCH = 16;                         // key / query channels per stage (one k step of m16n8k16)
 constexpr int VCH = 32;                         // value channels per stage
 constexpr int BC = 24;                          // key / value box columns
