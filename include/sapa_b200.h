@@ -48,6 +48,12 @@ extern "C" {
 const char *sapa_last_error(void);
 /* ABI version of this header (bumped on any signature change). */
 int sapa_abi_version(void);
+/* The TMA kernels never spin without a limit: a wait on a shared-memory barrier that gives up (which only a
+ * malfunction can cause) makes the kernel return early and sets a flag on the device.  This reads the flags of the
+ * current device: 0 = no wait ever gave up, bit 0 = fused forward / backward stage 1, bit 1 = gradient gather,
+ * -1 = the flags could not be read.  It synchronises the device; meant for tests and for diagnosing wrong
+ * results, not for the hot path.  No counterpart in the reference. */
+int sapa_wait_timeout_flags(void);
 
 /* ------------------------------------------------------------------ SAPA-B, separate ops ------------- */
 

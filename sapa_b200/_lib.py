@@ -38,7 +38,7 @@ _SIGNATURES = {
     "sapa_deform_fused_forward": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
 }
 EXPORTS = sorted(list(_SIGNATURES) + ["sapa_last_error", "sapa_abi_version", "sapa_fused_backward_workspace",
-                                           "sapa_fused_backward_static_capacity"])
+                                           "sapa_fused_backward_static_capacity", "sapa_wait_timeout_flags"])
 
 
 def lib() -> ctypes.CDLL:
@@ -68,6 +68,8 @@ def lib() -> ctypes.CDLL:
     handle.sapa_fused_backward_workspace.restype = ctypes.c_size_t
     handle.sapa_fused_backward_static_capacity.argtypes = []
     handle.sapa_fused_backward_static_capacity.restype = ctypes.c_size_t
+    handle.sapa_wait_timeout_flags.argtypes = []
+    handle.sapa_wait_timeout_flags.restype = ctypes.c_int
     if handle.sapa_abi_version() != ABI_VERSION:
         raise RuntimeError("libsapa_b200.so has a different ABI version than this Python package; rebuild it")
     _lib = handle
@@ -113,6 +115,12 @@ def call(name: str, device: torch.device, *args, allow_unsupported: bool = False
         msg = handle.sapa_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"{name} failed with status {status}: {msg}")
     return 0
+
+
+def wait_timeout_flags(device) -> int:
+    """Bit mask of the kernels whose bounded barrier waits ever gave up on ``device`` (0 = none); synchronises."""
+    with torch.cuda.device(device):
+        return int(lib().sapa_wait_timeout_flags())
 
 
 def fused_backward_workspace(B, H, W, K, s, code) -> int:

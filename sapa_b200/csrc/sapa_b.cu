@@ -543,6 +543,8 @@ int launch_fused_tma(bool bwd, const void *q, const void *k, const void *v, void
 int launch_fused_mma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
                      int rows, int ytop0, int dtype, cudaStream_t st);
 
+int tma_wait_timeout_flag();
+int gath_wait_timeout_flag();
 // tensor-core transposed aggregation (sapa_gath_mma.cu)
 bool gath_mma_supported(int W, int dtype);
 int launch_gath_mma(const void *hi, const void *wt, void *out, int B, int C, int H, int W, int dtype, cudaStream_t st);
@@ -677,6 +679,12 @@ static int run_gath(const void *hi, const void *wt, void *out, int B, int Cc, in
 using namespace sapa;
 
 extern "C" {
+
+int sapa_wait_timeout_flags(void) {
+    const int a = tma_wait_timeout_flag(), b = gath_wait_timeout_flag();
+    if (a < 0 || b < 0) return -1;
+    return (a ? 1 : 0) | (b ? 2 : 0);
+}
 
 int sapa_qk_forward(const void *query, const void *key, void *out, int B, int d, int H, int W, int K, int s, int dtype,
                     void *stream) {

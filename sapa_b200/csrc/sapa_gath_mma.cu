@@ -427,4 +427,11 @@ int launch_gath_mma(const void *hi, const void *wt, void *out, int B, int C, int
     return SAPA_ERR_UNSUPPORTED;
 }
 
+// 1 if a bounded mbarrier wait of the gather kernel ever gave up on the current device (synchronises the device).
+int gath_wait_timeout_flag() {
+    int flag = 0;
+    if (cudaMemcpyFromSymbol(&flag, gmma::g_wait_timeout, sizeof(int)) != cudaSuccess) return -1;
+    return flag;
+}
+
 }  // namespace sapa

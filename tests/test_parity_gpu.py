@@ -503,3 +503,9 @@ def test_config4_decoder_pyramid_bf16_forward(sp):
     assert got.shape == (B, 256, 128, 128) and got.dtype == torch.bfloat16
     assert rel_err(host64(got), host64(want)) < 2e-2
     assert rel_err(host64(fused32), host64(want)) < 1e-5
+
+
+def test_no_barrier_wait_gave_up(sp):
+    """Runs after the other tests of this file: every bounded mbarrier wait of the TMA kernels completed."""
+    from sapa_b200 import _lib
+    assert _lib.wait_timeout_flags(DEV) == 0
