@@ -538,7 +538,7 @@ static inline int grid_1d(long long total, int threads) {
 // tensor-core fused forward (sapa_mma.cu)
 bool fused_mma_supported(int W, int dtype);
 bool fused_tma_supported(int W, int dtype);
-int launch_fused_tma(bool bwd, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d, int C,
+int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d, int C,
                      int H, int W, int rows, int ytop0, int dtype, cudaStream_t st);
 int launch_fused_mma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
                      int rows, int ytop0, int dtype, cudaStream_t st);
@@ -624,6 +624,10 @@ static int check_common(const char *fn, int B, int C, int H, int W, int K, int s
 // sim / agg / gath dispatchers (tiled when possible, else generic)
 static int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
                    cudaStream_t st) {
+    if (K == 5 && s == 2 && fused_impl_choice() == 0 && fused_tma_supported(W, dtype)) {     // logit half of the TMA kernel
+        const int e = launch_fused_tma(2, hi, lo, nullptr, nullptr, out, nullptr, B, Cc, 0, H, W, H, 0, dtype, st);
+        if (e != SAPA_ERR_UNSUPPORTED) return e;
+    }
     if (tiled_supported(K, s, dtype)) {
         TileArgs a{};
         a.hi = hi; a.lo1 = lo; a.out_slots = out;
@@ -640,6 +644,10 @@ static int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int
 
 static int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
                    cudaStream_t st) {
+    if (K == 5 && s == 2 && fused_impl_choice() == 0 && fused_tma_supported(W, dtype)) {     // aggregation half of the TMA kernel
+        const int e = launch_fused_tma(3, nullptr, nullptr, lo, out, const_cast<void *>(wt), nullptr, B, 0, Cc, H, W, H, 0, dtype, st);
+        if (e != SAPA_ERR_UNSUPPORTED) return e;
+    }
     if (tiled_supported(K, s, dtype)) {
         TileArgs a{};
         a.slots_in = wt; a.lo2 = lo; a.out_hi = out;
@@ -740,7 +748,7 @@ int sapa_fused_forward_slab(const void *query, const void *key, const void *valu
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int impl = fused_impl_choice();
     if (K == 5 && impl == 0 && fused_tma_supported(W, dtype)) {
-        const int e = launch_fused_tma(false, query, key, value, out, attn, nullptr, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
+        const int e = launch_fused_tma(0, query, key, value, out, attn, nullptr, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
     if (K == 5 && impl != 1 && fused_mma_supported(W, dtype))
@@ -775,7 +783,7 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
     bool stage1_done = false;
     if (K == 5 && s == 2 && fused_impl_choice() == 0 && fused_tma_supported(W, dtype)) {
         // tensor-core kernel (the fused forward's data flow with the softmax backward in the middle)
-        const int e = launch_fused_tma(true, grad_out, value, key, grad_query, const_cast<void *>(attn), dS, B, C, d, H, W, H, 0,
+        const int e = launch_fused_tma(1, grad_out, value, key, grad_query, const_cast<void *>(attn), dS, B, C, d, H, W, H, 0,
                                        dtype, st);
         if (e != SAPA_OK && e != SAPA_ERR_UNSUPPORTED) return e;
         stage1_done = e == SAPA_OK;

@@ -61,6 +61,12 @@ constexpr int SCHED_SLOTS = 256;
 __device__ unsigned g_next_tile[SCHED_SLOTS];
 __device__ unsigned g_ctas_done[SCHED_SLOTS];
 
+// kernel modes: the fused forward, stage 1 of the fused backward, and the two separate ops of the reference's API
+constexpr int MODE_FWD = 0;    // out = atn(softmax(sim(query, key)), value); attn = optional softmax output
+constexpr int MODE_BWD = 1;    // see the float32 kernel
+constexpr int MODE_SIM = 2;    // logits only: attn (output) = sim(query, key); no value stages
+constexpr int MODE_AGG = 3;    // aggregation only: out = atn(attn (input weights), value); no key stages
+
 struct Args {
     void *out, *attn;      // attn: forward = optional output (softmax), backward = input (saved softmax)
     void *ws;              // backward only: logit gradients [B, 25, 2H, 2W], written for the key-gradient gather
@@ -128,7 +134,9 @@ __device__ __forceinline__ int swz(int col, int channel) { return ((((col >> 2) 
 //              "key" map the value tensor (logits = dA = sim(grad_out, value) over C channels); the middle step is the
 //              softmax backward dS = A * (dA - sum_k A_k dA_k) with the saved attention map, stored to `ws`; the
 //              "value" map is the key tensor and the output is grad_query = agg(dS, key).
-template <bool BWD>
+// MODE_SIM / MODE_AGG: the logit half / the aggregation half alone (sapa_qk_forward, sapa_av_forward and the halves of
+//              the separate backward ops); the weights of MODE_AGG are read where MODE_BWD reads the attention map.
+template <int MODE>
 __global__ void __launch_bounds__(NT, CTAS_PER_SM)
 sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                           const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap, const Args a) {
@@ -212,6 +220,21 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     unsigned phi[2][5][2];                 // B fragments of the aggregation: probabilities of cells (t, t+4); their
                                            // low tf32 terms are derived where they are used (2 ALU ops, 20 registers saved)
 
+    // cells (2t, 2t+1) of the logit fragment -> cells (t, t+4), the k order of the value fragments
+    auto realign = [&]() {
+        const int src_a = (lane & ~3) | (t >> 1), src_b = src_a + 2;
+        const bool odd = t & 1;
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int dy = 0; dy < 5; ++dy) {
+                const float a0 = __shfl_sync(0xffffffffu, s[dy][2 * r], src_a), a1 = __shfl_sync(0xffffffffu, s[dy][2 * r + 1], src_a);
+                const float b0 = __shfl_sync(0xffffffffu, s[dy][2 * r], src_b), b1 = __shfl_sync(0xffffffffu, s[dy][2 * r + 1], src_b);
+                phi[r][dy][0] = __float_as_uint(odd ? a1 : a0);
+                phi[r][dy][1] = __float_as_uint(odd ? b1 : b0);
+            }
+    };
+
     int gs = 0;
     for (int ti = 0;; ++ti) {
     // written by thread 0 at least one barrier earlier (tile 0 is known to everybody)
@@ -226,6 +249,19 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     for (int r = 0; r < 2; ++r)
 #pragma unroll
         for (int dy = 0; dy < 5; ++dy) s[dy][2 * r] = s[dy][2 * r + 1] = 0.f;
+
+    if (MODE == MODE_AGG) {      // the weights come from memory instead of from the logit stages
+        const bool pix_ok = y < a.H && x0 + 4 * h + l < a.W;
+        const float *ap = static_cast<const float *>(a.attn) + (size_t)n * 25 * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h) + g;
+#pragma unroll
+        for (int dy = 0; dy < 5; ++dy)
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                s[dy][2 * r] = (pix_ok && ok0) ? __ldg(ap + (size_t)(dy * 5 + 2 * t - l) * hi_plane + (size_t)r * sW) : 0.f;
+                s[dy][2 * r + 1] = (pix_ok && ok1) ? __ldg(ap + (size_t)(dy * 5 + 2 * t + 1 - l) * hi_plane + (size_t)r * sW) : 0.f;
+            }
+        realign();
+    }
 
     for (int it = 0; it < total; ++it, ++gs) {
         __syncthreads();     // everyone is done with the slot that is refilled next and has written its output fragment
@@ -264,7 +300,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                     mma_tf32(s[dy], ah, tf32_lo(b0), tf32_lo(b1));
                 }
             }
-            if (it == nk - 1 && BWD) {
+            if (it == nk - 1 && MODE == MODE_BWD) {
                 // softmax backward over the 25 window slots of each pixel (spread over the 4 lanes of a quad)
                 const bool pix_ok = y < a.H && x0 + 4 * h + l < a.W;
                 const size_t poff = (size_t)n * 25 * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h) + g;
@@ -301,7 +337,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                         }
                 }
             }
-            if (it == nk - 1 && !BWD) {
+            if (it == nk - 1 && MODE == MODE_FWD) {
                 // softmax over the 25 window slots of each pixel (spread over the 4 lanes of a quad)
 #pragma unroll
                 for (int r = 0; r < 2; ++r) {
@@ -326,6 +362,8 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
 #pragma unroll
                     for (int dy = 0; dy < 5; ++dy) { s[dy][2 * r] *= inv; s[dy][2 * r + 1] *= inv; }
                 }
+            }
+            if (it == nk - 1 && (MODE == MODE_FWD || MODE == MODE_SIM)) {      // probabilities, or the raw logits of MODE_SIM
                 if (a.attn != nullptr && y < a.H && x0 + 4 * h + l < a.W) {
                     float *an = static_cast<float *>(a.attn) + (size_t)n * 25 * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h) + g;
 #pragma unroll
@@ -337,20 +375,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                         }
                 }
             }
-            if (it == nk - 1) {
-                // cells (2t, 2t+1) -> cells (t, t+4), the k order of the value fragments; split into tf32 hi / lo
-                const int src_a = (lane & ~3) | (t >> 1), src_b = src_a + 2;
-                const bool odd = t & 1;
-#pragma unroll
-                for (int r = 0; r < 2; ++r)
-#pragma unroll
-                    for (int dy = 0; dy < 5; ++dy) {
-                        const float a0 = __shfl_sync(0xffffffffu, s[dy][2 * r], src_a), a1 = __shfl_sync(0xffffffffu, s[dy][2 * r + 1], src_a);
-                        const float b0 = __shfl_sync(0xffffffffu, s[dy][2 * r], src_b), b1 = __shfl_sync(0xffffffffu, s[dy][2 * r + 1], src_b);
-                        const unsigned ua = __float_as_uint(odd ? a1 : a0), ub = __float_as_uint(odd ? b1 : b0);
-                        phi[r][dy][0] = ua; phi[r][dy][1] = ub;
-                    }
-            }
+            if (it == nk - 1 && MODE != MODE_SIM) realign();
         } else {
             // ------------------------------------------------------------- aggregation: Out[16 ch][8 px] += V[16 ch][8 cells] P[8 cells][8 px]
             const unsigned vb = stage + wrow * (F_VCH * ROWB);
@@ -419,7 +444,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     }
     // the tile's last output block
     __syncthreads();
-    if (tid == 0) {
+    if (tid == 0 && MODE != MODE_SIM) {
         tma_store_4d(&omap, obuf_addr + ((nv - 1) & 1) * O_BYTES, 2 * x0, (nv - 1) * F_VCH, 2 * y0, n);
         asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
         asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
@@ -532,7 +557,7 @@ __device__ __forceinline__ float ex2_ftz(float x) {
     return y;
 }
 
-template <typename T, bool BWD>     // BWD: see the float32 kernel
+template <typename T, int MODE>     // modes: see the float32 kernel
 __global__ void __launch_bounds__(h16::NT, h16::CTAS_PER_SM)
 sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                          const __grid_constant__ CUtensorMap vmap, const Args a) {
@@ -677,6 +702,22 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 #pragma unroll
                     for (int i = 0; i < 4; ++i) s[p][dy][i] = 0.f;
         }
+        if (MODE == MODE_AGG && it == 0) {      // the weights come from memory, already in the packed pair layout
+            const unsigned *ap = static_cast<const unsigned *>(a.attn) +
+                                 (((size_t)n * 25 * hi_plane + (size_t)(2 * y + r) * sW + 2 * x0 + 2 * t) >> 1);
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const bool pix = row_ok && (p == 0 ? col_ok0 : col_ok1);
+#pragma unroll
+                for (int dy = 0; dy < 5; ++dy) {
+                    unsigned ulo = 0u, uhi = 0u;
+                    if (pix && ok_lo[p]) ulo = __ldg(ap + (size_t)(dy * 5 + dx_lo[p]) * plane_w + 4 * p);
+                    if (pix && ok_hi[p]) uhi = __ldg(ap + (size_t)(dy * 5 + dx_lo[p] + 8) * plane_w + 4 * p);
+                    pb[p][dy][0] = movmatrix_trans(ulo);
+                    pb[p][dy][1] = movmatrix_trans(uhi);
+                }
+            }
+        }
         const unsigned stage = ring_addr + slot * h16::SLOT_BYTES;
 
         if (it < nk) {
@@ -694,7 +735,7 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_addr + 8 * slot);
-            if (it == nk - 1 && BWD) {
+            if (it == nk - 1 && MODE == MODE_BWD) {
                 // softmax backward; the saved attention map is read and the logit gradients are written as 32-bit
                 // pairs (the two pixels of a lane are neighbours in memory)
                 const size_t poff = ((size_t)n * 25 * hi_plane + (size_t)(2 * y + r) * sW + 2 * x0 + 2 * t) >> 1;
@@ -729,7 +770,7 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
                     }
                 }
             }
-            if (it == nk - 1 && !BWD) {
+            if (it == nk - 1 && MODE == MODE_FWD) {
                 // softmax over the 25 window slots of each pixel: 5 rows here x the lanes with the same t.
                 // exp(x - m) = 2^(x * log2(e) - m * log2(e)): one FMA and one ex2 per element.
 #pragma unroll
@@ -768,6 +809,17 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
                         pb[p][dy][1] = pack_pair(T(), s[p][dy][2] * i0, s[p][dy][3] * i1);
                     }
                 }
+            }
+            if (it == nk - 1 && MODE == MODE_SIM) {      // raw logits
+#pragma unroll
+                for (int p = 0; p < 2; ++p)
+#pragma unroll
+                    for (int dy = 0; dy < 5; ++dy) {
+                        pb[p][dy][0] = pack_pair(T(), s[p][dy][0], s[p][dy][1]);
+                        pb[p][dy][1] = pack_pair(T(), s[p][dy][2], s[p][dy][3]);
+                    }
+            }
+            if (it == nk - 1 && (MODE == MODE_FWD || MODE == MODE_SIM)) {
                 if (a.attn != nullptr && row_ok) {
                     // the two pixels of a pair are neighbours in memory: one 32-bit store per (window slot, pair)
                     unsigned *an = reinterpret_cast<unsigned *>(static_cast<T *>(a.attn) + (size_t)n * 25 * hi_plane +
@@ -783,7 +835,7 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
                         }
                 }
             }
-            if (it == nk - 1) {
+            if (it == nk - 1 && MODE != MODE_SIM) {
                 // S^T accumulator fragments -> B fragments of the aggregation
 #pragma unroll
                 for (int p = 0; p < 2; ++p)
@@ -910,29 +962,37 @@ bool fused_tma_supported(int W, int dtype) {
 }
 
 // Returns SAPA_ERR_UNSUPPORTED when a tensor map cannot be built (the caller then uses another kernel).
-// bwd = false: out = atn(softmax(sim(q, k)), v), attn = optional output.
-// bwd = true : q = grad_out [B,d,2H,2W], k = value [B,d,H,W] (d = value channels), v = key [B,C,H,W] (C = key channels),
-//              attn = saved attention map (input), ws = logit gradients (output), out = grad_query [B,C,2H,2W].
-int launch_fused_tma(bool bwd, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d, int C,
+// mode 0 (forward): out = atn(softmax(sim(q, k)), v), attn = optional output.
+// mode 1 (backward stage 1): q = grad_out [B,d,2H,2W], k = value [B,d,H,W] (d = value channels), v = key [B,C,H,W]
+//        (C = key channels), attn = saved attention map (input), ws = logit gradients (output), out = grad_query.
+// mode 2 (sim): attn (output) = sim(q, k); v, out unused, C ignored.   mode 3 (agg): out = atn(attn (input), v); q, k unused, d ignored.
+int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d, int C,
                      int H, int W, int rows, int ytop0, int dtype, cudaStream_t st) {
     using namespace tma;
+    if (mode == MODE_SIM) C = 0;
+    if (mode == MODE_AGG) d = 0;
+    const bool use_qk = mode != MODE_AGG, use_v = mode != MODE_SIM;
     CUtensorMap qmap, kmap, vmap, omap;
-    bool ok;
+    bool ok = true;
     if (dtype == SAPA_F32) {
         const auto ty = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
         const auto sw = CU_TENSOR_MAP_SWIZZLE_64B;
-        ok = make_map(&qmap, q, 2 * W, 2 * H, d, B, F_KCH, ty, 4, HC, sw) && make_map(&kmap, k, W, rows, d, B, F_KCH, ty, 4, HC, sw) &&
-             make_map(&vmap, v, W, rows, C, B, F_VCH, ty, 4, HC, sw) && make_map(&omap, out, 2 * W, 2 * H, C, B, F_VCH, ty, 4, HC, sw);
+        if (use_qk) ok = ok && make_map(&qmap, q, 2 * W, 2 * H, d, B, F_KCH, ty, 4, HC, sw) && make_map(&kmap, k, W, rows, d, B, F_KCH, ty, 4, HC, sw);
+        if (use_v) ok = ok && make_map(&vmap, v, W, rows, C, B, F_VCH, ty, 4, HC, sw) && make_map(&omap, out, 2 * W, 2 * H, C, B, F_VCH, ty, 4, HC, sw);
     } else {
         const auto ty = dtype == SAPA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-        ok = make_map(&qmap, q, 2 * W, 2 * H, d, B, h16::KCH, ty, 2, 16, CU_TENSOR_MAP_SWIZZLE_32B) &&
-             make_map(&kmap, k, W, rows, d, B, h16::KCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE) &&
-             make_map(&vmap, v, W, rows, C, B, h16::VCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (use_qk) ok = ok && make_map(&qmap, q, 2 * W, 2 * H, d, B, h16::KCH, ty, 2, 16, CU_TENSOR_MAP_SWIZZLE_32B) &&
+                         make_map(&kmap, k, W, rows, d, B, h16::KCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (use_v) ok = ok && make_map(&vmap, v, W, rows, C, B, h16::VCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (!ok) {
         set_error("sapa_tma_fused: cuTensorMapEncodeTiled rejected the tensor layout");
         return SAPA_ERR_UNSUPPORTED;
     }
+    // maps a mode never touches still travel as kernel parameters: give them defined contents
+    if (!use_qk) { qmap = vmap; kmap = vmap; }
+    if (!use_v) { vmap = kmap; omap = kmap; }
+    if (dtype != SAPA_F32) omap = vmap;
     Args a{};
     a.out = out; a.attn = attn; a.ws = ws;
     a.B = B; a.d = d; a.C = C; a.H = H; a.W = W; a.rows = rows; a.ytop0 = ytop0;
@@ -941,16 +1001,33 @@ int launch_fused_tma(bool bwd, const void *q, const void *k, const void *v, void
     a.tiles_y = ceil_div(H, ROWS);
     constexpr int smem32 = NSTAGE * SLOT_BYTES + 2 * O_BYTES + 1024;
     const char *n32 = "sapa_tma_fused_f32_kernel", *n16 = "sapa_tma_fused_16_kernel";
+#define SAPA_TMA_LAUNCH32(M) launch_persistent(sapa_tma_fused_f32_kernel<M>, n32, NT, smem32, CTAS_PER_SM, a, st, qmap, kmap, vmap, omap)
+#define SAPA_TMA_LAUNCH16(T, M) \
+    launch_persistent(sapa_tma_fused_16_kernel<T, M>, n16, h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap)
     if (dtype == SAPA_F32) {
-        if (bwd) return launch_persistent(sapa_tma_fused_f32_kernel<true>, n32, NT, smem32, CTAS_PER_SM, a, st, qmap, kmap, vmap, omap);
-        return launch_persistent(sapa_tma_fused_f32_kernel<false>, n32, NT, smem32, CTAS_PER_SM, a, st, qmap, kmap, vmap, omap);
+        switch (mode) {
+            case MODE_FWD: return SAPA_TMA_LAUNCH32(MODE_FWD);
+            case MODE_BWD: return SAPA_TMA_LAUNCH32(MODE_BWD);
+            case MODE_SIM: return SAPA_TMA_LAUNCH32(MODE_SIM);
+            default: return SAPA_TMA_LAUNCH32(MODE_AGG);
+        }
     }
     if (dtype == SAPA_F16) {
-        if (bwd) return launch_persistent(sapa_tma_fused_16_kernel<__half, true>, n16, h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
-        return launch_persistent(sapa_tma_fused_16_kernel<__half, false>, n16, h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
+        switch (mode) {
+            case MODE_FWD: return SAPA_TMA_LAUNCH16(__half, MODE_FWD);
+            case MODE_BWD: return SAPA_TMA_LAUNCH16(__half, MODE_BWD);
+            case MODE_SIM: return SAPA_TMA_LAUNCH16(__half, MODE_SIM);
+            default: return SAPA_TMA_LAUNCH16(__half, MODE_AGG);
+        }
     }
-    if (bwd) return launch_persistent(sapa_tma_fused_16_kernel<__nv_bfloat16, true>, n16, h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
-    return launch_persistent(sapa_tma_fused_16_kernel<__nv_bfloat16, false>, n16, h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap);
+    switch (mode) {
+        case MODE_FWD: return SAPA_TMA_LAUNCH16(__nv_bfloat16, MODE_FWD);
+        case MODE_BWD: return SAPA_TMA_LAUNCH16(__nv_bfloat16, MODE_BWD);
+        case MODE_SIM: return SAPA_TMA_LAUNCH16(__nv_bfloat16, MODE_SIM);
+        default: return SAPA_TMA_LAUNCH16(__nv_bfloat16, MODE_AGG);
+    }
+#undef SAPA_TMA_LAUNCH32
+#undef SAPA_TMA_LAUNCH16
 }
 
 // 1 if a bounded mbarrier wait of the TMA kernel ever gave up on the current device (synchronises the device).
