@@ -153,6 +153,7 @@ def test_sapa_d_half_precision(sp, oracle, name, dtype):
 SHAPES_B = [  # B, d, C, H, W: tile overhang in both directions, channel-chunk tails, a single pixel
     (2, 64, 48, 9, 40), (1, 7, 5, 4, 33), (3, 2, 1, 1, 1), (1, 13, 9, 17, 3), (1, 32, 256, 8, 64),
     (4, 16, 40, 64, 64),   # 512 tiles: persistent CTAs take several tiles, 3 stages per tile against a ring of 4
+    (1, 8, 24, 6, 10),     # even width that is not a multiple of 4: cp.async forward, tensor-core gather with a ragged tile
 ]
 
 
