@@ -30,10 +30,9 @@ namespace sapa {
 namespace gmma {
 
 constexpr int ROWS = 4, COLS = 8;          // low-res output tile of a CTA
-constexpr int NCH = 16;                    // channels per stage = one m block
 constexpr int HR = 2 * (ROWS + 4);         // high-res rows per box
 constexpr int BPX = 32;                    // high-res pixels per box row: 2*x0-8 .. 2*x0+23 (used: 4 .. 27)
-constexpr int MAX_STAGE = 6;                // ring slots: 3 boxes of 32 KB (float32) or 6 of 16 KB (16-bit types)
+constexpr int NSTAGE = 3;                  // ring slots of 32 KB
 constexpr int NW = 2 * ROWS;               // 8 warps
 constexpr int NT = NW * 32;
 constexpr int CTAS_PER_SM = 2;
@@ -120,8 +119,9 @@ __device__ __forceinline__ unsigned pack_pair(__nv_bfloat16, float a, float b) {
 template <typename T> struct Geo {
     static constexpr int ES = (int)sizeof(T);
     static constexpr int ROWB = BPX * ES;                    // 128 bytes (float32, 128-byte swizzle) or 64 (64-byte swizzle)
-    static constexpr int BOX_BYTES = HR * NCH * ROWB;        // 32768 or 16384
-    static constexpr int NSTAGE = ES == 4 ? 3 : MAX_STAGE;
+    static constexpr int NB = ES == 4 ? 1 : 2;               // m blocks of 16 channels per stage (per-stage overhead dominates the
+    static constexpr int NCH = 16 * NB;                      //   16-bit kernel with its single MMA per block: it takes two)
+    static constexpr int BOX_BYTES = HR * NCH * ROWB;        // 32768
     static constexpr int SMEM_BYTES = NSTAGE * BOX_BYTES + 1024;
 };
 // byte offset of pixel `px` in the row of channel `ch` (rows are channel-minor: the row index modulo 8 is ch & 7)
@@ -135,12 +135,14 @@ __global__ void __launch_bounds__(NT, CTAS_PER_SM)
 sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
     using G = Geo<T>;
     constexpr bool F32 = sizeof(T) == 4;
-    constexpr int NSTAGE = G::NSTAGE;
+    constexpr int NB = G::NB, NCH = G::NCH;
     extern __shared__ unsigned char smem_dyn[];
-    constexpr int NX = NSTAGE + 1;    // exchange buffers: a warp can run at most NSTAGE stages ahead of its partner
+    // exchange buffers: the even-row warp releases a ring slot only after it has read its partner's sums of that stage,
+    // so the partner is never more than NSTAGE - 1 stages ahead of an unread buffer
+    constexpr int NX = NSTAGE;
     __shared__ __align__(8) unsigned long long bars[2 * NSTAGE + ROWS * NX];   // full[NSTAGE], empty[NSTAGE], pair[ROWS][NX]
-    __shared__ int tile_ids[8];      // ring of claimed tiles: the producer is at most MAX_STAGE (< 8) tiles ahead
-    __shared__ __align__(16) float xch[NX][ROWS][32][4];               // partial sums of the odd-row warps
+    __shared__ int tile_ids[8];      // ring of claimed tiles: the producer is at most NSTAGE (< 8) tiles ahead
+    __shared__ __align__(16) float xch[NX][ROWS][NB][32][4];           // partial sums of the odd-row warps
     const unsigned ring_addr = ((unsigned)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
     const unsigned full_addr = (unsigned)__cvta_generic_to_shared(bars), empty_addr = full_addr + 8 * NSTAGE;
     const unsigned pair_addr = empty_addr + 8 * NSTAGE;
@@ -277,46 +279,54 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
         }
         const unsigned stage = ring_addr + slot * G::BOX_BYTES + (2 * wy + r) * (NCH * G::ROWB);
 
-        // one accumulator per parent row: five independent MMA chains
-        float acc[5][4];
+        // one accumulator per parent row and m block: five (ten) independent MMA chains
+        float acc[NB][5][4];
 #pragma unroll
-        for (int j = 0; j < 5; ++j)
+        for (int b = 0; b < NB; ++b)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+            for (int j = 0; j < 5; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[b][j][i] = 0.f;
 #pragma unroll
         for (int j = 0; j < 5; ++j) {
-            const unsigned row = stage + 2 * j * (NCH * G::ROWB);
 #pragma unroll
             for (int kg = 0; kg < 3; ++kg) {
-                if constexpr (F32) {
-                    unsigned ah[4], al[4];
-                    ah[0] = lds32(row + a_off[kg][0]);
-                    ah[1] = lds32(row + a_off[kg][0] + 8 * G::ROWB);
-                    ah[2] = lds32(row + a_off[kg][1]);
-                    ah[3] = lds32(row + a_off[kg][1] + 8 * G::ROWB);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) al[i] = tf32_lo(ah[i]);
-                    mma_tf32(acc[j], ah, bw[j][kg][0], bw[j][kg][1]);
-                    mma_tf32(acc[j], al, bw[j][kg][0], bw[j][kg][1]);
-                    mma_tf32(acc[j], ah, tf32_lo(bw[j][kg][0]), tf32_lo(bw[j][kg][1]));
-                } else {
-                    const unsigned a0 = lds32(row + a_off[kg][0]), a1 = lds32(row + a_off[kg][0] + 8 * G::ROWB);
-                    mma_16_k8<T>(acc[j], a0, a1, bw[j][kg][0]);
+                for (int b = 0; b < NB; ++b) {
+                    const unsigned row = stage + 2 * j * (NCH * G::ROWB) + b * 16 * G::ROWB;
+                    if constexpr (F32) {
+                        unsigned ah[4], al[4];
+                        ah[0] = lds32(row + a_off[kg][0]);
+                        ah[1] = lds32(row + a_off[kg][0] + 8 * G::ROWB);
+                        ah[2] = lds32(row + a_off[kg][1]);
+                        ah[3] = lds32(row + a_off[kg][1] + 8 * G::ROWB);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) al[i] = tf32_lo(ah[i]);
+                        mma_tf32(acc[b][j], ah, bw[j][kg][0], bw[j][kg][1]);
+                        mma_tf32(acc[b][j], al, bw[j][kg][0], bw[j][kg][1]);
+                        mma_tf32(acc[b][j], ah, tf32_lo(bw[j][kg][0]), tf32_lo(bw[j][kg][1]));
+                    } else {
+                        const unsigned a0 = lds32(row + a_off[kg][0]), a1 = lds32(row + a_off[kg][0] + 8 * G::ROWB);
+                        mma_16_k8<T>(acc[b][j], a0, a1, bw[j][kg][0]);
+                    }
                 }
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty_addr + 8 * slot);
+        if (r == 1 && lane == 0) mbar_arrive(empty_addr + 8 * slot);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[0][i] += (acc[1][i] + acc[2][i]) + (acc[3][i] + acc[4][i]);
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[b][0][i] += (acc[b][1][i] + acc[b][2][i]) + (acc[b][3][i] + acc[b][4][i]);
 
         // The odd-row warp hands its sums to the even-row warp of the same output row through one of NX buffers,
         // each with its own mbarrier (one arrival per use, so use number u of a buffer completes its phase u).
         const int xi = gs % NX;
-        float *xb = &xch[xi][wy][lane][0];
         const unsigned pbar = pair_addr + 8 * (wy * NX + xi);
         if (r == 1) {
-            *reinterpret_cast<float4 *>(xb) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+                *reinterpret_cast<float4 *>(&xch[xi][wy][b][lane][0]) = make_float4(acc[b][0][0], acc[b][0][1], acc[b][0][2], acc[b][0][3]);
             __syncwarp();
             if (lane == 0) mbar_arrive(pbar);
         } else {
@@ -324,19 +334,27 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
                 atomicExch(&g_wait_timeout, 1);
                 return;
             }
-            const float4 o4 = *reinterpret_cast<const float4 *>(xb);
-            acc[0][0] += o4.x; acc[0][1] += o4.y; acc[0][2] += o4.z; acc[0][3] += o4.w;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                const float4 o4 = *reinterpret_cast<const float4 *>(&xch[xi][wy][b][lane][0]);
+                acc[b][0][0] += o4.x; acc[b][0][1] += o4.y; acc[b][0][2] += o4.z; acc[b][0][3] += o4.w;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_addr + 8 * slot);
             // D fragment: d0,d1 = G[ch g][cols 2t, 2t+1], d2,d3 = G[ch g+8][same]
             const int c0 = it * NCH;
-            if (store_ok) {
-                T *o = o_ptr + (size_t)c0 * a.H * a.W;
 #pragma unroll
-                for (int half = 0; half < 2; ++half)
-                    if (c0 + 8 * half + g < a.C) {
-                        T *oh = o + (size_t)(8 * half) * a.H * a.W;
-                        if constexpr (F32) *reinterpret_cast<float2 *>(oh) = make_float2(acc[0][2 * half], acc[0][2 * half + 1]);
-                        else *reinterpret_cast<unsigned *>(oh) = pack_pair(T(), acc[0][2 * half], acc[0][2 * half + 1]);
-                    }
+            for (int b = 0; b < NB; ++b) {
+                if (store_ok) {
+                    T *o = o_ptr + (size_t)(c0 + 16 * b) * a.H * a.W;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+                        if (c0 + 16 * b + 8 * half + g < a.C) {
+                            T *oh = o + (size_t)(8 * half) * a.H * a.W;
+                            if constexpr (F32) *reinterpret_cast<float2 *>(oh) = make_float2(acc[b][0][2 * half], acc[b][0][2 * half + 1]);
+                            else *reinterpret_cast<unsigned *>(oh) = pack_pair(T(), acc[b][0][2 * half], acc[b][0][2 * half + 1]);
+                        }
+                }
             }
         }
         if (++slot == NSTAGE) { slot = 0; phase ^= 1; }
@@ -372,7 +390,7 @@ static int launch(const void *hi, const void *wt, void *out, int B, int C, int H
     const int sH = 2 * H, sW = 2 * W;
     const cuuint64_t dims[4] = {(cuuint64_t)sW, (cuuint64_t)C, (cuuint64_t)sH, (cuuint64_t)B};
     const cuuint64_t strides[3] = {(cuuint64_t)sH * sW * G::ES, (cuuint64_t)sW * G::ES, (cuuint64_t)C * sH * sW * G::ES};
-    const cuuint32_t box[4] = {(cuuint32_t)BPX, (cuuint32_t)NCH, (cuuint32_t)HR, 1u};
+    const cuuint32_t box[4] = {(cuuint32_t)BPX, (cuuint32_t)G::NCH, (cuuint32_t)HR, 1u};
     const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
     const CUtensorMapDataType ty = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
