@@ -337,19 +337,6 @@ def main():
     barrier()
     t_wall1 = time.perf_counter()
     elapsed_ms = start.elapsed_time(end)
-    if len([x for x in sampler.samples if t_wall0 <= x[0] <= t_wall1]) < 3:
-        t_end = time.perf_counter() + 0.3      # identical load, untimed, only so that the clocks can be sampled
-        i = 0
-        while time.perf_counter() < t_end:
-            step(i)
-            i += 1
-            if i % 64 == 0:
-                torch.cuda.synchronize()
-        torch.cuda.synchronize()
-    sampler.stop_flag.set()
-    sampler.join(timeout=2)
-    clocks = sampler.summary(t_wall0, t_wall1)
-
     if world > 1:
         tt = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -359,6 +346,20 @@ def main():
         pix_per_step = float(pp.item())
     else:
         pix_per_step = float(pix_per_step_rank)
+    # A timed region shorter than a few clock samples: run the identical load a little longer, untimed, only so that
+    # the clocks can be sampled.  The decision and the number of extra steps derive from the max-reduced time, so
+    # every rank takes the same path (a row-sharded step contains an exchange with the neighbouring ranks).
+    if elapsed_ms < 40.0:
+        extra = min(20000, int(300.0 / max(elapsed_ms / args.steps, 1e-3)) + 1)
+        for i in range(extra):
+            step(i)
+            if i % 64 == 63:
+                torch.cuda.synchronize()
+        barrier()
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+    clocks = sampler.summary(t_wall0, t_wall1)
+
     ms_per_step = elapsed_ms / args.steps
     value = pix_per_step / (ms_per_step * 1e-3) / 1e6
 
