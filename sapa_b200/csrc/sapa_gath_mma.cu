@@ -380,6 +380,9 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// one host-side counter for all element types: they share g_next_tile / g_ctas_done
+static std::atomic<unsigned> g_next_sched_slot{0};
+
 template <typename T>
 static int launch(const void *hi, const void *wt, void *out, int B, int C, int H, int W, cudaStream_t st) {
     using G = Geo<T>;
@@ -421,8 +424,7 @@ static int launch(const void *hi, const void *wt, void *out, int B, int C, int H
     }
     const long long resident = (long long)CTAS_PER_SM * sms;
     const unsigned grid = (unsigned)(nblocks < resident ? nblocks : resident);
-    static std::atomic<unsigned> next_slot{0};
-    a.sched_slot = (int)(next_slot.fetch_add(1u) % SCHED_SLOTS);
+    a.sched_slot = (int)(g_next_sched_slot.fetch_add(1u) % SCHED_SLOTS);
     sapa_gath_mma_kernel<T><<<grid, NT, G::SMEM_BYTES, st>>>(xmap, a);
     return check_launch(name);
 }

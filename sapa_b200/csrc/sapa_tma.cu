@@ -923,6 +923,10 @@ static bool make_map(CUtensorMap *map, const void *base, int width, int height, 
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// one host-side counter for every kernel of this file: they all share g_next_tile / g_ctas_done, so two launches that
+// may be in flight together (different streams, different kernels) must never get the same slot
+static std::atomic<unsigned> g_next_sched_slot{0};
+
 // Opts in to the dynamic shared memory, sizes the persistent grid, picks a scheduler slot and launches.
 template <typename Kernel, typename... Maps>
 static int launch_persistent(Kernel kernel, const char *name, int threads, int smem, int ctas_per_sm, Args &a, cudaStream_t st,
@@ -945,8 +949,7 @@ static int launch_persistent(Kernel kernel, const char *name, int threads, int s
     const long long resident = (long long)ctas_per_sm * sms;
     // persistent grid with dynamic tile claiming (static striding left SMs with 6 to 8 tiles instead of ~6.9)
     const unsigned grid = (unsigned)(nblocks < resident ? nblocks : resident);
-    static std::atomic<unsigned> next_slot{0};
-    a.sched_slot = (int)(next_slot.fetch_add(1u) % SCHED_SLOTS);
+    a.sched_slot = (int)(g_next_sched_slot.fetch_add(1u) % SCHED_SLOTS);
     kernel<<<grid, threads, smem, st>>>(maps..., a);
     return check_launch(name);
 }
