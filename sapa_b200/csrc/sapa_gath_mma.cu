@@ -19,15 +19,15 @@
 //     sums through shared memory (an mbarrier handshake per pair and stage), nothing is CTA-wide in the steady state;
 //   * ring protocol: full / empty mbarriers, lane 0 of warp 0 refills a slot as soon as all 8 warps released it;
 //     every wait is bounded and raises g_wait_timeout instead of spinning for ever.
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tma_util.cuh"
 
 #include <atomic>
 
 namespace sapa {
 
 namespace gmma {
+
+using namespace tmau;
 
 constexpr int ROWS = 4, COLS = 8;          // low-res output tile of a CTA
 constexpr int HR = 2 * (ROWS + 4);         // high-res rows per box
@@ -36,11 +36,8 @@ constexpr int NSTAGE = 3;                  // ring slots of 32 KB
 constexpr int NW = 2 * ROWS;               // 8 warps
 constexpr int NT = NW * 32;
 constexpr int CTAS_PER_SM = 2;
-constexpr unsigned TF32_MASK = 0xffffe000u;
-constexpr int WAIT_LIMIT = 1 << 22;
 
 __device__ int g_wait_timeout = 0;
-constexpr int SCHED_SLOTS = 256;           // see sapa_tma.cu: one counter pair per launch in flight
 __device__ unsigned g_next_tile[SCHED_SLOTS];
 __device__ unsigned g_ctas_done[SCHED_SLOTS];
 
@@ -52,52 +49,6 @@ struct Args {
     int sched_slot;
 };
 
-__device__ __forceinline__ void mbar_init(unsigned bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, int bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_test_wait(unsigned bar, unsigned parity) {     // never suspends
-    unsigned ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned bar, unsigned parity) {   // false when the limit was reached
-    for (int i = 0; i < WAIT_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void tma_load_4d(unsigned dst, const CUtensorMap *map, unsigned bar, int c0, int c1, int c2, int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ unsigned lds32(unsigned addr) {
-    unsigned v;
-    asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ unsigned tf32_lo(unsigned x) {
-    return __float_as_uint(__uint_as_float(x) - __uint_as_float(x & TF32_MASK));
-}
-__device__ __forceinline__ void mma_tf32(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-    asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 template <typename T>
 __device__ __forceinline__ void mma_16_k8(float (&d)[4], unsigned a0, unsigned a1, unsigned b0) {
     if constexpr (std::is_same<T, __half>::value)
@@ -107,15 +58,6 @@ __device__ __forceinline__ void mma_16_k8(float (&d)[4], unsigned a0, unsigned a
         asm("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(b0));
 }
-__device__ __forceinline__ unsigned pack_pair(__half, float a, float b) {
-    const __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<const unsigned *>(&h);
-}
-__device__ __forceinline__ unsigned pack_pair(__nv_bfloat16, float a, float b) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<const unsigned *>(&h);
-}
-
 template <typename T> struct Geo {
     static constexpr int ES = (int)sizeof(T);
     static constexpr int ROWB = BPX * ES;                    // 128 bytes (float32, 128-byte swizzle) or 64 (64-byte swizzle)
@@ -363,23 +305,6 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
 }
 
 // ---------------------------------------------------------------------------------- host side
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// cuTensorMapEncodeTiled is a driver entry point, looked up through the runtime (the library links only cudart)
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
 // one host-side counter for all element types: they share g_next_tile / g_ctas_done
 static std::atomic<unsigned> g_next_sched_slot{0};
 
@@ -387,19 +312,12 @@ template <typename T>
 static int launch(const void *hi, const void *wt, void *out, int B, int C, int H, int W, cudaStream_t st) {
     using G = Geo<T>;
     const char *name = "sapa_gath_mma_kernel";
-    EncodeTiledFn encode = encode_tiled_fn();
-    if (encode == nullptr) return SAPA_ERR_UNSUPPORTED;
     CUtensorMap xmap;
-    const int sH = 2 * H, sW = 2 * W;
-    const cuuint64_t dims[4] = {(cuuint64_t)sW, (cuuint64_t)C, (cuuint64_t)sH, (cuuint64_t)B};
-    const cuuint64_t strides[3] = {(cuuint64_t)sH * sW * G::ES, (cuuint64_t)sW * G::ES, (cuuint64_t)C * sH * sW * G::ES};
-    const cuuint32_t box[4] = {(cuuint32_t)BPX, (cuuint32_t)G::NCH, (cuuint32_t)HR, 1u};
-    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
     const CUtensorMapDataType ty = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     const CUtensorMapSwizzle sw = sizeof(T) == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-    if (encode(&xmap, ty, 4, const_cast<void *>(hi), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    if (encode_tiled_fn() == nullptr) return SAPA_ERR_UNSUPPORTED;
+    if (!make_nchw_map(&xmap, hi, 2 * W, 2 * H, C, B, BPX, G::NCH, HR, ty, G::ES, sw)) {
         set_error("%s: cuTensorMapEncodeTiled rejected the tensor layout", name);
         return SAPA_ERR_UNSUPPORTED;
     }

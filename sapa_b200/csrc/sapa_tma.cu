@@ -16,9 +16,7 @@
 //
 // The logits are computed on the tensor cores as well (3 x tf32, M = 16 pixels, N = 8 window cells, K = 8
 // channels): on the FP32 pipe that loop was bound by shared-memory wavefronts (12 per 10 packed FMAs).
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tma_util.cuh"
 
 #include <atomic>
 
@@ -26,6 +24,8 @@
 namespace sapa {
 
 namespace tma {
+
+using namespace tmau;
 
 constexpr int ROWS = 4, COLS = 8;          // low-res tile of a CTA
 constexpr int HH = ROWS + 4;               // halo rows
@@ -49,15 +49,12 @@ constexpr int K_BYTES = HH * F_KCH * ROWB;   // 8192: key box [8 rows][16 ch][16
 constexpr int V_BYTES = HH * F_VCH * ROWB;   // 16384
 constexpr int SLOT_BYTES = V_BYTES > 2 * K_BYTES ? V_BYTES : 2 * K_BYTES;
 constexpr int O_BYTES = 2 * ROWS * F_VCH * ROWB;   // 16384: output box [8 hi rows][32 ch][16 hi cols], double-buffered        // = K_BYTES + the query box [8 hi rows][16 ch][16 hi cols] of 8192 bytes
-constexpr unsigned TF32_MASK = 0xffffe000u;
 constexpr int CTAS_PER_SM = SAPA_F32_CTAS;  // resident CTAs per SM the register budget is tuned for
-constexpr int WAIT_LIMIT = 1 << 22;        // bounded mbarrier wait (each try suspends for a while in hardware)
 
 __device__ int g_wait_timeout = 0;         // set when a bounded wait gave up (read by tma_wait_timeout_flag)
 // Dynamic tile scheduler of the persistent grid.  Every launch uses one of SCHED_SLOTS counter pairs (chosen
 // round-robin on the host); the last CTA of a launch to exit resets its pair, so a pair is clean again long
 // before the round-robin comes back to it (that would need SCHED_SLOTS launches resident at the same time).
-constexpr int SCHED_SLOTS = 256;
 __device__ unsigned g_next_tile[SCHED_SLOTS];
 __device__ unsigned g_ctas_done[SCHED_SLOTS];
 
@@ -76,55 +73,6 @@ struct Args {
     int sched_slot;        // index into g_next_tile / g_ctas_done
 };
 
-__device__ __forceinline__ void mbar_init(unsigned bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, int bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// returns false when the limit was reached
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned bar, unsigned parity) {
-    for (int i = 0; i < WAIT_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void tma_load_4d(unsigned dst, const CUtensorMap *map, unsigned bar, int c0, int c1, int c2, int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-
-__device__ __forceinline__ void mma_tf32(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-    asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// 32-bit load from a shared-memory address (state-space address, so the compiler emits LDS with an immediate
-// offset instead of a generic load with 64-bit address arithmetic)
-__device__ __forceinline__ unsigned lds32(unsigned addr) {
-    unsigned v;
-    asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ void sts64(unsigned addr, float a, float b) {
-    asm volatile("st.shared.v2.f32 [%0], {%1, %2};\n" ::"r"(addr), "f"(a), "f"(b) : "memory");
-}
-// shared -> global tile store; out-of-range parts of the box (tile overhang, channel tail) are clipped
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, unsigned src, int c0, int c1, int c2, int c3) {
-    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n"
-                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-// low term of the two-term tf32 split (the high term is the register itself: the tensor core reads its top 19 bits)
-__device__ __forceinline__ unsigned tf32_lo(unsigned x) {
-    return __float_as_uint(__uint_as_float(x) - __uint_as_float(x & TF32_MASK));
-}
 // byte offset of element `col` of a 64-byte row under the 64-byte swizzle: the 16-byte chunk index is XORed with
 // bits 7..8 of the row's byte offset, which for channel-minor rows of 64 bytes is (channel >> 1) & 3
 __device__ __forceinline__ int swz(int col, int channel) { return ((((col >> 2) ^ (channel >> 1)) & 3) << 4) | ((col & 3) << 2); }
@@ -459,17 +407,6 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     }
 }
 
-__device__ __forceinline__ bool mbar_test_wait(unsigned bar, unsigned parity) {     // never suspends
-    unsigned ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-
 // ---------------------------------------------------------------------------------- float16 / bfloat16
 // Same tile (4 x 8 low-res pixels) and scheduler as the float32 kernel; what differs:
 //   * key / value boxes are 24 columns wide and start at x0 - 8, the nearest 16-byte boundary below the halo
@@ -538,14 +475,6 @@ __device__ __forceinline__ void mma_h16(float (&d)[4], unsigned a0, unsigned a1,
     else
         asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned pack_pair(__half, float a, float b) {
-    const __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<const unsigned *>(&h);
-}
-__device__ __forceinline__ unsigned pack_pair(__nv_bfloat16, float a, float b) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<const unsigned *>(&h);
 }
 __device__ __forceinline__ float2 unpack_pair(__half, unsigned u) { return __half22float2(*reinterpret_cast<const __half2 *>(&u)); }
 __device__ __forceinline__ float2 unpack_pair(__nv_bfloat16, unsigned u) {
@@ -891,38 +820,6 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 }
 
 // ---------------------------------------------------------------------------------- host side
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// cuTensorMapEncodeTiled is a driver entry point; it is looked up through the runtime so that the library links
-// only against cudart.
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
-// 4-D map over a dense NCHW tensor seen as (x, channel, y, image); box = box_w columns x box_ch channels x 8 rows
-static bool make_map(CUtensorMap *map, const void *base, int width, int height, int channels, int images, int box_ch,
-                     CUtensorMapDataType type, int esize, int box_w, CUtensorMapSwizzle swizzle) {
-    EncodeTiledFn encode = encode_tiled_fn();
-    if (encode == nullptr) return false;
-    const cuuint64_t dims[4] = {(cuuint64_t)width, (cuuint64_t)channels, (cuuint64_t)height, (cuuint64_t)images};
-    const cuuint64_t strides[3] = {(cuuint64_t)height * width * esize, (cuuint64_t)width * esize,
-                                   (cuuint64_t)channels * height * width * esize};
-    const cuuint32_t box[4] = {(cuuint32_t)box_w, (cuuint32_t)box_ch, 8u, 1u};
-    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
-    return encode(map, type, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // one host-side counter for every kernel of this file: they all share g_next_tile / g_ctas_done, so two launches that
 // may be in flight together (different streams, different kernels) must never get the same slot
 static std::atomic<unsigned> g_next_sched_slot{0};
@@ -980,13 +877,13 @@ int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void
     if (dtype == SAPA_F32) {
         const auto ty = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
         const auto sw = CU_TENSOR_MAP_SWIZZLE_64B;
-        if (use_qk) ok = ok && make_map(&qmap, q, 2 * W, 2 * H, d, B, F_KCH, ty, 4, HC, sw) && make_map(&kmap, k, W, rows, d, B, F_KCH, ty, 4, HC, sw);
-        if (use_v) ok = ok && make_map(&vmap, v, W, rows, C, B, F_VCH, ty, 4, HC, sw) && make_map(&omap, out, 2 * W, 2 * H, C, B, F_VCH, ty, 4, HC, sw);
+        if (use_qk) ok = ok && make_nchw_map(&qmap, q, 2 * W, 2 * H, d, B, HC, F_KCH, HH, ty, 4, sw) && make_nchw_map(&kmap, k, W, rows, d, B, HC, F_KCH, HH, ty, 4, sw);
+        if (use_v) ok = ok && make_nchw_map(&vmap, v, W, rows, C, B, HC, F_VCH, HH, ty, 4, sw) && make_nchw_map(&omap, out, 2 * W, 2 * H, C, B, HC, F_VCH, HH, ty, 4, sw);
     } else {
         const auto ty = dtype == SAPA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-        if (use_qk) ok = ok && make_map(&qmap, q, 2 * W, 2 * H, d, B, h16::KCH, ty, 2, 16, CU_TENSOR_MAP_SWIZZLE_32B) &&
-                         make_map(&kmap, k, W, rows, d, B, h16::KCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE);
-        if (use_v) ok = ok && make_map(&vmap, v, W, rows, C, B, h16::VCH, ty, 2, h16::BC, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (use_qk) ok = ok && make_nchw_map(&qmap, q, 2 * W, 2 * H, d, B, 16, h16::KCH, HH, ty, 2, CU_TENSOR_MAP_SWIZZLE_32B) &&
+                         make_nchw_map(&kmap, k, W, rows, d, B, h16::BC, h16::KCH, HH, ty, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (use_v) ok = ok && make_nchw_map(&vmap, v, W, rows, C, B, h16::BC, h16::VCH, HH, ty, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (!ok) {
         set_error("sapa_tma_fused: cuTensorMapEncodeTiled rejected the tensor layout");
