@@ -425,7 +425,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
 namespace h16 {
 constexpr int COLS = 8;                         // low-res columns of a CTA tile
 #ifndef SAPA_H16_NSTAGE
-#define SAPA_H16_NSTAGE 6                       // ring slots (a build-time tuning knob)
+#define SAPA_H16_NSTAGE 5                       // ring slots of 20 KB (a build-time tuning knob)
 #endif
 constexpr int NSTAGE = SAPA_H16_NSTAGE;
 constexpr int NW = 2 * ROWS;                    // 8 warps
@@ -434,7 +434,10 @@ constexpr int NT = NW * 32;
 #define SAPA_H16_CTAS 2
 #endif
 constexpr int CTAS_PER_SM = SAPA_H16_CTAS;      // resident CTAs per SM the register budget is tuned for
-constexpr int KCH = 16;                         // key / query channels per stage (one k step of m16n8k16)
+#ifndef SAPA_H16_KCH
+#define SAPA_H16_KCH 32                           // 2 k steps per stage: half as many logit stages (measured 4 % / 9 % faster
+#endif                                           // forward / backward than 16)
+constexpr int KCH = SAPA_H16_KCH;                // key / query channels per stage (k steps of 16 for m16n8k16)
 constexpr int VCH = 32;                         // value channels per stage
 constexpr int BC = 24;                          // key / value box columns
 constexpr int KROW = BC * 2;                    // 48 bytes
@@ -651,16 +654,19 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 
         if (it < nk) {
             // ------------------------------------------------------------- logits
-            unsigned qb[4];
-            ldsm_x4_trans(qb, stage + q_off);
-            const unsigned ka_addr = stage + k_off, kc_addr = stage + k_off2;
 #pragma unroll
-            for (int dy = 0; dy < 5; ++dy) {
-                unsigned ka[4], kc[2];
-                ldsm_x4_trans(ka, ka_addr + dy * (KCH * KROW));
-                ldsm_x2_trans(kc, kc_addr + dy * (KCH * KROW));
-                mma_h16<T>(s[0][dy], ka[0], ka[1], ka[2], ka[3], qb[0], qb[1]);
-                mma_h16<T>(s[1][dy], ka[1], kc[0], ka[3], kc[1], qb[2], qb[3]);
+            for (int ks = 0; ks < KCH / 16; ++ks) {
+                unsigned qb[4];
+                ldsm_x4_trans(qb, stage + q_off + ks * 16 * QROW);
+                const unsigned ka_addr = stage + k_off + ks * 16 * KROW, kc_addr = stage + k_off2 + ks * 16 * KROW;
+#pragma unroll
+                for (int dy = 0; dy < 5; ++dy) {
+                    unsigned ka[4], kc[2];
+                    ldsm_x4_trans(ka, ka_addr + dy * (KCH * KROW));
+                    ldsm_x2_trans(kc, kc_addr + dy * (KCH * KROW));
+                    mma_h16<T>(s[0][dy], ka[0], ka[1], ka[2], ka[3], qb[0], qb[1]);
+                    mma_h16<T>(s[1][dy], ka[1], kc[0], ka[3], kc[1], qb[2], qb[3]);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_addr + 8 * slot);
