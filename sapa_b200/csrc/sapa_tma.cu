@@ -438,7 +438,10 @@ constexpr int CTAS_PER_SM = SAPA_H16_CTAS;      // resident CTAs per SM the regi
 #define SAPA_H16_KCH 32                           // 2 k steps per stage: half as many logit stages (measured 4 % / 9 % faster
 #endif                                           // forward / backward than 16)
 constexpr int KCH = SAPA_H16_KCH;                // key / query channels per stage (k steps of 16 for m16n8k16)
-constexpr int VCH = 32;                         // value channels per stage
+#ifndef SAPA_H16_VCH
+#define SAPA_H16_VCH 32
+#endif
+constexpr int VCH = SAPA_H16_VCH;                // value channels per stage (multiple of 16)
 constexpr int BC = 24;                          // key / value box columns
 constexpr int KROW = BC * 2;                    // 48 bytes
 constexpr int QROW = 32;                        // 16 high-res pixels
