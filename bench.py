@@ -40,7 +40,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused-forward launch at cfg2, from the ncu capture
 # summarised under profiles/ (null until a capture exists for that dtype).
-NCU_TRAFFIC_BYTES = {"f32": 75_536_128 + 83_335_168, "bf16": 37_782_784 + 17_393_408, "f16": None}   # profiles/fused_fwd_tma_cfg2_f32.md
+NCU_TRAFFIC_BYTES = {"f32": 75_536_128 + 83_335_168, "bf16": 37_796_096 + 16_380_672, "f16": None}   # profiles/fused_fwd_tma_cfg2_f32.md
 
 
 def algorithmic_bytes(w, esize):
