@@ -506,6 +506,45 @@ def test_config4_decoder_pyramid_bf16_forward(sp):
     assert rel_err(host64(fused32), host64(want)) < 1e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_forward_and_backward_replay_from_a_cuda_graph(sp, dtype):
+    """The entry points neither synchronise nor allocate, so a stream capture of forward + backward replays to the
+    same bits as the eager calls (new inputs are written into the captured buffers between replays)."""
+    from sapa_b200 import _lib
+    B, d, C, H, W, K, s = 2, 32, 48, 12, 24, 5, 2
+    g = torch.Generator().manual_seed(11)
+    mk = lambda *sh: torch.randn(*sh, generator=g).to(DEV, dtype)
+    q, k, v, go = mk(B, d, s * H, s * W), mk(B, d, H, W), mk(B, C, H, W), mk(B, C, s * H, s * W)
+    out, attn = torch.empty_like(go), torch.empty(B, K * K, s * H, s * W, device=DEV, dtype=dtype)
+    gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    code = _lib.dtype_code(q)
+    nb = _lib.fused_backward_workspace(B, H, W, K, s, code)
+    ws = torch.empty(nb, dtype=torch.uint8, device=DEV)
+
+    def run():
+        _lib.call("sapa_fused_forward", DEV, q, k, v, out, attn, B, d, C, H, W, K, s, code)
+        _lib.call("sapa_fused_backward", DEV, go, q, k, v, attn, gq, gk, gv, ws, nb, B, d, C, H, W, K, s, code)
+
+    run()                                   # warm-up outside the capture (tensor-map encoder lookup, function attributes)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            run()
+    for seed in (21, 22):
+        g2 = torch.Generator().manual_seed(seed)
+        for t in (q, k, v, go):
+            t.copy_(torch.randn(*t.shape, generator=g2).to(DEV, dtype))
+        graph.replay()
+        torch.cuda.synchronize()
+        got = [t.clone() for t in (out, gq, gk, gv)]
+        run()
+        torch.cuda.synchronize()
+        for a, b in zip(got, (out, gq, gk, gv)):
+            assert torch.equal(a, b)
+
+
 def test_no_barrier_wait_gave_up(sp):
     """Runs after the other tests of this file: every bounded mbarrier wait of the TMA kernels completed."""
     from sapa_b200 import _lib
