@@ -154,6 +154,7 @@ SHAPES_B = [  # B, d, C, H, W: tile overhang in both directions, channel-chunk t
     (2, 64, 48, 9, 40), (1, 7, 5, 4, 33), (3, 2, 1, 1, 1), (1, 13, 9, 17, 3), (1, 32, 256, 8, 64),
     (4, 16, 40, 64, 64),   # 512 tiles: persistent CTAs take several tiles, 3 stages per tile against a ring of 4
     (1, 8, 24, 6, 10),     # even width that is not a multiple of 4: cp.async forward, tensor-core gather with a ragged tile
+    (2, 5, 7, 2, 4),       # an image smaller than one TMA box in both directions
 ]
 
 
@@ -181,7 +182,7 @@ def test_sapa_b_seeded_vs_oracle(sp, oracle, shape, K):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("shape", [(2, 64, 48, 9, 40), (4, 16, 40, 64, 64), (1, 24, 72, 7, 8), (1, 8, 16, 5, 12)])
+@pytest.mark.parametrize("shape", [(2, 64, 48, 9, 40), (4, 16, 40, 64, 64), (1, 24, 72, 7, 8), (1, 8, 16, 5, 12), (2, 5, 7, 2, 8)])
 def test_sapa_b_half_precision_fused_forward_vs_oracle(sp, oracle, shape, dtype):
     """16-bit fused forward (rows of 16 bytes: tensor-map kernel; W=12: cp.async kernel) against the float64 oracle
     evaluated on the same rounded inputs; tolerance 1e-2 (16-bit probabilities and outputs)."""
