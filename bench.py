@@ -392,7 +392,7 @@ def main():
     ms_per_step = elapsed_ms / args.steps
     value = pix_per_step / (ms_per_step * 1e-3) / 1e6
 
-    # ---- the same kernel-only measurement for the other element types of config 2 (not the headline; N = 1 only) ----
+    # ---- the same kernel-only measurement for the other element types at the same shapes (not the headline; N = 1 only) ----
     other = {}
     if world == 1 and not args.no_extra and args.workload == "cfg2":
         for name in [n for n in DTYPES if n != args.dtype]:

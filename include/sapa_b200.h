@@ -119,7 +119,7 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
  * The scratch for the logit gradients is a 16 MiB array built into the library, so:
  *   - every GPU that loads the library holds those 16 MiB until the process exits;
  *   - problems whose scratch (sapa_fused_backward_workspace) exceeds sapa_fused_backward_static_capacity()
- *     are refused with SAPA_ERR_WORKSPACE (config 2 in float32, 13.1 MB, fits);
+ *     are refused with SAPA_ERR_WORKSPACE (B=8, 64x64 -> 128x128 in float32 needs 13.1 MB and fits);
  *   - the first call on each device looks the array's address up (cudaGetSymbolAddress, with that device
  *     current); make that first call before any stream capture begins;
  *   - all calls share the one array, which keeps the previous call's contents (nothing needs clearing: it is

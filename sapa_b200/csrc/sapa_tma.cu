@@ -3,7 +3,7 @@
 // Same mathematics and MMA mapping as sapa_mma.cu (3 x tf32 m16n8k8, probabilities kept in registers), but the
 // key / query / value tiles are brought into shared memory by the tensor memory accelerator instead of per-lane
 // cp.async copies.  Measured reason: with 64-byte row segments the cp.async path delivers about one 16-byte
-// lane-copy per clock per SM (4.6 TB/s over the GPU), which alone costs 43 us at config 2, more than the HBM
+// lane-copy per clock per SM (4.6 TB/s over the GPU), which alone costs 43 us at B=8, C=256, d=64, 64x64 -> 128x128, more than the HBM
 // time of the whole op.  One elected thread now issues one cp.async.bulk.tensor per tile:
 //   * tensors are described as 4-D maps (x, channel, y, image); a box of 16 columns x NCH channels x 8 rows
 //     lands in shared memory as [row][channel][16 columns], i.e. 64-byte rows, with the 64-byte swizzle mode;

@@ -47,7 +47,7 @@ SAPA_D_CASES = {
     "d_far": dict(B=1, Cq=4, C=8, H=5, W=6, P=3, s=2, G=2, sigma=4.0),          # many samples outside the image
     "d_s1g1": dict(B=1, Cq=3, C=5, H=4, W=5, P=4, s=1, G=1, sigma=1.0),
 }
-# BASELINE config 1: the CPU-runnable single-op case (1x1 projections, then SAPA-B attention)
+# benchmark configuration 1: the CPU-runnable single-op case (1x1 projections, then SAPA-B attention)
 CFG1 = dict(B=1, Cx=64, Cy=64, H=16, W=16, d=32, K=5, s=2)
 
 

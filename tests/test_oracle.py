@@ -102,7 +102,7 @@ def test_unfold_port_deform_matches_reference_python(name):
 
 
 def test_config1_single_op_forward(oracle):
-    """BASELINE config 1: B=1, X 64x16x16, Y 64x32x32, 1x1 projections to d=32, K=5, s=2, float32."""
+    """Benchmark configuration 1 (the CPU-runnable single-op case): B=1, X 64x16x16, Y 64x32x32, 1x1 projections to d=32, K=5, s=2, float32."""
     g = Golden("cfg1")
     X, Y, Wq, Wk = (g.inputs[k] for k in ("X", "Y", "Wq", "Wk"))
     q = np.einsum("oc,bchw->bohw", Wq, Y).astype(np.float32)

@@ -208,7 +208,7 @@ def test_sapa_b_half_precision_fused_forward_vs_oracle(sp, oracle, shape, dtype)
 
 
 def test_sapa_b_config2_full_size_vs_oracle_float32(sp, oracle):
-    """BASELINE config 2 at full size: B=8, C=256, 64^2 -> 128^2, d=64, K=5, s=2, forward and backward."""
+    """Benchmark configuration 2 at full size: B=8, C=256, 64^2 -> 128^2, d=64, K=5, s=2, forward and backward."""
     B, d, C, H, W, K, s = 8, 64, 256, 64, 64, 5, 2
     g = torch.Generator().manual_seed(0)
     q = torch.randn(B, d, s * H, s * W, generator=g)
@@ -295,7 +295,7 @@ def test_sapa_d_seeded_vs_oracle(sp, oracle, cfg):
 
 
 def test_sapa_d_config3_full_size_properties(sp, oracle):
-    """BASELINE config 3 at full size (q/k channels 64 = 16 per group): fused == separate, a 1-image slice of
+    """Benchmark configuration 3 at full size (q/k channels 64 = 16 per group): fused == separate, a 1-image slice of
     the batch against the oracle, and linearity in the value."""
     B, Cq, C, H, W, P, G, s = 8, 64, 256, 64, 64, 9, 4, 2
     g = torch.Generator().manual_seed(3)
@@ -480,7 +480,7 @@ def test_error_behaviour_on_cuda_tensors(sp):
 
 
 def test_config4_decoder_pyramid_bf16_forward(sp):
-    """BASELINE config 4 (stand-in wiring, random init): encoder features of 64/128/320/512 channels at
+    """Benchmark configuration 4 (stand-in wiring, random init): encoder features of 64/128/320/512 channels at
     128^2/64^2/32^2/16^2 are projected to 256 channels and upsampled 16^2 -> 32^2 -> 64^2 -> 128^2 by three
     chained SAPA modules (d=32, K=5), bf16, forward only.  Checked against the same modules in float32 on the
     separate-op path (1e-2 of the output range; batch 2 instead of 16 keeps the test small)."""
