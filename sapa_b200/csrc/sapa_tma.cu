@@ -1,20 +1,22 @@
-// sapa_tma.cu — float32 fused SAPA-B forward (K = 5, s = 2) with TMA staging.
+// sapa_tma.cu — SAPA-B for K = 5, s = 2 with TMA staging and the contractions on the tensor cores: one float32 kernel
+// and one float16 / bfloat16 kernel, each in four modes (fused forward, stage 1 of the fused backward, logits only,
+// aggregation only).
 //
-// Same mathematics and MMA mapping as sapa_mma.cu (3 x tf32 m16n8k8, probabilities kept in registers), but the
-// key / query / value tiles are brought into shared memory by the tensor memory accelerator instead of per-lane
-// cp.async copies.  Measured reason: with 64-byte row segments the cp.async path delivers about one 16-byte
-// lane-copy per clock per SM (4.6 TB/s over the GPU), which alone costs 43 us at B=8, C=256, d=64, 64x64 -> 128x128, more than the HBM
-// time of the whole op.  One elected thread now issues one cp.async.bulk.tensor per tile:
-//   * tensors are described as 4-D maps (x, channel, y, image); a box of 16 columns x NCH channels x 8 rows
-//     lands in shared memory as [row][channel][16 columns], i.e. 64-byte rows, with the 64-byte swizzle mode;
+// Same mathematics as sapa_mma.cu (probabilities kept in registers between the logit MMAs and the aggregation
+// MMAs), but the key / query / value tiles are brought into shared memory by the tensor memory accelerator instead
+// of per-lane cp.async copies.  Measured reason: with 64-byte row segments the cp.async path delivers about one
+// 16-byte lane-copy per clock per SM (4.6 TB/s over the GPU), which alone costs 43 us at B=8, C=256, d=64,
+// 64x64 -> 128x128, more than the HBM time of the whole op.  One elected thread issues one cp.async.bulk.tensor per tile:
+//   * tensors are described as 4-D maps (x, channel, y, image); a box of BW columns x NCH channels x 8 rows lands
+//     in shared memory as [row][channel][BW columns] (float32: 16 columns = 64-byte rows with the 64-byte swizzle);
 //   * coordinates outside the tensor (image border, tile overhang, channel tails) are filled with zeros by the
 //     hardware, which is exactly the reference's border rule;
 //   * completion is signalled on an mbarrier per ring slot (expect_tx = box bytes); every wait is bounded and
 //     raises a device-side error flag instead of spinning for ever.
-// With channel-minor rows of 64 bytes and the 64-byte swizzle, the per-lane fragment loads of the aggregation
-// (lane = 4 * channel + cell) touch 32 different banks.
+// With channel-minor rows of 64 bytes and the 64-byte swizzle, the per-lane fragment loads of the float32
+// aggregation (lane = 4 * channel + cell) touch 32 different banks.
 //
-// The logits are computed on the tensor cores as well (3 x tf32, M = 16 pixels, N = 8 window cells, K = 8
+// float32 computes the logits on the tensor cores as well (3 x tf32, M = 16 pixels, N = 8 window cells, K = 8
 // channels): on the FP32 pipe that loop was bound by shared-memory wavefronts (12 per 10 packed FMAs).
 #include "tma_util.cuh"
 
@@ -47,8 +49,8 @@ constexpr int NT = 2 * ROWS * 32;          // 8 warps: (row, 4-pixel half)
 constexpr int ROWB = HC * 4;               // 64 bytes
 constexpr int K_BYTES = HH * F_KCH * ROWB;   // 8192: key box [8 rows][16 ch][16 cols]
 constexpr int V_BYTES = HH * F_VCH * ROWB;   // 16384
-constexpr int SLOT_BYTES = V_BYTES > 2 * K_BYTES ? V_BYTES : 2 * K_BYTES;
-constexpr int O_BYTES = 2 * ROWS * F_VCH * ROWB;   // 16384: output box [8 hi rows][32 ch][16 hi cols], double-buffered        // = K_BYTES + the query box [8 hi rows][16 ch][16 hi cols] of 8192 bytes
+constexpr int SLOT_BYTES = V_BYTES > 2 * K_BYTES ? V_BYTES : 2 * K_BYTES;   // a key stage = key box + query box of K_BYTES each
+constexpr int O_BYTES = 2 * ROWS * F_VCH * ROWB;   // 16384: output box [8 hi rows][32 ch][16 hi cols], double-buffered
 constexpr int CTAS_PER_SM = SAPA_F32_CTAS;  // resident CTAs per SM the register budget is tuned for
 
 __device__ int g_wait_timeout = 0;         // set when a bounded wait gave up (read by tma_wait_timeout_flag)
