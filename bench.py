@@ -477,6 +477,41 @@ def main():
                                          "mpix_per_s": pix_per_step_rank / (ms_d * 1e-3) / 1e6,
                                          "config": {"groups": G_, "points": P_, "offset_sigma": 0.5}}
         del t, off, g_out, attn_b
+        # Decoder pyramid (stand-in wiring, random init, forward only, bf16, B = 16): features of 64 / 128 / 320 / 512
+        # channels at 128^2 / 64^2 / 32^2 / 16^2, each projected to 256 channels by a 1x1 convolution, then three
+        # chained SAPA modules (d = 32, K = 5) upsample 16^2 -> 32^2 -> 64^2 -> 128^2.  Whole-module time: GroupNorm
+        # and the 1x1 convolutions are torch kernels, the attention is the fused kernel.
+        torch.manual_seed(0)
+        PB = 16
+        feats = [torch.randn(PB, c, r, r, device=device, dtype=torch.bfloat16) for c, r in ((64, 128), (128, 64), (320, 32), (512, 16))]
+        proj = [torch.nn.Conv2d(c, 256, 1).to(device, torch.bfloat16) for c in (64, 128, 320, 512)]
+        ups = [sapa_b200.SAPA(256, embedding_dim=32).to(device, torch.bfloat16) for _ in range(3)]
+
+        def pyramid():
+            with torch.no_grad():
+                ys = [p(f) for p, f in zip(proj, feats)]
+                x = ys[3]
+                for level, m in zip((2, 1, 0), ups):
+                    x = m(ys[level], x)
+                return x
+
+        def upsampling_only():
+            with torch.no_grad():
+                x = ys_fixed[3]
+                for level, m in zip((2, 1, 0), ups):
+                    x = m(ys_fixed[level], x)
+                return x
+
+        with torch.no_grad():
+            ys_fixed = [p(f) for p, f in zip(proj, feats)]
+        ms_p, ms_u = time_path(pyramid, 10), time_path(upsampling_only, 10)
+        pyr_pix = PB * (32 * 32 + 64 * 64 + 128 * 128)
+        paths["decoder_pyramid_bf16"] = {"ms": ms_p, "ms_sapa_modules_only": ms_u, "batch": PB,
+                                         "mpix_per_s": pyr_pix / (ms_u * 1e-3) / 1e6,
+                                         "note": "three chained SAPA modules incl. GroupNorm and 1x1 projections (torch kernels); "
+                                                 "ms = with the four 256-channel feature projections, mpix_per_s = upsampled pixels of "
+                                                 "the three levels / ms_sapa_modules_only"}
+        del feats, proj, ups, ys_fixed
 
     # ---- end to end: public op, pinned host buffers in and out, copies inside the timed region ----
     e2e_steps = max(3, min(args.steps, 30))
