@@ -7,6 +7,7 @@ reference's three steps ``qk -> F.softmax -> av`` on this library's kernels.
 """
 from __future__ import annotations
 
+import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
@@ -26,6 +27,17 @@ def _check_impl(impl: str) -> str:
     if impl not in ("fused", "separate"):
         raise ValueError(f"impl must be 'fused' or 'separate', got {impl!r}")
     return impl
+
+
+def _common_dtype(*tensors):
+    """Under ``torch.autocast`` the 1x1 projections come out in the autocast type while the value (the module's
+    un-normalised input) keeps the caller's type; the kernels want one element type, so everything is cast to the
+    autocast type.  Outside autocast the tensors pass through untouched (mismatches are then reported by the op).
+    The reference modules have no autocast handling (sapa_base.py:26-40, sapa_deform.py:34-53)."""
+    if tensors[0].is_cuda and torch.is_autocast_enabled():
+        dtype = torch.get_autocast_gpu_dtype()
+        return tuple(t.to(dtype) for t in tensors)
+    return tensors
 
 
 class SAPA(nn.Module):
@@ -50,6 +62,7 @@ class SAPA(nn.Module):
         return self.attention(self.q(y_normed), self.k(x_normed), x)
 
     def attention(self, q, k, v):
+        q, k, v = _common_dtype(q, k, v)
         if self.impl == "fused":
             return sapa_fused(q.contiguous(), k.contiguous(), v.contiguous(), self.up_kernel_size, self.up_factor)
         attn = F.softmax(qk(q, k, self.up_kernel_size, self.up_factor), dim=1)
@@ -86,6 +99,7 @@ class SAPADeform(nn.Module):
         return self.attention(q, k, x, offset)
 
     def attention(self, q, k, x, offset):
+        q, k, x, offset = _common_dtype(q, k, x, offset)
         if self.impl == "fused":
             return deform_sapa_fused(q.contiguous(), k.contiguous(), x.contiguous(), offset.contiguous(),
                                      self.num_point, self.up_factor, self.groups)

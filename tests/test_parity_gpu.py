@@ -507,6 +507,20 @@ def test_config4_decoder_pyramid_bf16_forward(sp):
     assert rel_err(host64(fused32), host64(want)) < 1e-5
 
 
+def test_modules_under_autocast(sp):
+    """Inside torch.autocast the projections are bfloat16 and the value float32: the modules cast to the autocast
+    type and give the bfloat16 result (the reference modules have no autocast handling)."""
+    torch.manual_seed(3)
+    y, x = torch.randn(2, 64, 24, 32, device=DEV), torch.randn(2, 64, 12, 16, device=DEV)
+    for m in (sp.SAPA(64, embedding_dim=16).to(DEV), sp.SAPADeform(64, embedding_dim=8).to(DEV)):
+        with torch.no_grad():
+            want = m(y, x)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                got = m(y, x)
+        assert got.dtype == torch.bfloat16 and got.shape == want.shape
+        assert rel_err(host64(got), host64(want)) < 3e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_fused_forward_and_backward_replay_from_a_cuda_graph(sp, dtype):
     """The entry points neither synchronise nor allocate, so a stream capture of forward + backward replays to the
