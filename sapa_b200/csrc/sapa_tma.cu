@@ -427,7 +427,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
 namespace h16 {
 constexpr int COLS = 8;                         // low-res columns of a CTA tile
 #ifndef SAPA_H16_NSTAGE
-#define SAPA_H16_NSTAGE 5                       // ring slots of 20 KB (a build-time tuning knob)
+#define SAPA_H16_NSTAGE 4                       // ring slots of 20 KB (a build-time tuning knob; 4 measured 2 % faster than 5)
 #endif
 constexpr int NSTAGE = SAPA_H16_NSTAGE;
 constexpr int NW = 2 * ROWS;                    // 8 warps
