@@ -44,7 +44,10 @@ constexpr int HC = 16;                     // halo columns x0-4 .. x0+11 = one 6
 #endif
 constexpr int F_KCH = SAPA_F32_KCH;        // key / query channels per stage (multiple of 8)
 constexpr int F_VCH = SAPA_F32_VCH;        // value channels per stage (multiple of 16)
-constexpr int NSTAGE = 4;
+#ifndef SAPA_F32_NSTAGE
+#define SAPA_F32_NSTAGE 4
+#endif
+constexpr int NSTAGE = SAPA_F32_NSTAGE;    // ring slots of 16 KB
 constexpr int NT = 2 * ROWS * 32;          // 8 warps: (row, 4-pixel half)
 constexpr int ROWB = HC * 4;               // 64 bytes
 constexpr int K_BYTES = HH * F_KCH * ROWB;   // 8192: key box [8 rows][16 ch][16 cols]
