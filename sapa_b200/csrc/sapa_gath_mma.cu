@@ -12,7 +12,7 @@
 // 3-term split for float32 (hi*hi + lo*hi + hi*lo), f16 / bf16 natively.
 //   * W does not depend on the channel: each warp loads its 15 B fragments (5 parent rows x 3 pixel groups) from
 //     the weight tensor ONCE per tile and keeps them in registers while the channels stream by;
-//   * X comes through a TMA ring (box = 32 px x 16 channels x 16 high-res rows, starting at pixel 2*x0 - 8 so that
+//   * X comes through a TMA ring (box = 32 px x 16 (float32) or 32 (16-bit) channels x 16 high-res rows, starting at pixel 2*x0 - 8 so that
 //     rows begin on a 32-byte boundary; zero fill outside the image); swizzled rows make the per-lane fragment
 //     loads bank-conflict-free;
 //   * warp = (output row, upper / lower high-res row of the parents): the two warps of a row add their partial
