@@ -16,7 +16,10 @@
  * (ph/s - (K-1)/2 + dy, pw/s - (K-1)/2 + dx); neighbours outside the image contribute zero
  * (qk_cuda_kernel.cu:50-66, av_cuda_kernel.cu:57-61).
  *
- * Pointers must be aligned to 16 bytes.  `stream` is a cudaStream_t passed as void* (NULL = default
+ * Pointers must be aligned to the element size; the fast kernels additionally need 16-byte alignment (what any
+ * allocator returns).  The separate ops and sapa_fused_backward send a tensor view whose storage offset breaks that
+ * alignment to the scalar generic kernels (the reference accepts such views too); the fused forward entry points
+ * return SAPA_ERR_ALIGNMENT for it.  `stream` is a cudaStream_t passed as void* (NULL = default
  * stream).  The current CUDA device must be the one that owns the pointers.  Functions are re-entrant
  * and do not synchronise.
  */
@@ -46,13 +49,22 @@ extern "C" {
 
 /* Text of the last error raised on the calling thread ("" if none). */
 const char *sapa_last_error(void);
+/* Names of the kernels the most recent entry-point call on the calling thread launched, comma separated and in
+ * launch order (e.g. "sapa_tma_fused_f32_kernel<bwd>,sapa_gath_mma_kernel,sapa_gath_mma_kernel"); "" before the
+ * first call.  A host-side record (no device work): tests use it to assert which kernel a shape exercised, so that
+ * a silent fall-back to a slower kernel cannot pass unnoticed.  No counterpart in the reference. */
+const char *sapa_last_kernels(void);
 /* ABI version of this header (bumped on any signature change). */
 int sapa_abi_version(void);
 /* The TMA kernels never spin without a limit: a wait on a shared-memory barrier that gives up (which only a
  * malfunction can cause) makes the kernel return early and sets a flag on the device.  This reads the flags of the
  * current device: 0 = no wait ever gave up, bit 0 = fused forward / backward stage 1, bit 1 = gradient gather,
- * -1 = the flags could not be read.  It synchronises the device; meant for tests and for diagnosing wrong
- * results, not for the hot path.  No counterpart in the reference. */
+ * -1 = the flags could not be read.  Reading a raised flag clears it and resets the tile schedulers of that kernel
+ * family (a CTA that gave up leaves its scheduler counters dirty), so the library is usable again afterwards.
+ * It synchronises the device; meant for tests and for diagnosing wrong results, not for the hot path.
+ * Graph replays: a launch captured into a CUDA graph keeps its scheduler counters for every replay; replays of
+ * graphs holding these kernels must not overlap each other on one device (ordinary launches on other streams may
+ * overlap them freely).  No counterpart in the reference. */
 int sapa_wait_timeout_flags(void);
 
 /* ------------------------------------------------------------------ SAPA-B, separate ops ------------- */

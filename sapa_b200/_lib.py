@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("SAPA_B200_LIB") or os.path.join(_HERE, "libsapa_b200.
 SAPA_F32, SAPA_F16, SAPA_BF16, SAPA_F64 = 0, 1, 2, 3
 _DTYPE_CODE = {torch.float32: SAPA_F32, torch.float16: SAPA_F16, torch.bfloat16: SAPA_BF16, torch.float64: SAPA_F64}
 SAPA_ERR_UNSUPPORTED = -5
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _lib = None
 
@@ -37,7 +37,7 @@ _SIGNATURES = {
     "sapa_deform_av_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_fused_forward": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
 }
-EXPORTS = sorted(list(_SIGNATURES) + ["sapa_last_error", "sapa_abi_version", "sapa_fused_backward_workspace",
+EXPORTS = sorted(list(_SIGNATURES) + ["sapa_last_error", "sapa_last_kernels", "sapa_abi_version", "sapa_fused_backward_workspace",
                                            "sapa_fused_backward_static_capacity", "sapa_wait_timeout_flags"])
 
 
@@ -62,6 +62,8 @@ def lib() -> ctypes.CDLL:
         fn.restype = ctypes.c_int
     handle.sapa_last_error.argtypes = []
     handle.sapa_last_error.restype = ctypes.c_char_p
+    handle.sapa_last_kernels.argtypes = []
+    handle.sapa_last_kernels.restype = ctypes.c_char_p
     handle.sapa_abi_version.argtypes = []
     handle.sapa_abi_version.restype = ctypes.c_int
     handle.sapa_fused_backward_workspace.argtypes = [_i, _i, _i, _i, _i, _i]
@@ -115,6 +117,19 @@ def call(name: str, device: torch.device, *args, allow_unsupported: bool = False
         msg = handle.sapa_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"{name} failed with status {status}: {msg}")
     return 0
+
+
+def last_kernels() -> list[str]:
+    """Kernels launched by the most recent entry-point call of this thread, in launch order."""
+    text = lib().sapa_last_kernels().decode("utf-8", "replace")
+    return text.split(",") if text else []
+
+
+def aligned(t: torch.Tensor) -> torch.Tensor:
+    """``t`` itself when its first element sits on a 16-byte boundary, else a fresh copy (a contiguous view with an odd
+    storage offset, e.g. ``x[1:]`` of an odd-sized image, is legal input for the reference; the fused kernels need
+    vector alignment)."""
+    return t if t.data_ptr() % 16 == 0 else t.clone()
 
 
 def wait_timeout_flags(device) -> int:

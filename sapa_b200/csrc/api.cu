@@ -1,4 +1,5 @@
-// api.cu — error plumbing of the C ABI: a thread-local message buffer, never exit()/abort().
+// api.cu — error and dispatch plumbing of the C ABI: a thread-local message buffer (never exit()/abort()) and a
+// thread-local record of the kernels the last entry-point call launched.
 #include "common.cuh"
 
 #include <cstring>
@@ -6,6 +7,7 @@
 namespace sapa {
 
 static thread_local char g_error[512] = "";
+static thread_local char g_kernels[512] = "";
 
 void set_error(const char *fmt, ...) {
     va_list ap;
@@ -14,9 +16,21 @@ void set_error(const char *fmt, ...) {
     va_end(ap);
 }
 
+void trace_reset() { g_kernels[0] = '\0'; }
+
+void trace_kernel(const char *name) {
+    const size_t used = strlen(g_kernels), add = strlen(name);
+    if (used + add + 2 > sizeof(g_kernels)) return;
+    if (used != 0) g_kernels[used] = ',';
+    memcpy(g_kernels + used + (used != 0), name, add + 1);
+}
+
 int check_launch(const char *what) {
     const cudaError_t err = cudaGetLastError();
-    if (err == cudaSuccess) return SAPA_OK;
+    if (err == cudaSuccess) {
+        trace_kernel(what);
+        return SAPA_OK;
+    }
     set_error("%s: launch failed: %s", what, cudaGetErrorString(err));
     return SAPA_ERR_LAUNCH;
 }
@@ -27,6 +41,8 @@ extern "C" {
 
 const char *sapa_last_error(void) { return sapa::g_error; }
 
-int sapa_abi_version(void) { return 1; }
+const char *sapa_last_kernels(void) { return sapa::g_kernels; }
+
+int sapa_abi_version(void) { return 2; }
 
 }  // extern "C"

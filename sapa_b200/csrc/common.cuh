@@ -64,7 +64,9 @@ __device__ __forceinline__ void atomic_add(double *p, double v) { atomicAdd(p, v
 
 // ---------------------------------------------------------------------------------- host helpers
 void set_error(const char *fmt, ...);   // stores a thread-local message, see api.cu
-int check_launch(const char *what);     // cudaGetLastError() -> SAPA_OK / SAPA_ERR_LAUNCH
+int check_launch(const char *what);     // cudaGetLastError() -> SAPA_OK (and records `what`) / SAPA_ERR_LAUNCH
+void trace_reset();                     // start of an entry point: forget the kernels of the previous call
+void trace_kernel(const char *name);    // appended by check_launch: read back through sapa_last_kernels()
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -88,11 +90,17 @@ inline int ceil_div(long long a, long long b) { return static_cast<int>((a + b -
         }                                  \
     } while (0)
 
-#define SAPA_CHECK_PTR(fn, p)                                                                      \
-    do {                                                                                           \
-        SAPA_REQUIRE((p) != nullptr, SAPA_ERR_ARGUMENT, "%s: %s is NULL", fn, #p);                  \
-        SAPA_REQUIRE(::sapa::aligned16(p), SAPA_ERR_ALIGNMENT, "%s: %s is not 16-byte aligned", fn, #p); \
+// every tensor pointer must be non-null and aligned to its element size; 16-byte alignment is only needed by the
+// vectorised / tiled / tensor-map kernels and is checked where those are chosen (all_aligned16)
+// (uses the entry point's `dtype` argument)
+#define SAPA_CHECK_PTR(fn, p)                                                                                  \
+    do {                                                                                                       \
+        SAPA_REQUIRE((p) != nullptr, SAPA_ERR_ARGUMENT, "%s: %s is NULL", fn, #p);                              \
+        SAPA_REQUIRE(::sapa::dtype_size(dtype) != 0 && reinterpret_cast<uintptr_t>(p) % ::sapa::dtype_size(dtype) == 0, \
+                     SAPA_ERR_ALIGNMENT, "%s: %s is not aligned to the element size", fn, #p);                  \
     } while (0)
+
+template <typename... P> inline bool all_aligned16(const P *...p) { return (aligned16(p) && ...); }
 
 // Runs the lambda body with `scalar_t` bound to the element type named by the dtype code.
 // SAPA_DISPATCH_FAST: f32 / f16 / bf16 (tiled kernels).  SAPA_DISPATCH_ALL adds f64 (generic kernels).

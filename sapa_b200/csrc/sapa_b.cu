@@ -22,7 +22,6 @@
 //   * generic kernels for every other odd K, s >= 1 and for f64: one thread per output element.
 #include "common.cuh"
 
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -549,28 +548,6 @@ int gath_wait_timeout_flag();
 bool gath_mma_supported(int W, int dtype);
 int launch_gath_mma(const void *hi, const void *wt, void *out, int B, int C, int H, int W, int dtype, cudaStream_t st);
 
-// SAPA_GATH_IMPL=tile selects the FP32-pipe gather kernel for A/B measurements
-static int gath_impl_choice() {
-    static const int value = [] {
-        const char *e = getenv("SAPA_GATH_IMPL");
-        return (e != nullptr && strcmp(e, "tile") == 0) ? 1 : 0;
-    }();
-    return value;
-}
-
-// SAPA_FUSED_IMPL selects a fused-forward kernel for A/B measurements: "tile" = FP32-pipe tiled kernel,
-// "mma" = tensor-core kernel with cp.async staging, unset / anything else = the best available
-// (float32 with 16-byte aligned rows: tensor-core kernel with TMA staging).
-static int fused_impl_choice() {
-    static const int value = [] {
-        const char *e = getenv("SAPA_FUSED_IMPL");
-        if (e != nullptr && strcmp(e, "tile") == 0) return 1;
-        if (e != nullptr && strcmp(e, "mma") == 0) return 2;
-        return 0;
-    }();
-    return value;
-}
-
 static bool tiled_supported(int K, int s, int dtype) {
     return dtype != SAPA_F64 && s == 2 && (K == 5 || K == 3);
 }
@@ -587,7 +564,9 @@ static int launch_tile(TileArgs a, cudaStream_t st) {
         return SAPA_ERR_ARGUMENT;
     }
     sapa_tile_kernel<T, Shape, MODE, 3><<<(unsigned)blocks, Shape::NT, 0, st>>>(a);
-    return check_launch("sapa_tile_kernel");
+    constexpr const char *names[4] = {"sapa_tile_kernel<sim>", "sapa_tile_kernel<agg>", "sapa_tile_kernel<fused>",
+                                      "sapa_tile_kernel<bwd>"};
+    return check_launch(names[MODE]);
 }
 
 template <typename T, int MODE>
@@ -624,11 +603,12 @@ static int check_common(const char *fn, int B, int C, int H, int W, int K, int s
 // sim / agg / gath dispatchers (tiled when possible, else generic)
 static int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
                    cudaStream_t st) {
-    if (K == 5 && s == 2 && fused_impl_choice() == 0 && fused_tma_supported(W, dtype)) {     // logit half of the TMA kernel
+    const bool al = all_aligned16(hi, lo, out);     // misaligned views take the scalar generic kernels
+    if (al && K == 5 && s == 2 && fused_tma_supported(W, dtype)) {     // logit half of the TMA kernel
         const int e = launch_fused_tma(2, hi, lo, nullptr, nullptr, out, nullptr, B, Cc, 0, H, W, H, 0, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
-    if (tiled_supported(K, s, dtype)) {
+    if (al && tiled_supported(K, s, dtype)) {
         TileArgs a{};
         a.hi = hi; a.lo1 = lo; a.out_slots = out;
         a.B = B; a.C1 = Cc; a.C2 = 0; a.H = H; a.W = W; a.rows = H; a.ytop0 = 0;
@@ -644,11 +624,12 @@ static int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int
 
 static int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
                    cudaStream_t st) {
-    if (K == 5 && s == 2 && fused_impl_choice() == 0 && fused_tma_supported(W, dtype)) {     // aggregation half of the TMA kernel
+    const bool al = all_aligned16(wt, lo, out);
+    if (al && K == 5 && s == 2 && fused_tma_supported(W, dtype)) {     // aggregation half of the TMA kernel
         const int e = launch_fused_tma(3, nullptr, nullptr, lo, out, const_cast<void *>(wt), nullptr, B, 0, Cc, H, W, H, 0, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
-    if (tiled_supported(K, s, dtype)) {
+    if (al && tiled_supported(K, s, dtype)) {
         TileArgs a{};
         a.slots_in = wt; a.lo2 = lo; a.out_hi = out;
         a.B = B; a.C1 = 0; a.C2 = Cc; a.H = H; a.W = W; a.rows = H; a.ytop0 = 0;
@@ -664,11 +645,12 @@ static int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int
 
 static int run_gath(const void *hi, const void *wt, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
                     cudaStream_t st) {
-    if (K == 5 && s == 2 && gath_impl_choice() == 0 && gath_mma_supported(W, dtype)) {
+    const bool al = all_aligned16(hi, wt, out);
+    if (al && K == 5 && s == 2 && gath_mma_supported(W, dtype)) {
         const int e = launch_gath_mma(hi, wt, out, B, Cc, H, W, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
-    if (tiled_supported(K, s, dtype)) {
+    if (al && tiled_supported(K, s, dtype)) {
         return SAPA_DISPATCH_FAST(dtype, [&] {
             return launch_gath<scalar_t>(static_cast<const scalar_t *>(hi), static_cast<const scalar_t *>(wt),
                                          static_cast<scalar_t *>(out), B, Cc, H, W, K, st);
@@ -697,6 +679,7 @@ int sapa_wait_timeout_flags(void) {
 int sapa_qk_forward(const void *query, const void *key, void *out, int B, int d, int H, int W, int K, int s, int dtype,
                     void *stream) {
     const char *fn = "sapa_qk_forward";
+    trace_reset();
     if (int e = check_common(fn, B, d, H, W, K, s, dtype)) return e;
     SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, out);
     return run_sim(query, key, out, B, d, H, W, K, s, dtype, static_cast<cudaStream_t>(stream));
@@ -705,6 +688,7 @@ int sapa_qk_forward(const void *query, const void *key, void *out, int B, int d,
 int sapa_qk_backward(const void *grad_out, const void *query, const void *key, void *grad_query, void *grad_key, int B,
                      int d, int H, int W, int K, int s, int dtype, void *stream) {
     const char *fn = "sapa_qk_backward";
+    trace_reset();
     if (int e = check_common(fn, B, d, H, W, K, s, dtype)) return e;
     SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key);
     SAPA_CHECK_PTR(fn, grad_query); SAPA_CHECK_PTR(fn, grad_key);
@@ -716,6 +700,7 @@ int sapa_qk_backward(const void *grad_out, const void *query, const void *key, v
 int sapa_av_forward(const void *attn, const void *value, void *out, int B, int C, int H, int W, int K, int s, int dtype,
                     void *stream) {
     const char *fn = "sapa_av_forward";
+    trace_reset();
     if (int e = check_common(fn, B, C, H, W, K, s, dtype)) return e;
     SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, out);
     return run_agg(attn, value, out, B, C, H, W, K, s, dtype, static_cast<cudaStream_t>(stream));
@@ -724,6 +709,7 @@ int sapa_av_forward(const void *attn, const void *value, void *out, int B, int C
 int sapa_av_backward(const void *grad_out, const void *attn, const void *value, void *grad_attn, void *grad_value, int B,
                      int C, int H, int W, int K, int s, int dtype, void *stream) {
     const char *fn = "sapa_av_backward";
+    trace_reset();
     if (int e = check_common(fn, B, C, H, W, K, s, dtype)) return e;
     SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, value);
     SAPA_CHECK_PTR(fn, grad_attn); SAPA_CHECK_PTR(fn, grad_value);
@@ -735,23 +721,24 @@ int sapa_av_backward(const void *grad_out, const void *attn, const void *value, 
 int sapa_fused_forward_slab(const void *query, const void *key, const void *value, void *out, void *attn, int B, int d,
                             int C, int H, int W, int halo_top, int halo_bottom, int K, int s, int dtype, void *stream) {
     const char *fn = "sapa_fused_forward";
+    trace_reset();
     if (int e = check_common(fn, B, d, H, W, K, s, dtype)) return e;
     SAPA_REQUIRE(C > 0, SAPA_ERR_ARGUMENT, "%s: C must be positive", fn);
     SAPA_REQUIRE(halo_top >= 0 && halo_bottom >= 0, SAPA_ERR_ARGUMENT, "%s: negative halo", fn);
     SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, out);
-    if (attn != nullptr) SAPA_REQUIRE(aligned16(attn), SAPA_ERR_ALIGNMENT, "%s: attn is not 16-byte aligned", fn);
+    SAPA_REQUIRE(all_aligned16(query, key, value, out) && (attn == nullptr || aligned16(attn)), SAPA_ERR_ALIGNMENT,
+                 "%s: the fused kernels need 16-byte aligned tensors (copy the misaligned view, or use the separate ops)", fn);
     SAPA_REQUIRE(tiled_supported(K, s, dtype), SAPA_ERR_UNSUPPORTED,
                  "%s: no fused kernel for K=%d s=%d dtype=%d (use the separate ops)", fn, K, s, dtype);
     TileArgs a{};
     a.hi = query; a.lo1 = key; a.lo2 = value; a.out_hi = out; a.out_slots = attn;
     a.B = B; a.C1 = d; a.C2 = C; a.H = H; a.W = W; a.rows = halo_top + H + halo_bottom; a.ytop0 = halo_top;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int impl = fused_impl_choice();
-    if (K == 5 && impl == 0 && fused_tma_supported(W, dtype)) {
+    if (K == 5 && fused_tma_supported(W, dtype)) {
         const int e = launch_fused_tma(0, query, key, value, out, attn, nullptr, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
-    if (K == 5 && impl != 1 && fused_mma_supported(W, dtype))
+    if (K == 5 && fused_mma_supported(W, dtype))
         return launch_fused_mma(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
     return SAPA_DISPATCH_FAST(dtype, [&] { return launch_tile_ks<scalar_t, MODE_FUSED>(a, K, st); });
 }
@@ -770,6 +757,7 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
                         void *grad_query, void *grad_key, void *grad_value, void *workspace, size_t workspace_bytes, int B,
                         int d, int C, int H, int W, int K, int s, int dtype, void *stream) {
     const char *fn = "sapa_fused_backward";
+    trace_reset();
     if (int e = check_common(fn, B, d, H, W, K, s, dtype)) return e;
     SAPA_REQUIRE(C > 0, SAPA_ERR_ARGUMENT, "%s: C must be positive", fn);
     SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value);
@@ -781,7 +769,9 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     void *dS = workspace;
     bool stage1_done = false;
-    if (K == 5 && s == 2 && fused_impl_choice() == 0 && fused_tma_supported(W, dtype)) {
+    // misaligned views (a storage offset that is not a multiple of 16 bytes) take the chain of scalar generic kernels
+    const bool al = all_aligned16(grad_out, query, key, value, attn, grad_query, grad_key, grad_value);
+    if (al && K == 5 && s == 2 && fused_tma_supported(W, dtype)) {
         // tensor-core kernel (the fused forward's data flow with the softmax backward in the middle)
         const int e = launch_fused_tma(1, grad_out, value, key, grad_query, const_cast<void *>(attn), dS, B, C, d, H, W, H, 0,
                                        dtype, st);
@@ -789,7 +779,7 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
         stage1_done = e == SAPA_OK;
     }
     if (stage1_done) {
-    } else if (tiled_supported(K, s, dtype)) {
+    } else if (al && tiled_supported(K, s, dtype)) {
         // one kernel: dA = sim(dOut, V) -> softmax backward with the saved A -> dS (workspace), dQ = agg(dS, Key)
         TileArgs a{};
         a.hi = grad_out; a.lo1 = value; a.slots_in = attn; a.lo2 = key; a.out_slots = dS; a.out_hi = grad_query;

@@ -292,6 +292,7 @@ extern "C" {
 int sapa_deform_qk_forward(const void *query, const void *key, const void *offset, void *out, int B, int Cq, int H, int W,
                            int P, int s, int G, int dtype, void *stream) {
     const char *fn = "sapa_deform_qk_forward";
+    trace_reset();
     if (int e = check_deform(fn, B, Cq, Cq, H, W, P, s, G, dtype)) return e;
     SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, out);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -307,6 +308,7 @@ int sapa_deform_qk_forward(const void *query, const void *key, const void *offse
 int sapa_deform_av_forward(const void *attn, const void *value, const void *offset, void *out, int B, int C, int H, int W,
                            int P, int s, int G, int dtype, void *stream) {
     const char *fn = "sapa_deform_av_forward";
+    trace_reset();
     if (int e = check_deform(fn, B, C, C, H, W, P, s, G, dtype)) return e;
     SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, out);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -324,6 +326,7 @@ int sapa_deform_av_forward(const void *attn, const void *value, const void *offs
 int sapa_deform_fused_forward(const void *query, const void *key, const void *value, const void *offset, void *out,
                               void *attn, int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream) {
     const char *fn = "sapa_deform_fused_forward";
+    trace_reset();
     if (int e = check_deform(fn, B, Cq, C, H, W, P, s, G, dtype)) return e;
     SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset);
     SAPA_CHECK_PTR(fn, out);
@@ -349,6 +352,7 @@ int sapa_deform_qk_backward(const void *grad_out, const void *query, const void 
                             void *grad_key, void *grad_offset, int B, int Cq, int H, int W, int P, int s, int G, int dtype,
                             void *stream) {
     const char *fn = "sapa_deform_qk_backward";
+    trace_reset();
     if (int e = check_deform(fn, B, Cq, Cq, H, W, P, s, G, dtype)) return e;
     SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, offset);
     SAPA_CHECK_PTR(fn, grad_query); SAPA_CHECK_PTR(fn, grad_key); SAPA_CHECK_PTR(fn, grad_offset);
@@ -371,6 +375,7 @@ int sapa_deform_av_backward(const void *grad_out, const void *attn, const void *
                             void *grad_value, void *grad_offset, int B, int C, int H, int W, int P, int s, int G, int dtype,
                             void *stream) {
     const char *fn = "sapa_deform_av_backward";
+    trace_reset();
     if (int e = check_deform(fn, B, C, C, H, W, P, s, G, dtype)) return e;
     SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset);
     SAPA_CHECK_PTR(fn, grad_attn); SAPA_CHECK_PTR(fn, grad_value); SAPA_CHECK_PTR(fn, grad_offset);

@@ -306,7 +306,7 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
 
 // ---------------------------------------------------------------------------------- host side
 // one host-side counter for all element types: they share g_next_tile / g_ctas_done
-static std::atomic<unsigned> g_next_sched_slot{0};
+static std::atomic<unsigned> g_next_sched_slot{0}, g_next_captured_slot{0};
 
 template <typename T>
 static int launch(const void *hi, const void *wt, void *out, int B, int C, int H, int W, cudaStream_t st) {
@@ -342,7 +342,7 @@ static int launch(const void *hi, const void *wt, void *out, int B, int C, int H
     }
     const long long resident = (long long)CTAS_PER_SM * sms;
     const unsigned grid = (unsigned)(nblocks < resident ? nblocks : resident);
-    a.sched_slot = (int)(g_next_sched_slot.fetch_add(1u) % SCHED_SLOTS);
+    a.sched_slot = next_sched_slot(g_next_sched_slot, g_next_captured_slot, st);
     sapa_gath_mma_kernel<T><<<grid, NT, G::SMEM_BYTES, st>>>(xmap, a);
     return check_launch(name);
 }
@@ -365,10 +365,20 @@ int launch_gath_mma(const void *hi, const void *wt, void *out, int B, int C, int
     return SAPA_ERR_UNSUPPORTED;
 }
 
-// 1 if a bounded mbarrier wait of the gather kernel ever gave up on the current device (synchronises the device).
+// 1 if a bounded mbarrier wait of the gather kernel gave up on the current device since the last query (synchronises
+// the device); reading a raised flag clears it and zeroes every scheduler pair (a CTA that gave up skipped the
+// last-CTA reset of its pair).
 int gath_wait_timeout_flag() {
     int flag = 0;
     if (cudaMemcpyFromSymbol(&flag, gmma::g_wait_timeout, sizeof(int)) != cudaSuccess) return -1;
+    if (flag != 0) {
+        static const unsigned zeros[tmau::SCHED_SLOTS] = {};
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(gmma::g_next_tile, zeros, sizeof(zeros)) != cudaSuccess ||
+            cudaMemcpyToSymbol(gmma::g_ctas_done, zeros, sizeof(zeros)) != cudaSuccess ||
+            cudaMemcpyToSymbol(gmma::g_wait_timeout, &zero, sizeof(int)) != cudaSuccess)
+            return -1;
+    }
     return flag;
 }
 

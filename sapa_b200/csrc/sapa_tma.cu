@@ -836,7 +836,7 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 // ---------------------------------------------------------------------------------- host side
 // one host-side counter for every kernel of this file: they all share g_next_tile / g_ctas_done, so two launches that
 // may be in flight together (different streams, different kernels) must never get the same slot
-static std::atomic<unsigned> g_next_sched_slot{0};
+static std::atomic<unsigned> g_next_sched_slot{0}, g_next_captured_slot{0};
 
 // Opts in to the dynamic shared memory, sizes the persistent grid, picks a scheduler slot and launches.
 template <typename Kernel, typename... Maps>
@@ -860,7 +860,7 @@ static int launch_persistent(Kernel kernel, const char *name, int threads, int s
     const long long resident = (long long)ctas_per_sm * sms;
     // persistent grid with dynamic tile claiming (static striding left SMs with 6 to 8 tiles instead of ~6.9)
     const unsigned grid = (unsigned)(nblocks < resident ? nblocks : resident);
-    a.sched_slot = (int)(g_next_sched_slot.fetch_add(1u) % SCHED_SLOTS);
+    a.sched_slot = next_sched_slot(g_next_sched_slot, g_next_captured_slot, st);
     kernel<<<grid, threads, smem, st>>>(maps..., a);
     return check_launch(name);
 }
@@ -900,7 +900,8 @@ int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void
         if (use_v) ok = ok && make_nchw_map(&vmap, v, W, rows, C, B, h16::BC, h16::VCH, HH, ty, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (!ok) {
-        set_error("sapa_tma_fused: cuTensorMapEncodeTiled rejected the tensor layout");
+        set_error("sapa_tma_fused (mode %d): cuTensorMapEncodeTiled rejected the tensor layout (CUresult %d)", mode,
+                  last_encode_result());
         return SAPA_ERR_UNSUPPORTED;
     }
     // maps a mode never touches still travel as kernel parameters: give them defined contents
@@ -914,7 +915,11 @@ int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void
     a.tiles_x = ceil_div(W, COLS);
     a.tiles_y = ceil_div(H, ROWS);
     constexpr int smem32 = NSTAGE * SLOT_BYTES + 2 * O_BYTES + 1024;
-    const char *n32 = "sapa_tma_fused_f32_kernel", *n16 = "sapa_tma_fused_16_kernel";
+    static const char *const names32[4] = {"sapa_tma_fused_f32_kernel<fwd>", "sapa_tma_fused_f32_kernel<bwd>",
+                                           "sapa_tma_fused_f32_kernel<sim>", "sapa_tma_fused_f32_kernel<agg>"};
+    static const char *const names16[4] = {"sapa_tma_fused_16_kernel<fwd>", "sapa_tma_fused_16_kernel<bwd>",
+                                           "sapa_tma_fused_16_kernel<sim>", "sapa_tma_fused_16_kernel<agg>"};
+    const char *n32 = names32[mode & 3], *n16 = names16[mode & 3];
 #define SAPA_TMA_LAUNCH32(M) launch_persistent(sapa_tma_fused_f32_kernel<M>, n32, NT, smem32, CTAS_PER_SM, a, st, qmap, kmap, vmap, omap)
 #define SAPA_TMA_LAUNCH16(T, M) \
     launch_persistent(sapa_tma_fused_16_kernel<T, M>, n16, h16::NT, h16::SMEM_BYTES, h16::CTAS_PER_SM, a, st, qmap, kmap, vmap)
@@ -944,10 +949,20 @@ int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void
 #undef SAPA_TMA_LAUNCH16
 }
 
-// 1 if a bounded mbarrier wait of the TMA kernel ever gave up on the current device (synchronises the device).
+// 1 if a bounded mbarrier wait of the TMA kernels gave up on the current device since the last query (synchronises the
+// device).  A CTA that gives up leaves without taking part in the last-CTA reset of its scheduler pair, so a raised
+// flag also means that pair may be dirty: reading a raised flag clears it and zeroes every scheduler pair.
 int tma_wait_timeout_flag() {
     int flag = 0;
     if (cudaMemcpyFromSymbol(&flag, tma::g_wait_timeout, sizeof(int)) != cudaSuccess) return -1;
+    if (flag != 0) {
+        static const unsigned zeros[tmau::SCHED_SLOTS] = {};
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(tma::g_next_tile, zeros, sizeof(zeros)) != cudaSuccess ||
+            cudaMemcpyToSymbol(tma::g_ctas_done, zeros, sizeof(zeros)) != cudaSuccess ||
+            cudaMemcpyToSymbol(tma::g_wait_timeout, &zero, sizeof(int)) != cudaSuccess)
+            return -1;
+    }
     return flag;
 }
 

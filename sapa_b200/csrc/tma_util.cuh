@@ -6,12 +6,15 @@
 
 #include <cuda.h>
 
+#include <atomic>
+
 namespace sapa {
 namespace tmau {
 
 constexpr unsigned TF32_MASK = 0xffffe000u;
 constexpr int WAIT_LIMIT = 1 << 22;        // bounded mbarrier wait (each try suspends for a while in hardware)
 constexpr int SCHED_SLOTS = 256;           // scheduler counter pairs per translation unit (one per launch in flight)
+constexpr int SCHED_EAGER = 192;           // pairs [0, SCHED_EAGER) serve ordinary launches, the rest launches under stream capture
 
 __device__ __forceinline__ void mbar_init(unsigned bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
@@ -101,6 +104,23 @@ inline EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Scheduler pair for the next launch on `st`.  A launch recorded into a CUDA graph keeps its pair for every replay,
+// so captured launches draw from a range of their own that the round-robin of ordinary launches never enters:
+// a replay can then never share a pair with an ordinary launch in flight on another stream.  (Two replays of graphs
+// that hold the same pair must not overlap on the GPU: replay one graph at a time per device, or on one stream.)
+inline int next_sched_slot(std::atomic<unsigned> &eager, std::atomic<unsigned> &captured, cudaStream_t st) {
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &status) == cudaSuccess && status != cudaStreamCaptureStatusNone)
+        return SCHED_EAGER + (int)(captured.fetch_add(1u) % (unsigned)(SCHED_SLOTS - SCHED_EAGER));
+    return (int)(eager.fetch_add(1u) % (unsigned)SCHED_EAGER);
+}
+
+// CUresult of the most recent cuTensorMapEncodeTiled call on this thread (for error messages)
+inline int &last_encode_result() {
+    static thread_local int code = 0;
+    return code;
+}
+
 // 4-D map over a dense NCHW tensor seen as (x, channel, y, image); box = box_w columns x box_ch channels x box_rows rows
 inline bool make_nchw_map(CUtensorMap *map, const void *base, int width, int height, int channels, int images, int box_w,
                           int box_ch, int box_rows, CUtensorMapDataType type, int esize, CUtensorMapSwizzle swizzle) {
@@ -111,8 +131,10 @@ inline bool make_nchw_map(CUtensorMap *map, const void *base, int width, int hei
                                    (cuuint64_t)channels * height * width * esize};
     const cuuint32_t box[4] = {(cuuint32_t)box_w, (cuuint32_t)box_ch, (cuuint32_t)box_rows, 1u};
     const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
-    return encode(map, type, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const CUresult r = encode(map, type, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    last_encode_result() = (int)r;
+    return r == CUDA_SUCCESS;
 }
 
 }  // namespace tmau

@@ -100,6 +100,7 @@ def fused_supported(kernel_size: int, scale_factor: int, dtype: torch.dtype) -> 
 
 def fused_forward_raw(query, key, value, kernel_size, scale_factor, want_attn, halo=(0, 0)):
     """Run the fused kernel; returns (out, attn or None).  ``halo`` = extra key/value rows (top, bottom)."""
+    query, key, value = _lib.aligned(query), _lib.aligned(key), _lib.aligned(value)
     n, d, hq, wq = query.shape
     c = value.size(1)
     h, w = hq // scale_factor, wq // scale_factor
