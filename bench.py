@@ -37,10 +37,22 @@ WORKLOADS = {
 DTYPES = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_HBM_GBS = 6650.0
+# one metric string for both arms (the GPU kernels and --impl reference): the ratio between the arms is only defined
+# when they measure the same thing on the same workload
+METRIC = "upsampled Mpix/s (SAPA-B forward: sim -> softmax -> atn)"
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one fused-forward launch at cfg2, from the ncu capture
-# summarised under profiles/ (null until a capture exists for that dtype).
-NCU_TRAFFIC_BYTES = {"f32": 75_536_128 + 83_335_168, "bf16": 37_796_096 + 16_380_672, "f16": None}   # profiles/fused_fwd_tma_cfg2_f32.md
+def ncu_traffic(dtype_name, kernels):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one fused-forward launch at cfg2, from the tracked summary of an
+    ncu capture (``profiles/fused_fwd_cfg2_traffic.json``); None when there is no capture for this element type or when the
+    capture was made with another kernel than the one that just ran."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "fused_fwd_cfg2_traffic.json")) as f:
+            entry = json.load(f).get(dtype_name)
+    except Exception:
+        return None
+    if not entry or entry.get("kernel") not in kernels:
+        return None
+    return int(entry["dram_bytes_read"]) + int(entry["dram_bytes_write"])
 
 
 def algorithmic_bytes(w, esize):
@@ -180,12 +192,12 @@ def run_reference(args, w):
     value = pix * args.steps / dt / 1e6
     threads = torch.get_num_threads() if which == "unfold" else c_oracle.num_threads()
     line = {
-        "impl": "reference", "metric": "upsampled Mpix/s (SAPA-B forward: sim -> softmax -> atn)", "value": value,
+        "impl": "reference", "metric": METRIC, "value": value,
         "unit": "Mpix/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": config_dict(args, w, note="CPU path of the reference (F.unfold/einsum formulation or scalar C port, "
-                                            "whichever is faster on this host)"),
+        "config": config_dict(args, w),
+        "note": "CPU path of the reference (F.unfold/einsum formulation or scalar C port, whichever is faster on this host)",
         "cpu_baseline": {"value": value, "unit": "Mpix/s", "cores": threads, "kind": "port",
                          "sample": f"each step = {nb} of {w['B']} images, float32, restatement '{which}'"},
         "e2e": {"value": value, "unit": "Mpix/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -194,15 +206,15 @@ def run_reference(args, w):
     print(json.dumps(line), flush=True)
 
 
-def config_dict(args, w, note=None):
-    c = {"workload": f"{args.workload}: SAPA-B fused forward, B={w['B']} per GPU" if w["scaling"] == "weak"
-         else f"{args.workload}: SAPA-B fused forward, B={w['B']} total ({w['shard']}-sharded)",
-         "B": w["B"], "C": w["C"], "d": w["d"], "low_res": [w["H"], w["W"]],
-         "high_res": [w["s"] * w["H"], w["s"] * w["W"]], "kernel_size": w["K"], "scale": w["s"],
-         "sharding": w["shard"]}
-    if note:
-        c["note"] = note
-    return c
+def config_dict(args, w):
+    """The workload, identical in both arms."""
+    return {"workload": f"{args.workload}: SAPA-B forward, B={w['B']} per GPU" if w["scaling"] == "weak"
+            else f"{args.workload}: SAPA-B forward, B={w['B']} total ({w['shard']}-sharded)",
+            "B": w["B"], "C": w["C"], "d": w["d"], "low_res": [w["H"], w["W"]],
+            "high_res": [w["s"] * w["H"], w["s"] * w["W"]], "kernel_size": w["K"], "scale": w["s"],
+            "sharding": w["shard"],
+            "l2": "inputs and outputs rotate over buffer sets larger than the 126 MB L2 (GPU arm); the CPU arm "
+                  "streams a batch far larger than the host caches"}
 
 
 # ------------------------------------------------------------------ GPU arm
@@ -355,6 +367,8 @@ def main():
         for i in range(rest):
             step(i)
 
+    step(0)
+    kernels_per_step = sapa_b200._lib.last_kernels()     # which kernel the entry point chose (host-side record)
     sampler = ClockSampler(local)
     sampler.start()
     run_steps(args.warmup)
@@ -565,16 +579,17 @@ def main():
     if rank == 0:
         peak, peak_kind = measured_peak()
         achieved = bytes_per_launch / (ms_per_step * 1e-3) / 1e9
-        traffic = NCU_TRAFFIC_BYTES.get(args.dtype) if args.workload == "cfg2" and world == 1 else None
+        traffic = ncu_traffic(args.dtype, kernels_per_step) if args.workload == "cfg2" and world == 1 else None
         line = {
-            "metric": "upsampled Mpix/s (SAPA-B fused forward: sim -> softmax -> atn)", "value": value, "unit": "Mpix/s",
+            "metric": METRIC, "value": value, "unit": "Mpix/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None, "dtype": args.dtype,
             "data": "synthetic",
-            "config": dict(config_dict(args, w), l2=f"{nsets} rotating input/output sets "
-                           f"({nsets * bytes_per_launch / 1e6:.0f} MB) > 126 MB L2",
-                           launch=(f"CUDA graph of {nsets} launches (one per buffer set), replayed" if graph is not None
-                                   else "one call per step from Python")),
+            "config": config_dict(args, w),
+            "timing": {"l2": f"{nsets} rotating input/output sets ({nsets * bytes_per_launch / 1e6:.0f} MB) > 126 MB L2",
+                       "launch": (f"CUDA graph of {nsets} launches (one per buffer set), replayed" if graph is not None
+                                  else "one call per step from Python"),
+                       "kernels_per_step": kernels_per_step},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "Mpix/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "how": "sapa_b200.sapa_fused on pinned host tensors, double-buffered "
