@@ -217,6 +217,62 @@ def config_dict(args, w):
                   "streams a batch far larger than the host caches"}
 
 
+# ------------------------------------------------------------------ the reference's own CUDA extensions (GPU baseline)
+
+def reference_cuda_ext_times(wl, device, time_path):
+    """Device time of the UNMODIFIED reference extensions (``oracle/_ref``: qk_ext, av_ext, dqk, dav) on the cfg2 /
+    cfg3 shapes in float32, called the way the reference's autograd Functions call them (sapa/sapa/sapa_func.py:24-26,
+    44-46, 69-71, 89-91; deformsapa/deformsapa/deform_func.py), including their zero-filled outputs.  Outside every timed
+    region of this library; reported next to it as the GPU baseline."""
+    path = os.path.join(ROOT, "oracle", "_ref")
+    names = ("qk_ext", "av_ext", "dqk", "dav")
+    if not all(os.path.exists(os.path.join(path, n + ".so")) for n in names):
+        return {"unavailable": "oracle/_ref is not built (python oracle/build_ref.py <reference checkout>)"}
+    import importlib
+    if path not in sys.path:
+        sys.path.append(path)
+    qk_ext, av_ext, dqk, dav = (importlib.import_module(n) for n in names)
+    B, d, C, H, W, K, s = wl["B"], wl["d"], wl["C"], wl["H"], wl["W"], wl["K"], wl["s"]
+    t = make_inputs(wl, torch.float32, device, seed=901)
+    q, k, v = t["q"], t["k"], t["v"]
+    go = torch.randn(B, C, s * H, s * W, device=device)
+    state = {}
+
+    def fwd():
+        sim = q.new_zeros((B, K * K, s * H, s * W))
+        qk_ext.forward(k, q, K, s, sim)
+        attn = torch.softmax(sim, dim=1)
+        out = v.new_zeros((B, C, s * H, s * W))
+        av_ext.forward(v, attn, K, s, out)
+        state["attn"] = attn
+
+    def bwd():
+        attn = state["attn"]
+        gv, ga = torch.zeros_like(v), torch.zeros_like(attn)
+        av_ext.backward(go, v, attn, K, s, gv, ga)
+        gs = attn * (ga - (attn * ga).sum(dim=1, keepdim=True))
+        gk, gq = torch.zeros_like(k), torch.zeros_like(q)
+        qk_ext.backward(gs, k, q, K, s, gk, gq)
+
+    G_, P_ = 4, 9
+    off = torch.randn(B, G_ * P_ * 2, s * H, s * W, device=device) * 0.5
+
+    def dfwd():
+        sim = q.new_zeros((B, G_, P_, s * H, s * W))
+        dqk.forward(q, k, off, P_, s, G_, sim)
+        attn = torch.softmax(sim, dim=2)
+        out = v.new_zeros((B, C, s * H, s * W))
+        dav.forward(attn, v, off, P_, s, G_, out)
+
+    pix = B * s * H * s * W
+    res = {}
+    for name, fn, steps in (("sapa_b_forward", fwd, 5), ("sapa_b_backward", bwd, 3), ("sapa_d_forward", dfwd, 3)):
+        ms = time_path(fn, steps, warm=2)
+        res[name] = {"ms": ms, "mpix_per_s": pix / (ms * 1e-3) / 1e6}
+    res["note"] = "unmodified reference kernels compiled for sm_100a, float32, legacy default stream, same shapes"
+    return res
+
+
 # ------------------------------------------------------------------ GPU arm
 
 def main():
@@ -446,8 +502,8 @@ def main():
     if world == 1 and not args.no_extra and args.workload == "cfg2":
         peak_gbs = measured_peak()[0]
 
-        def time_path(fn, steps):
-            for _ in range(5):
+        def time_path(fn, steps, warm=5):
+            for _ in range(warm):
                 fn()
             torch.cuda.synchronize()
             flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)   # L2 flushed between iterations
@@ -526,6 +582,7 @@ def main():
                                                  "ms = with the four 256-channel feature projections, mpix_per_s = upsampled pixels of "
                                                  "the three levels / ms_sapa_modules_only"}
         del feats, proj, ups, ys_fixed
+        paths["reference_cuda_ext"] = reference_cuda_ext_times(wl, device, time_path)
 
     # ---- end to end: public op, pinned host buffers in and out, copies inside the timed region ----
     e2e_steps = max(3, min(args.steps, 30))

@@ -49,10 +49,13 @@ extern "C" {
 
 /* Text of the last error raised on the calling thread ("" if none). */
 const char *sapa_last_error(void);
-/* Names of the kernels the most recent entry-point call on the calling thread launched, comma separated and in
- * launch order (e.g. "sapa_tma_fused_f32_kernel<bwd>,sapa_gath_mma_kernel,sapa_gath_mma_kernel"); "" before the
- * first call.  A host-side record (no device work): tests use it to assert which kernel a shape exercised, so that
- * a silent fall-back to a slower kernel cannot pass unnoticed.  No counterpart in the reference. */
+/* Names of the kernels the most recent entry-point call of the process launched (on whichever thread: PyTorch runs
+ * the backward of an autograd Function on a worker thread), comma separated and in launch order, e.g.
+ * "sapa_tma_fused_f32_kernel<bwd>,sapa_gath_mma_kernel,sapa_gath_mma_kernel"; "" before the first call.  A host-side
+ * record (no device work) meant for tests and diagnostics: they assert which kernel a shape exercised, so that a
+ * silent fall-back to a slower kernel cannot pass unnoticed.  With several threads calling at once it describes
+ * whichever call started last.  The returned string is valid until the calling thread asks again.
+ * No counterpart in the reference. */
 const char *sapa_last_kernels(void);
 /* ABI version of this header (bumped on any signature change). */
 int sapa_abi_version(void);
@@ -180,6 +183,18 @@ int sapa_deform_av_backward(const void *grad_out, const void *attn, const void *
 int sapa_deform_fused_forward(const void *query, const void *key, const void *value, const void *offset,
                               void *out, void *attn,
                               int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
+
+/* Gradients of sapa_deform_fused_forward with respect to query, key, value and offset from grad_out and the
+ * attention map it saved, in one kernel: the chain DeformAVBackward -> softmax backward over the points ->
+ * DeformQKBackward of the reference (deform_av_cuda_kernel.cu:230-292, sapa_deform.py:52, deform_qk_cuda_kernel.cu:
+ * 233-296) with the offsets and the attention read once and the two offset gradients added in the kernel (autograd
+ * adds them in the reference, because the offset feeds both ops).  grad_key and grad_value are scatter targets
+ * (float atomics): FLOAT32 buffers for SAPA_F16 / SAPA_BF16, like grad_query (FLOAT64 for SAPA_F64); grad_offset has the
+ * call's dtype.  All four are overwritten.  Supported: P <= 16; otherwise SAPA_ERR_UNSUPPORTED. */
+int sapa_deform_fused_backward(const void *grad_out, const void *query, const void *key, const void *value,
+                               const void *offset, const void *attn,
+                               void *grad_query, void *grad_key, void *grad_value, void *grad_offset,
+                               int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
 
 #ifdef __cplusplus
 }

@@ -36,6 +36,7 @@ _SIGNATURES = {
     "sapa_deform_av_forward": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_av_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_fused_forward": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_deform_fused_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
 }
 EXPORTS = sorted(list(_SIGNATURES) + ["sapa_last_error", "sapa_last_kernels", "sapa_abi_version", "sapa_fused_backward_workspace",
                                            "sapa_fused_backward_static_capacity", "sapa_wait_timeout_flags"])

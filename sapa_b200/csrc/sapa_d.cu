@@ -259,6 +259,100 @@ __global__ void deform_bwd_kernel(const T *__restrict__ top, const T *__restrict
     }
 }
 
+// ---------------------------------------------------------------------------------- backward, fused
+// Gradients of out = deform_av(softmax_p(deform_qk(q, k, off)), v, off) in ONE kernel.  One thread per (image, group,
+// high-res pixel) walks the P points three times, with the per-point values parked in shared memory:
+//   pass A (aggregation):  dA_p = sum_c dOut_c * val_c(p);  dV_c[corner] += w * dOut_c * A_p (atomic scatter);
+//                          offset gradient of the aggregation;
+//   pass B (softmax):      dS_p = A_p * (dA_p - sum_q A_q dA_q);
+//   pass C (similarity):   dQ_c = sum_p dS_p * val_c(p) (this thread is the only writer: plain stores, deterministic);
+//                          dKey_c[corner] += w * dS_p * Q_c (atomic scatter); offset gradient of the similarity.
+// The two offset gradients are added here, so the offsets and the attention map are read once and no intermediate
+// tensor ([B,G,P,sH,sW] attention gradient, logit gradient, second offset gradient) ever reaches HBM.
+template <typename T, int NTHR>
+__global__ void __launch_bounds__(NTHR)
+deform_fused_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ query, const T *__restrict__ key,
+                        const T *__restrict__ value, const T *__restrict__ offset, const T *__restrict__ attn,
+                        typename AccOf<T>::type *__restrict__ grad_query, typename AccOf<T>::type *__restrict__ grad_key,
+                        typename AccOf<T>::type *__restrict__ grad_value, T *__restrict__ grad_offset,
+                        int B, int Cq, int C, int H, int W, int P, int s, int G) {
+    using A = typename AccOf<T>::type;
+    __shared__ A s_h[MAXP][NTHR], s_w[MAXP][NTHR], s_d[MAXP][NTHR], s_gw[MAXP][NTHR], s_gh[MAXP][NTHR];
+    const int sH = s * H, sW = s * W, AC = G * P, gq = Cq / G, gc = C / G;
+    const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
+    const int tx = threadIdx.x;
+    const long long total = (long long)B * G * hi;
+    for (long long i = blockIdx.x * (long long)NTHR + tx; i < total; i += (long long)gridDim.x * NTHR) {
+        const size_t pix = (size_t)(i % hi);
+        const int qw = (int)(pix % sW), qh = (int)(pix / sW);
+        const int g = (int)((i / hi) % G);
+        const int b = (int)(i / (hi * G));
+        const size_t k0 = (size_t)b * AC + (size_t)g * P;              // first (group, point) plane of this thread
+        const T *ap = attn + k0 * hi + pix;
+        // ---- pass A
+        A dot = 0;
+        for (int p = 0; p < P; ++p) {
+            const A w = A(qw / s) + to_acc(offset[(k0 + p) * 2 * hi + pix]);
+            const A h = A(qh / s) + to_acc(offset[(k0 + p) * 2 * hi + hi + pix]);
+            Bilinear<A> bl;
+            bl.setup(h, w, H, W);
+            A dA = 0, g_w = 0, g_h = 0;
+            if (bl.inside) {
+                const A hh = A(1) - bl.lh, hw = A(1) - bl.lw;
+                const A a_p = to_acc(ap[(size_t)p * hi]);
+                const size_t ch0 = (size_t)b * C + (size_t)g * gc;
+                for (int c = 0; c < gc; ++c) {
+                    A v00, v01, v10, v11;
+                    bl.corners(value + (ch0 + c) * lo, v00, v01, v10, v11);
+                    const A t = to_acc(grad_out[(ch0 + c) * hi + pix]);
+                    dA += t * (bl.w00 * v00 + bl.w01 * v01 + bl.w10 * v10 + bl.w11 * v11);
+                    const A tw = t * a_p;
+                    A *gp = grad_value + (ch0 + c) * lo;
+                    if (bl.i00 >= 0) atomic_add(gp + bl.i00, bl.w00 * tw);
+                    if (bl.i01 >= 0) atomic_add(gp + bl.i01, bl.w01 * tw);
+                    if (bl.i10 >= 0) atomic_add(gp + bl.i10, bl.w10 * tw);
+                    if (bl.i11 >= 0) atomic_add(gp + bl.i11, bl.w11 * tw);
+                    g_w += (-hh * v00 + hh * v01 - bl.lh * v10 + bl.lh * v11) * tw;
+                    g_h += (-hw * v00 - bl.lw * v01 + hw * v10 + bl.lw * v11) * tw;
+                }
+                dot += a_p * dA;
+            }
+            s_h[p][tx] = h; s_w[p][tx] = w; s_d[p][tx] = dA; s_gw[p][tx] = g_w; s_gh[p][tx] = g_h;
+        }
+        // ---- pass B + C
+        const size_t qch0 = (size_t)b * Cq + (size_t)g * gq;
+        for (int p = 0; p < P; ++p) {
+            const A dS = to_acc(ap[(size_t)p * hi]) * (s_d[p][tx] - dot);
+            Bilinear<A> bl;
+            bl.setup(s_h[p][tx], s_w[p][tx], H, W);
+            A g_w = s_gw[p][tx], g_h = s_gh[p][tx];
+            const bool first = p == 0;
+            if (bl.inside) {
+                const A hh = A(1) - bl.lh, hw = A(1) - bl.lw;
+                for (int c = 0; c < gq; ++c) {
+                    A v00, v01, v10, v11;
+                    bl.corners(key + (qch0 + c) * lo, v00, v01, v10, v11);
+                    const A val = bl.w00 * v00 + bl.w01 * v01 + bl.w10 * v10 + bl.w11 * v11;
+                    A *qg = grad_query + (qch0 + c) * hi + pix;
+                    *qg = first ? dS * val : *qg + dS * val;
+                    const A tw = dS * to_acc(query[(qch0 + c) * hi + pix]);
+                    A *gp = grad_key + (qch0 + c) * lo;
+                    if (bl.i00 >= 0) atomic_add(gp + bl.i00, bl.w00 * tw);
+                    if (bl.i01 >= 0) atomic_add(gp + bl.i01, bl.w01 * tw);
+                    if (bl.i10 >= 0) atomic_add(gp + bl.i10, bl.w10 * tw);
+                    if (bl.i11 >= 0) atomic_add(gp + bl.i11, bl.w11 * tw);
+                    g_w += (-hh * v00 + hh * v01 - bl.lh * v10 + bl.lh * v11) * tw;
+                    g_h += (-hw * v00 - bl.lw * v01 + hw * v10 + bl.lw * v11) * tw;
+                }
+            } else if (first) {
+                for (int c = 0; c < gq; ++c) grad_query[(qch0 + c) * hi + pix] = A(0);
+            }
+            grad_offset[(k0 + p) * 2 * hi + pix] = from_acc<T>(g_w);
+            grad_offset[(k0 + p) * 2 * hi + hi + pix] = from_acc<T>(g_h);
+        }
+    }
+}
+
 static inline int grid_1d(long long total, int threads) {
     long long blocks = (total + threads - 1) / threads;
     const long long cap = 148LL * 64;
@@ -390,6 +484,35 @@ int sapa_deform_av_backward(const void *grad_out, const void *attn, const void *
             static_cast<const scalar_t *>(offset), nullptr, static_cast<scalar_t *>(grad_attn), static_cast<A *>(grad_value),
             static_cast<scalar_t *>(grad_offset), B, C, H, W, P, s, G);
         return check_launch("deform_bwd_kernel<av>");
+    });
+}
+
+int sapa_deform_fused_backward(const void *grad_out, const void *query, const void *key, const void *value,
+                               const void *offset, const void *attn, void *grad_query, void *grad_key, void *grad_value,
+                               void *grad_offset, int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype,
+                               void *stream) {
+    const char *fn = "sapa_deform_fused_backward";
+    trace_reset();
+    if (int e = check_deform(fn, B, Cq, C, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value);
+    SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, grad_offset);
+    SAPA_REQUIRE(grad_query != nullptr && grad_key != nullptr && grad_value != nullptr, SAPA_ERR_ARGUMENT,
+                 "%s: a gradient buffer is NULL", fn);
+    SAPA_REQUIRE(P <= MAXP, SAPA_ERR_UNSUPPORTED, "%s: no fused kernel for num_point=%d (use the separate ops)", fn, P);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t acc = dtype == SAPA_F64 ? 8 : 4;
+    if (int e = memset_async(grad_key, (size_t)B * Cq * H * W * acc, st, fn)) return e;
+    if (int e = memset_async(grad_value, (size_t)B * C * H * W * acc, st, fn)) return e;
+    return SAPA_DISPATCH_ALL(dtype, [&] {
+        using A = typename AccOf<scalar_t>::type;
+        constexpr int NTHR = sizeof(A) == 8 ? 64 : 128;      // five per-point arrays of MAXP x NTHR accumulators in shared memory
+        const long long total = (long long)B * G * s * H * s * W;
+        deform_fused_bwd_kernel<scalar_t, NTHR><<<grid_1d(total, NTHR), NTHR, 0, st>>>(
+            static_cast<const scalar_t *>(grad_out), static_cast<const scalar_t *>(query), static_cast<const scalar_t *>(key),
+            static_cast<const scalar_t *>(value), static_cast<const scalar_t *>(offset), static_cast<const scalar_t *>(attn),
+            static_cast<A *>(grad_query), static_cast<A *>(grad_key), static_cast<A *>(grad_value),
+            static_cast<scalar_t *>(grad_offset), B, Cq, C, H, W, P, s, G);
+        return check_launch("deform_fused_bwd_kernel");
     });
 }
 

@@ -125,8 +125,9 @@ def deform_fused_supported(num_point: int, dtype: torch.dtype) -> bool:
 
 class DeformSapaFusedFunction(Function):
     """deform_av(softmax_p(deform_qk(q, k, offset)), v, offset) as one op (``SAPADeform.attention``,
-    sapa_deform.py:51-53).  The backward chains the two separate backward kernels around the softmax
-    gradient and sums the two offset gradients (the offset feeds both ops)."""
+    sapa_deform.py:51-53).  The backward is one kernel too (``sapa_deform_fused_backward``): both scatter steps, the
+    softmax gradient over the points between them and the sum of the two offset gradients (the offset feeds both
+    ops)."""
 
     @staticmethod
     def forward(ctx, query, key, value, offset, num_point, scale_factor, groups):
@@ -162,9 +163,22 @@ class DeformSapaFusedFunction(Function):
         assert grad_output.is_cuda
         query, key, value, offset, attn = ctx.saved_tensors
         num_point, scale_factor, groups = ctx.cfg
-        grad_attn, grad_value, goff_av = deform_av_backward_raw(grad_output.contiguous(), attn, value, offset, num_point,
+        grad_output = grad_output.contiguous()
+        if deform_fused_supported(num_point, query.dtype) or (num_point <= 16 and query.dtype == torch.float64):
+            acc = _acc_dtype(query)
+            grad_query = torch.empty(query.shape, dtype=acc, device=query.device)
+            grad_key = torch.empty(key.shape, dtype=acc, device=key.device)
+            grad_value = torch.empty(value.shape, dtype=acc, device=value.device)
+            grad_offset = torch.empty_like(offset)
+            n, cq, h, w = key.shape
+            _lib.call("sapa_deform_fused_backward", query.device, grad_output, query, key, value, offset, attn, grad_query,
+                      grad_key, grad_value, grad_offset, n, cq, value.size(1), h, w, num_point, scale_factor, groups,
+                      _lib.dtype_code(query))
+            return (grad_query.to(query.dtype), grad_key.to(key.dtype), grad_value.to(value.dtype), grad_offset,
+                    None, None, None)
+        # more than 16 points: the separate backward kernels around the softmax gradient
+        grad_attn, grad_value, goff_av = deform_av_backward_raw(grad_output, attn, value, offset, num_point,
                                                                 scale_factor, groups)
-        # softmax backward over the point axis, in the accumulation precision
         a32, g32 = attn.float() if attn.dtype != torch.float64 else attn, grad_attn.float() if attn.dtype != torch.float64 else grad_attn
         grad_sim = (a32 * (g32 - (a32 * g32).sum(dim=2, keepdim=True))).to(attn.dtype)
         grad_query, grad_key, goff_qk = deform_qk_backward_raw(grad_sim, query, key, offset, num_point, scale_factor, groups)

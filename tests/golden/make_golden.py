@@ -1,11 +1,16 @@
 """Generate the golden vectors of ``tests/golden/*.npz`` from the REFERENCE's own code.
 
-Two producers, both running reference code only (nothing from this repository's kernels or oracle):
+Three producers, all running reference code only (nothing from this repository's kernels or oracle):
 
 ``python tests/golden/make_golden.py cpu  [--reference /path/to/sapa]``
     imports the reference's PyTorch check functions (sapa/sapa/forward_check.py:9-24,
     deformsapa/deformsapa/forward_check.py:6-40), evaluates them in float64 on seeded inputs and takes
     gradients by autograd through them.  Runs without a GPU.  Writes ``pyref_<case>.npz``.
+
+``python tests/golden/make_golden.py modules --reference /path/to/sapa``
+    instantiates the reference's ``SAPA`` / ``SAPADeform`` modules on the CPU (float64, their attention evaluated with
+    the same PyTorch check functions) and stores ``state_dict``, inputs, output and input gradients.  Writes
+    ``pyref_mod_<case>.npz``.
 
 ``python tests/golden/make_golden.py cuda --out DIR``
     loads ``pyref_<case>.npz`` and feeds the same inputs to the reference's compiled CUDA extensions
@@ -139,6 +144,68 @@ def make_cpu(reference: str):
     print("wrote cfg1")
 
 
+# ------------------------------------------------------------------ producer 1b: the reference's nn.Modules (CPU)
+
+# name -> (class, constructor kwargs, low-res size, offset-projection std); dim_y / dim_x are multiples of 32 (GroupNorm(32, .))
+MODULE_CASES = {
+    "mod_sapa": ("SAPA", dict(dim_y=64, dim_x=96, embedding_dim=16), (2, 6, 8), None),
+    "mod_sapa_nonorm": ("SAPA", dict(dim_y=32, embedding_dim=8, norm=False, qkv_bias=False), (1, 5, 12), None),
+    "mod_deform": ("SAPADeform", dict(dim_y=32, dim_x=64, embedding_dim=8, norm=True), (2, 6, 8), 0.3),
+    "mod_deform_low": ("SAPADeform", dict(dim_y=32, num_point=5, groups=2, embedding_dim=4, high_offset=False), (1, 4, 8), 0.3),
+}
+
+
+def make_modules(reference: str):
+    """Instantiates the reference's own ``SAPA`` / ``SAPADeform`` classes (sapa_base.py:7-49, sapa_deform.py:7-62) on
+    the CPU in float64, with ``sapa.qk/av`` and ``deformsapa.deform_qk/deform_av`` bound to the reference's PyTorch
+    check functions (its CUDA ops need a GPU), and stores state_dict, inputs, output and input gradients (computed in float64, stored as float32)."""
+    import importlib.util
+    import types
+    sys.path.insert(0, HERE)
+    import _ref_import
+    fb, fd = _ref_import.load(reference)
+    stub_b, stub_d = types.ModuleType("sapa"), types.ModuleType("deformsapa")
+    stub_b.qk, stub_b.av = fb.qk_pytorch, fb.av_pytorch
+    stub_d.deform_qk, stub_d.deform_av = fd.deform_qk_pytorch, fd.deform_av_pytorch
+    sys.modules["sapa"], sys.modules["deformsapa"] = stub_b, stub_d
+    classes = {}
+    for cls, rel in (("SAPA", "sapa_base.py"), ("SAPADeform", "sapa_deform.py")):
+        spec = importlib.util.spec_from_file_location("ref_" + cls, os.path.join(reference, rel))
+        m = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(m)
+        classes[cls] = getattr(m, cls)
+    for i, (name, (cls, kwargs, (B, H, W), off_std)) in enumerate(MODULE_CASES.items()):
+        torch.manual_seed(300 + i)
+        mod = classes[cls](**kwargs)
+        g = torch.Generator().manual_seed(400 + i)
+        with torch.no_grad():      # make every parameter non-trivial (the default affine GroupNorm is the identity)
+            for pname, p in mod.named_parameters():
+                if pname.startswith("norm"):
+                    p.add_(_randn(g, *p.shape, scale=0.3))
+                elif pname.endswith("bias"):
+                    p.copy_(_randn(g, *p.shape, scale=0.1))
+                elif pname.startswith("offset") and off_std is not None:
+                    p.copy_(_randn(g, *p.shape, scale=off_std / (p.shape[1] ** 0.5)))
+                else:
+                    p.copy_(_randn(g, *p.shape, scale=0.2))
+        s = mod.up_factor
+        dim_y, dim_x = kwargs["dim_y"], kwargs.get("dim_x") or kwargs["dim_y"]
+        x = _randn(g, B, dim_x, H, W)
+        y = _randn(g, B, dim_y, s * H, s * W)
+        grad_out = _randn(g, B, dim_x, s * H, s * W)
+        mod = mod.double()
+        xd, yd = x.double().requires_grad_(), y.double().requires_grad_()
+        out = mod(yd, xd)
+        gx, gy = torch.autograd.grad(out, (xd, yd), grad_out.double())
+        arrs = {"sd_" + k: v.detach().float().numpy() for k, v in mod.state_dict().items()}
+        arrs.update(in_x=x.numpy(), in_y=y.numpy(), in_grad_out=grad_out.numpy(),
+                    out_out=out.detach().float().numpy(), out_dx=gx.float().numpy(), out_dy=gy.float().numpy())
+        arrs["meta_class"] = np.asarray(cls)
+        arrs.update({"kw_" + k: np.asarray(v) for k, v in kwargs.items()})
+        np.savez_compressed(os.path.join(HERE, f"pyref_{name}.npz"), **arrs)
+        print("wrote", name)
+
+
 # ------------------------------------------------------------------ producer 2: reference CUDA extensions (GPU)
 
 def make_cuda(out_dir: str):
@@ -205,12 +272,17 @@ def make_cuda(out_dir: str):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", choices=["cpu", "cuda"])
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("which", choices=["cpu", "modules", "cuda"])
+    ap.add_argument("--reference", default=os.environ.get("SAPA_REFERENCE"),
+                    help="path of a tiny-smart/sapa checkout (or set SAPA_REFERENCE); needed by `cpu` and `modules`")
     ap.add_argument("--out", default=HERE)
     a = ap.parse_args()
+    if a.which in ("cpu", "modules") and not a.reference:
+        ap.error("--reference (or SAPA_REFERENCE) is required")
     if a.which == "cpu":
         make_cpu(a.reference)
+    elif a.which == "modules":
+        make_modules(a.reference)
     else:
         make_cuda(a.out)
 
