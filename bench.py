@@ -273,6 +273,69 @@ def reference_cuda_ext_times(wl, device, time_path):
     return res
 
 
+# ------------------------------------------------------------------ BASELINE config 5 (strong scaling over the ranks)
+
+def measure_config5(name, world, rank, device, dist, steps=10, warm=3):
+    """SAPA-B fused forward in bfloat16 on the whole of config 5a (B=64, 128^2 -> 256^2, batch-sharded) or 5b (one
+    1024^2 -> 2048^2 image in row slabs with a 2-row halo exchange) split over the ranks of this run; at N = 1 the whole
+    workload runs on one GPU.  Inputs (1.2 GB) and output (2.1 GB) are far larger than L2.  Device time by CUDA events
+    around `steps` steps between barriers, max over ranks."""
+    import sapa_b200
+    from sapa_b200 import sharding
+    w = dict(WORKLOADS[name])
+    K, s, dtype = w["K"], w["s"], torch.bfloat16
+    wl = dict(w)
+    if world > 1:
+        if w["shard"] == "batch":
+            sl = sharding.batch_slice(w["B"], world, rank)
+            wl["B"] = sl.stop - sl.start
+        else:
+            sl = sharding.row_slice(w["H"], world, rank)
+            wl["H"] = sl.stop - sl.start
+    gen = torch.Generator(device=device).manual_seed(50 + rank)       # 1.2 G elements: drawn on the device
+    shapes = dict(q=(wl["B"], wl["d"], s * wl["H"], s * wl["W"]), k=(wl["B"], wl["d"], wl["H"], wl["W"]),
+                  v=(wl["B"], wl["C"], wl["H"], wl["W"]))
+    t = {n: torch.randn(*sh, generator=gen, device=device, dtype=dtype) for n, sh in shapes.items()}
+    out = torch.empty((wl["B"], wl["C"], s * wl["H"], s * wl["W"]), dtype=dtype, device=device)
+    code = sapa_b200._lib.dtype_code(t["q"])
+    slab = None
+    if w["shard"] == "rows" and world > 1:
+        slab = sharding.RowSlab(wl["B"], wl["d"], wl["C"], wl["H"], wl["W"], dtype, device, K, s)
+        slab.key.copy_(t["k"])
+        slab.value.copy_(t["v"])
+
+    def step():
+        if slab is not None:
+            slab.forward(t["q"], out)
+        else:
+            sapa_b200._lib.call("sapa_fused_forward", device, t["q"], t["k"], t["v"], out, None, wl["B"], wl["d"], wl["C"],
+                                wl["H"], wl["W"], K, s, code)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warm):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        tt = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    pix = w["B"] * s * w["H"] * s * w["W"]
+    return {"mpix_per_s": pix / (ms * 1e-3) / 1e6, "ms_per_step": ms, "steps": steps, "dtype": "bf16", "n_gpus": world,
+            "sharding": w["shard"], "scaling": "strong",
+            "workload": f"{name}: B={w['B']}, C={w['C']}, d={w['d']}, {w['H']}x{w['W']} -> {s * w['H']}x{s * w['W']}"}
+
+
 # ------------------------------------------------------------------ GPU arm
 
 def main():
@@ -376,14 +439,17 @@ def main():
         sets.append(t)
 
     row_sharded = w["shard"] == "rows" and world > 1
-    r = (K - 1) // 2
+    if row_sharded:       # key / value live in padded slabs (sharding.RowSlab); only the halo rows move per step
+        for t in sets:
+            t["slab"] = sharding.RowSlab(wl["B"], wl["d"], wl["C"], wl["H"], wl["W"], dtype, device, K, s)
+            t["slab"].key.copy_(t["k"])
+            t["slab"].value.copy_(t["v"])
+            del t["k"], t["v"]
 
     def step(i):
         t = sets[i % nsets]
-        if row_sharded:   # halo exchange (NCCL send/recv over NVLink) + slab kernel, every step
-            kp, vp = sharding.exchange_row_halo([t["k"], t["v"]], r)
-            sapa_b200._lib.call("sapa_fused_forward_slab", device, t["q"], kp, vp, t["out"], None, wl["B"], wl["d"],
-                                wl["C"], wl["H"], wl["W"], r, r, K, s, sapa_b200._lib.dtype_code(t["q"]))
+        if row_sharded:   # halo exchange (NCCL send/recv over NVLink) under the interior rows, then the border bands
+            t["slab"].forward(t["q"], t["out"])
         else:
             sapa_b200._lib.call("sapa_fused_forward", device, t["q"], t["k"], t["v"], t["out"], None, wl["B"], wl["d"],
                                 wl["C"], wl["H"], wl["W"], K, s, sapa_b200._lib.dtype_code(t["q"]))
@@ -584,6 +650,12 @@ def main():
         del feats, proj, ups, ys_fixed
         paths["reference_cuda_ext"] = reference_cuda_ext_times(wl, device, time_path)
 
+    # ---- BASELINE config 5 at this N: batch-sharded and row-sharded bfloat16 forward, strong scaling ----
+    config5 = {}
+    if not args.no_extra and args.workload == "cfg2":
+        for name in ("cfg5a", "cfg5b"):
+            config5[name] = measure_config5(name, world, rank, device, dist)
+
     # ---- end to end: public op, pinned host buffers in and out, copies inside the timed region ----
     e2e_steps = max(3, min(args.steps, 30))
     host_in = [make_inputs(wl, dtype, device, seed=7 + i, pinned=True) for i in range(2)]
@@ -660,6 +732,8 @@ def main():
         if world == 1 and not args.no_extra and args.workload == "cfg2":
             line["other_dtypes"] = other
             line["other_paths"] = paths
+        if config5:
+            line["config5"] = config5
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(line), flush=True)

@@ -117,6 +117,15 @@ int sapa_fused_forward_slab(const void *query, const void *key, const void *valu
                             int B, int d, int C, int H, int W, int halo_top, int halo_bottom,
                             int K, int s, int dtype, void *stream);
 
+/* sapa_fused_forward_slab restricted to the band [row_begin, row_end) of the slab's H low-res rows (output rows
+ * 2*row_begin .. 2*row_end-1 of `out`, which is still the slab's whole [B,C,2H,2W] tensor, like `query`).  A sharded
+ * caller launches the rows that need no halo first and the border bands once the halos have arrived.  Partial bands
+ * need K = 5 and rows of 16 bytes (otherwise SAPA_ERR_UNSUPPORTED: call the band [0, H)).  No counterpart in the
+ * reference. */
+int sapa_fused_forward_slab_rows(const void *query, const void *key, const void *value, void *out, void *attn,
+                                 int B, int d, int C, int H, int W, int halo_top, int halo_bottom,
+                                 int row_begin, int row_end, int K, int s, int dtype, void *stream);
+
 /* Bytes of scratch sapa_fused_backward needs (grad of the logits, [B,K*K,sH,sW] elements of dtype). */
 size_t sapa_fused_backward_workspace(int B, int H, int W, int K, int s, int dtype);
 
@@ -136,7 +145,8 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
  *   - problems whose scratch (sapa_fused_backward_workspace) exceeds sapa_fused_backward_static_capacity()
  *     are refused with SAPA_ERR_WORKSPACE (B=8, 64x64 -> 128x128 in float32 needs 13.1 MB and fits);
  *   - the first call on each device looks the array's address up (cudaGetSymbolAddress, with that device
- *     current); make that first call before any stream capture begins;
+ *     current); make that first call before any stream capture begins.  The address is cached for the life of the
+ *     process: it assumes the device's primary context is never reset (cudaDeviceReset) while the library is loaded;
  *   - all calls share the one array, which keeps the previous call's contents (nothing needs clearing: it is
  *     fully rewritten before it is read), so two calls that overlap on the GPU (different streams) race.
  * Neither this function nor anything it calls allocates or frees memory. */

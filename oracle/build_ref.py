@@ -94,7 +94,8 @@ def build(reference: str, force: bool = False) -> list[str]:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("SAPA_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("SAPA_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"),
+                    help="path of a tiny-smart/sapa checkout (default: $SAPA_REFERENCE, else a `reference` folder next to this repository)")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     if not os.path.isdir(a.reference):

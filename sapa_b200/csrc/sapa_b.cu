@@ -538,7 +538,7 @@ static inline int grid_1d(long long total, int threads) {
 bool fused_mma_supported(int W, int dtype);
 bool fused_tma_supported(int W, int dtype);
 int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d, int C,
-                     int H, int W, int rows, int ytop0, int dtype, cudaStream_t st);
+                     int H, int W, int rows, int ytop0, int y_begin, int y_end, int dtype, cudaStream_t st);
 int launch_fused_mma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
                      int rows, int ytop0, int dtype, cudaStream_t st);
 
@@ -547,7 +547,7 @@ int cl_wait_timeout_flag();
 // float32 fused forward with channel-per-lane aggregation (sapa_cl.cu)
 bool fused_cl_supported(int W, int dtype);
 int launch_fused_cl(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
-                    int rows, int ytop0, cudaStream_t st);
+                    int rows, int ytop0, int y_begin, int y_end, cudaStream_t st);
 int gath_wait_timeout_flag();
 // tensor-core transposed aggregation (sapa_gath_mma.cu)
 bool gath_mma_supported(int W, int dtype);
@@ -610,7 +610,7 @@ static int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int
                    cudaStream_t st) {
     const bool al = all_aligned16(hi, lo, out);     // misaligned views take the scalar generic kernels
     if (al && K == 5 && s == 2 && fused_tma_supported(W, dtype)) {     // logit half of the TMA kernel
-        const int e = launch_fused_tma(2, hi, lo, nullptr, nullptr, out, nullptr, B, Cc, 0, H, W, H, 0, dtype, st);
+        const int e = launch_fused_tma(2, hi, lo, nullptr, nullptr, out, nullptr, B, Cc, 0, H, W, H, 0, 0, H, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
     if (al && tiled_supported(K, s, dtype)) {
@@ -631,7 +631,7 @@ static int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int
                    cudaStream_t st) {
     const bool al = all_aligned16(wt, lo, out);
     if (al && K == 5 && s == 2 && fused_tma_supported(W, dtype)) {     // aggregation half of the TMA kernel
-        const int e = launch_fused_tma(3, nullptr, nullptr, lo, out, const_cast<void *>(wt), nullptr, B, 0, Cc, H, W, H, 0, dtype, st);
+        const int e = launch_fused_tma(3, nullptr, nullptr, lo, out, const_cast<void *>(wt), nullptr, B, 0, Cc, H, W, H, 0, 0, H, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
     if (al && tiled_supported(K, s, dtype)) {
@@ -723,33 +723,47 @@ int sapa_av_backward(const void *grad_out, const void *attn, const void *value, 
     return run_gath(grad_out, attn, grad_value, B, C, H, W, K, s, dtype, st);                // dV = gath(dOut, A)
 }
 
-int sapa_fused_forward_slab(const void *query, const void *key, const void *value, void *out, void *attn, int B, int d,
-                            int C, int H, int W, int halo_top, int halo_bottom, int K, int s, int dtype, void *stream) {
+int sapa_fused_forward_slab_rows(const void *query, const void *key, const void *value, void *out, void *attn, int B, int d,
+                                 int C, int H, int W, int halo_top, int halo_bottom, int row_begin, int row_end, int K, int s,
+                                 int dtype, void *stream) {
     const char *fn = "sapa_fused_forward";
     trace_reset();
     if (int e = check_common(fn, B, d, H, W, K, s, dtype)) return e;
     SAPA_REQUIRE(C > 0, SAPA_ERR_ARGUMENT, "%s: C must be positive", fn);
     SAPA_REQUIRE(halo_top >= 0 && halo_bottom >= 0, SAPA_ERR_ARGUMENT, "%s: negative halo", fn);
+    SAPA_REQUIRE(0 <= row_begin && row_begin <= row_end && row_end <= H, SAPA_ERR_ARGUMENT,
+                 "%s: row band [%d, %d) is not inside [0, %d)", fn, row_begin, row_end, H);
     SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, out);
     SAPA_REQUIRE(all_aligned16(query, key, value, out) && (attn == nullptr || aligned16(attn)), SAPA_ERR_ALIGNMENT,
                  "%s: the fused kernels need 16-byte aligned tensors (copy the misaligned view, or use the separate ops)", fn);
     SAPA_REQUIRE(tiled_supported(K, s, dtype), SAPA_ERR_UNSUPPORTED,
                  "%s: no fused kernel for K=%d s=%d dtype=%d (use the separate ops)", fn, K, s, dtype);
+    if (row_begin == row_end) return SAPA_OK;
     TileArgs a{};
     a.hi = query; a.lo1 = key; a.lo2 = value; a.out_hi = out; a.out_slots = attn;
     a.B = B; a.C1 = d; a.C2 = C; a.H = H; a.W = W; a.rows = halo_top + H + halo_bottom; a.ytop0 = halo_top;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (K == 5 && fused_cl_supported(W, dtype)) {
-        const int e = launch_fused_cl(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, st);
+        const int e = launch_fused_cl(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, row_begin, row_end, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
     if (K == 5 && fused_tma_supported(W, dtype)) {
-        const int e = launch_fused_tma(0, query, key, value, out, attn, nullptr, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
+        const int e = launch_fused_tma(0, query, key, value, out, attn, nullptr, B, d, C, H, W, a.rows, a.ytop0, row_begin, row_end,
+                                       dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
+    // the remaining kernels (rows that are not 16-byte aligned, K = 3) always produce the whole slab
+    SAPA_REQUIRE(row_begin == 0 && row_end == H, SAPA_ERR_UNSUPPORTED,
+                 "%s: a partial row band needs K = 5 and rows of 16 bytes (call with the band [0, H) instead)", fn);
     if (K == 5 && fused_mma_supported(W, dtype))
         return launch_fused_mma(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, dtype, st);
     return SAPA_DISPATCH_FAST(dtype, [&] { return launch_tile_ks<scalar_t, MODE_FUSED>(a, K, st); });
+}
+
+int sapa_fused_forward_slab(const void *query, const void *key, const void *value, void *out, void *attn, int B, int d,
+                            int C, int H, int W, int halo_top, int halo_bottom, int K, int s, int dtype, void *stream) {
+    return sapa_fused_forward_slab_rows(query, key, value, out, attn, B, d, C, H, W, halo_top, halo_bottom, 0, H, K, s, dtype,
+                                        stream);
 }
 
 int sapa_fused_forward(const void *query, const void *key, const void *value, void *out, void *attn, int B, int d, int C,
@@ -783,7 +797,7 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
     if (al && K == 5 && s == 2 && fused_tma_supported(W, dtype)) {
         // tensor-core kernel (the fused forward's data flow with the softmax backward in the middle)
         const int e = launch_fused_tma(1, grad_out, value, key, grad_query, const_cast<void *>(attn), dS, B, C, d, H, W, H, 0,
-                                       dtype, st);
+                                       0, H, dtype, st);
         if (e != SAPA_OK && e != SAPA_ERR_UNSUPPORTED) return e;
         stage1_done = e == SAPA_OK;
     }

@@ -74,7 +74,8 @@ struct Args {
     void *ws;              // backward only: logit gradients [B, 25, 2H, 2W], written for the key-gradient gather
     int B, d, C, H, W;
     int rows, ytop0;
-    int tiles_x, tiles_y;
+    int y_begin, y_end;    // low-res output rows produced by this launch (a band of [0, H); the whole image except in row-slab calls)
+    int tiles_x, tiles_y;  // tiles_y covers the band only
     int sched_slot;        // index into g_next_tile / g_ctas_done
 };
 
@@ -135,7 +136,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             tile_ids[p_ti & 3] = claimed;
             if (claimed < 0) { exhausted = true; return; }
             p_x0 = (claimed % a.tiles_x) * COLS; claimed /= a.tiles_x;
-            p_y0 = (claimed % a.tiles_y) * ROWS; claimed /= a.tiles_y;
+            p_y0 = a.y_begin + (claimed % a.tiles_y) * ROWS; claimed /= a.tiles_y;
             p_n = claimed;
         }
         const unsigned slot = ring_addr + p_slot * SLOT_BYTES, bar = bar_addr + 8 * p_slot;
@@ -196,7 +197,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     const int bx = tile % a.tiles_x; tile /= a.tiles_x;
     const int by = tile % a.tiles_y; tile /= a.tiles_y;
     const int n = tile;
-    const int x0 = bx * COLS, y0 = by * ROWS;
+    const int x0 = bx * COLS, y0 = a.y_begin + by * ROWS;
     const int y = y0 + wrow;
 #pragma unroll
     for (int r = 0; r < 2; ++r)
@@ -204,7 +205,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         for (int dy = 0; dy < 5; ++dy) s[dy][2 * r] = s[dy][2 * r + 1] = 0.f;
 
     if (MODE == MODE_AGG) {      // the weights come from memory instead of from the logit stages
-        const bool pix_ok = y < a.H && x0 + 4 * h + l < a.W;
+        const bool pix_ok = y < a.y_end && x0 + 4 * h + l < a.W;
         const float *ap = static_cast<const float *>(a.attn) + (size_t)n * 25 * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h) + g;
 #pragma unroll
         for (int dy = 0; dy < 5; ++dy)
@@ -255,7 +256,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
             }
             if (it == nk - 1 && MODE == MODE_BWD) {
                 // softmax backward over the 25 window slots of each pixel (spread over the 4 lanes of a quad)
-                const bool pix_ok = y < a.H && x0 + 4 * h + l < a.W;
+                const bool pix_ok = y < a.y_end && x0 + 4 * h + l < a.W;
                 const size_t poff = (size_t)n * 25 * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h) + g;
                 const float *ap = static_cast<const float *>(a.attn) + poff;
                 float *wp = static_cast<float *>(a.ws) + poff;
@@ -317,7 +318,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 }
             }
             if (it == nk - 1 && (MODE == MODE_FWD || MODE == MODE_SIM)) {      // probabilities, or the raw logits of MODE_SIM
-                if (a.attn != nullptr && y < a.H && x0 + 4 * h + l < a.W) {
+                if (a.attn != nullptr && y < a.y_end && x0 + 4 * h + l < a.W) {
                     float *an = static_cast<float *>(a.attn) + (size_t)n * 25 * hi_plane + (size_t)(2 * y) * sW + 2 * (x0 + 4 * h) + g;
 #pragma unroll
                     for (int dy = 0; dy < 5; ++dy)
@@ -560,7 +561,7 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
                     return;
                 }
                 p_x0 = (claimed % a.tiles_x) * h16::COLS; claimed /= a.tiles_x;
-                p_y0 = (claimed % a.tiles_y) * ROWS; claimed /= a.tiles_y;
+                p_y0 = a.y_begin + (claimed % a.tiles_y) * ROWS; claimed /= a.tiles_y;
                 p_n = claimed;
             }
             const unsigned dst = ring_addr + p_slot * h16::SLOT_BYTES;
@@ -630,9 +631,9 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
             int tile = tile_ids[ti & 3];      // published by the producer before the barrier's phase completed
             if (tile < 0) break;
             x0 = (tile % a.tiles_x) * h16::COLS; tile /= a.tiles_x;
-            y = (tile % a.tiles_y) * ROWS + wrow; tile /= a.tiles_y;
+            y = a.y_begin + (tile % a.tiles_y) * ROWS + wrow; tile /= a.tiles_y;
             n = tile;
-            row_ok = y < Hlo; col_ok0 = x0 + t < Wlo; col_ok1 = x0 + 4 + t < Wlo;
+            row_ok = y < a.y_end; col_ok0 = x0 + t < Wlo; col_ok1 = x0 + 4 + t < Wlo;
             o_ptr = reinterpret_cast<unsigned *>(static_cast<T *>(a.out) + ((size_t)n * C + g) * hi_plane +
                                                  (size_t)(2 * y + r) * sW + 2 * x0 + 2 * t);
 #pragma unroll
@@ -881,7 +882,7 @@ bool fused_tma_supported(int W, int dtype) {
 //        (C = key channels), attn = saved attention map (input), ws = logit gradients (output), out = grad_query.
 // mode 2 (sim): attn (output) = sim(q, k); v, out unused, C ignored.   mode 3 (agg): out = atn(attn (input), v); q, k unused, d ignored.
 int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d, int C,
-                     int H, int W, int rows, int ytop0, int dtype, cudaStream_t st) {
+                     int H, int W, int rows, int ytop0, int y_begin, int y_end, int dtype, cudaStream_t st) {
     using namespace tma;
     if (mode == MODE_SIM) C = 0;
     if (mode == MODE_AGG) d = 0;
@@ -912,8 +913,9 @@ int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void
     a.out = out; a.attn = attn; a.ws = ws;
     a.B = B; a.d = d; a.C = C; a.H = H; a.W = W; a.rows = rows; a.ytop0 = ytop0;
     static_assert(h16::COLS == COLS, "both kernels use the same tile");
+    a.y_begin = y_begin; a.y_end = y_end;
     a.tiles_x = ceil_div(W, COLS);
-    a.tiles_y = ceil_div(H, ROWS);
+    a.tiles_y = ceil_div(y_end - y_begin, ROWS);
     constexpr int smem32 = NSTAGE * SLOT_BYTES + 2 * O_BYTES + 1024;
     static const char *const names32[4] = {"sapa_tma_fused_f32_kernel<fwd>", "sapa_tma_fused_f32_kernel<bwd>",
                                            "sapa_tma_fused_f32_kernel<sim>", "sapa_tma_fused_f32_kernel<agg>"};

@@ -4,9 +4,11 @@
   the ordinary ops on its slice of the batch (:func:`batch_slice`).
 * Row-slab sharding splits ONE image by low-res rows.  Output row ``ph`` reads key/value rows
   ``ph/s - r .. ph/s + r`` (r = (K-1)/2), so each rank needs r halo rows of key and value from each
-  neighbour; the image's own top and bottom are zero padding.  The halos travel as one point-to-point
-  message per neighbour (NCCL send/recv over NVLink on GPUs, gloo on CPU); the fused kernel then reads the
-  padded slab through ``sapa_fused_forward_slab``.  Nothing spins on the device.
+  neighbour; the image's own top and bottom are zero padding.  :class:`RowSlab` keeps a rank's key and value
+  resident in padded buffers (the halo rows are part of the buffer, so nothing is copied but the halo itself),
+  exchanges the 2 x r rows per step as one point-to-point message per neighbour (NCCL send/recv over NVLink on
+  GPUs, gloo on CPU) on a side stream, and meanwhile computes the rows that need no halo; the two border bands
+  follow when the halos have arrived.  Nothing spins on the device and no kernel reads another GPU's memory.
 
 The reference has no multi-device code; this module has no counterpart there.
 """
@@ -28,38 +30,45 @@ def row_slice(rows: int, world_size: int, rank: int) -> slice:
     return batch_slice(rows, world_size, rank)
 
 
-def exchange_row_halo(tensors, halo: int, group=None):
-    """Pad each local slab [B,C,Hl,W] to [B,C,halo+Hl+halo,W] with rows of the neighbouring ranks.
+def check_row_split(local_rows: int, halo: int, group=None) -> None:
+    """Every rank must own at least ``halo`` rows (a halo comes from the direct neighbour only).  The decision is
+    taken from the shares of ALL ranks, so that either every rank raises or none does: a rank that raised alone
+    would leave its neighbour waiting in a receive."""
+    world = dist.get_world_size(group)
+    if world == 1 or halo == 0:
+        return
+    shares = [None] * world
+    dist.all_gather_object(shares, int(local_rows), group=group)
+    if min(shares) < halo:
+        raise ValueError(f"row-slab sharding with a halo of {halo} rows needs at least {halo} rows on every rank, "
+                         f"got shares {shares}")
 
-    ``tensors`` is a list of slabs that share B, Hl, W, dtype and device (e.g. key and value); their halos are
-    packed into ONE message per neighbour.  Rank 0's top halo and the last rank's bottom halo stay zero,
-    which is the zero padding of the unsharded op.  Returns the list of padded slabs.
-    """
+
+def _exchange_into(padded, halo: int, group=None) -> None:
+    """Fill the halo rows of the padded slabs ``[B, C_i, halo + Hl + halo, W]`` in place: the top ``halo`` rows come
+    from the rank above, the bottom ones from the rank below; the halos of the first / last rank at the image border
+    are left as they are (zero).  The slabs' halos travel packed in ONE message per neighbour."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
-    first = tensors[0]
-    B, _, Hl, W = first.shape
-    if halo == 0:
-        return list(tensors)
-    if Hl < halo:
-        raise ValueError(f"each rank needs at least {halo} rows, got {Hl}")
-    chans = [t.size(1) for t in tensors]
+    if halo == 0 or world == 1:
+        return
+    first = padded[0]
+    B, _, Hp, W = first.shape
+    Hl = Hp - 2 * halo
+    chans = [t.size(1) for t in padded]
     ctot = sum(chans)
-
-    def pack(rows: slice) -> torch.Tensor:
-        return torch.cat([t[:, :, rows, :] for t in tensors], dim=1).contiguous()
-
-    padded = [t.new_zeros((B, c, Hl + 2 * halo, W)) for t, c in zip(tensors, chans)]
-    for p, t in zip(padded, tensors):
-        p[:, :, halo:halo + Hl, :] = t
-    ops, from_up, from_down = [], None, None
     to_global = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
+
+    def pack(lo: int) -> torch.Tensor:        # rows lo .. lo+halo of every slab, channels concatenated
+        return torch.cat([t[:, :, lo:lo + halo, :] for t in padded], dim=1).contiguous()
+
+    ops, from_up, from_down = [], None, None
     if rank > 0:
         from_up = first.new_empty((B, ctot, halo, W))
-        ops.append(dist.P2POp(dist.isend, pack(slice(0, halo)), to_global(rank - 1), group))
+        ops.append(dist.P2POp(dist.isend, pack(halo), to_global(rank - 1), group))
         ops.append(dist.P2POp(dist.irecv, from_up, to_global(rank - 1), group))
     if rank < world - 1:
         from_down = first.new_empty((B, ctot, halo, W))
-        ops.append(dist.P2POp(dist.isend, pack(slice(Hl - halo, Hl)), to_global(rank + 1), group))
+        ops.append(dist.P2POp(dist.isend, pack(Hl), to_global(rank + 1), group))
         ops.append(dist.P2POp(dist.irecv, from_down, to_global(rank + 1), group))
     if ops:
         for req in dist.batch_isend_irecv(ops):
@@ -71,20 +80,104 @@ def exchange_row_halo(tensors, halo: int, group=None):
         if from_down is not None:
             p[:, :, halo + Hl:, :] = from_down[:, c0:c0 + c]
         c0 += c
+
+
+def exchange_row_halo(tensors, halo: int, group=None):
+    """Pad each local slab [B,C,Hl,W] to [B,C,halo+Hl+halo,W] with rows of the neighbouring ranks.
+
+    ``tensors`` is a list of slabs that share B, Hl, W, dtype and device (e.g. key and value).  Rank 0's top halo
+    and the last rank's bottom halo stay zero, which is the zero padding of the unsharded op.  Returns the list of
+    padded slabs.  This convenience form copies the slabs; a caller that runs many steps keeps its key / value in a
+    :class:`RowSlab` instead, where only the halo rows move.
+    """
+    if halo == 0:
+        return list(tensors)
+    Hl = tensors[0].size(2)
+    check_row_split(Hl, halo, group)
+    padded = []
+    for t in tensors:
+        p = t.new_zeros((t.size(0), t.size(1), Hl + 2 * halo, t.size(3)))
+        p[:, :, halo:halo + Hl, :] = t
+        padded.append(p)
+    _exchange_into(padded, halo, group)
     return padded
 
 
+class RowSlab:
+    """One rank's share of a row-sharded fused SAPA-B forward.
+
+    ``key`` and ``value`` are views of the interior rows of padded buffers allocated once; whoever produces the key
+    and value of this rank writes them there (no copy per step).  :meth:`forward` then
+      1. starts the halo exchange on a side stream (pack 2 x r edge rows, one send + one receive per neighbour,
+         unpack into the halo rows of the padded buffers),
+      2. computes, on the caller's stream, the output rows whose windows stay inside the rank's own rows,
+      3. waits for the exchange and computes the top and bottom bands.
+    The result equals the matching rows of the unsharded ``sapa_fused`` bit for bit.  Forward only.
+    """
+
+    BAND = 4          # low-res rows per border band (a multiple of the kernels' tile heights, >= the halo)
+
+    def __init__(self, batch, channels_qk, channels_v, local_rows, width, dtype, device, kernel_size=5, scale_factor=2,
+                 group=None):
+        from .functions import fused_supported
+        if not fused_supported(kernel_size, scale_factor, dtype):
+            raise NotImplementedError("row-slab sharding needs the fused kernel (K in {3,5}, s = 2, f32/f16/bf16)")
+        self.K, self.s, self.group = kernel_size, scale_factor, group
+        self.halo = (kernel_size - 1) // 2
+        self.B, self.d, self.C, self.Hl, self.W = batch, channels_qk, channels_v, local_rows, width
+        check_row_split(local_rows, self.halo, group)
+        rows = local_rows + 2 * self.halo
+        self.key_padded = torch.zeros((batch, channels_qk, rows, width), dtype=dtype, device=device)
+        self.value_padded = torch.zeros((batch, channels_v, rows, width), dtype=dtype, device=device)
+        self.key = self.key_padded[:, :, self.halo:self.halo + local_rows, :]
+        self.value = self.value_padded[:, :, self.halo:self.halo + local_rows, :]
+        self._side = torch.cuda.Stream(device=device) if torch.device(device).type == "cuda" else None
+        self._halo_done = torch.cuda.Event() if self._side is not None else None
+
+    def _launch(self, query, out, row_begin, row_end):
+        from . import _lib
+        return _lib.call("sapa_fused_forward_slab_rows", out.device, query, self.key_padded, self.value_padded, out, None,
+                         self.B, self.d, self.C, self.Hl, self.W, self.halo, self.halo, row_begin, row_end, self.K, self.s,
+                         _lib.dtype_code(out), allow_unsupported=True)
+
+    def forward(self, query, out=None):
+        """``query`` [B, d, s*Hl, s*W] -> ``out`` [B, C, s*Hl, s*W] (allocated when not given)."""
+        from . import _lib
+        s, Hl = self.s, self.Hl
+        if out is None:
+            out = torch.empty((self.B, self.C, s * Hl, s * self.W), dtype=self.value_padded.dtype, device=query.device)
+        query = _lib.aligned(query.contiguous())
+        band = self.BAND
+        world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        overlap = self._side is not None and world > 1 and Hl > 2 * band
+        if overlap:
+            main = torch.cuda.current_stream(query.device)
+            self._side.wait_stream(main)                        # key / value of this step are complete
+            with torch.cuda.stream(self._side):
+                _exchange_into([self.key_padded, self.value_padded], self.halo, self.group)
+                self._halo_done.record(self._side)
+            status = self._launch(query, out, band, Hl - band)  # rows that read no halo, under the exchange
+            main.wait_event(self._halo_done)
+            if status == 0:
+                self._launch(query, out, 0, band)
+                self._launch(query, out, Hl - band, Hl)
+                return out
+        elif world > 1:
+            _exchange_into([self.key_padded, self.value_padded], self.halo, self.group)
+        status = self._launch(query, out, 0, Hl)               # one launch over the whole slab
+        if status != 0:
+            raise RuntimeError("sapa_fused_forward_slab_rows: " + _lib.lib().sapa_last_error().decode("utf-8", "replace"))
+        return out
+
+
 def sapa_fused_row_sharded(query, key, value, kernel_size=5, scale_factor=2, group=None):
-    """Fused SAPA-B forward on this rank's row slab.
+    """Fused SAPA-B forward on this rank's row slab (one-shot form: builds a :class:`RowSlab` and copies key / value in).
 
     ``query`` [B,d,s*Hl,s*W], ``key`` [B,d,Hl,W], ``value`` [B,C,Hl,W] hold the rank's rows of one larger
     image; the result equals the same rows of the unsharded ``sapa_fused``.  Forward only.
     """
-    from .functions import fused_forward_raw, fused_supported
-
-    if not fused_supported(kernel_size, scale_factor, value.dtype):
-        raise NotImplementedError("row-slab sharding needs the fused kernel (K in {3,5}, s = 2, f32/f16/bf16)")
-    halo = (kernel_size - 1) // 2
-    key_p, value_p = exchange_row_halo([key, value], halo, group)
-    out, _ = fused_forward_raw(query.contiguous(), key_p, value_p, kernel_size, scale_factor, False, halo=(halo, halo))
-    return out
+    slab = RowSlab(key.size(0), key.size(1), value.size(1), key.size(2), key.size(3), value.dtype, value.device,
+                   kernel_size, scale_factor, group)
+    slab.key.copy_(key)
+    slab.value.copy_(value)
+    return slab.forward(query)

@@ -48,3 +48,64 @@ def oracle():
     from oracle import c_oracle
     c_oracle.build()
     return c_oracle
+
+
+# ------------------------------------------------------------------ which kernel must serve which call
+# Mirrors the dispatch rules of csrc/sapa_b.cu so that a silent fall-back to a slower kernel fails a test instead of
+# passing on the fall-back's (correct) numbers.  W = low-res width; `wide` = 16-bit element types.
+
+def _tensor_map_rows(W, wide):
+    """Rows of every tensor on a 16-byte boundary: what the tensor-map (TMA) kernels need."""
+    return W % (8 if wide else 4) == 0
+
+
+def expected_fused_forward(K, s, W, dtype_name):
+    wide = dtype_name in ("f16", "bf16")
+    if s != 2 or K not in (3, 5) or dtype_name == "f64":
+        return None                                   # no fused kernel: the separate ops run
+    if K == 5 and dtype_name == "f32" and W % 4 == 0:
+        return ["sapa_cl_fused_f32_kernel"]
+    if K == 5 and wide and W % 8 == 0:
+        return ["sapa_tma_fused_16_kernel<fwd>"]
+    if K == 5 and (dtype_name == "f32" or W % 2 == 0):
+        return ["sapa_mma_fused_kernel"]
+    return ["sapa_tile_kernel<fused>"]
+
+
+def _gath(K, s, W, dtype_name):
+    wide = dtype_name in ("f16", "bf16")
+    if K == 5 and s == 2 and dtype_name != "f64" and W % (4 if wide else 2) == 0:
+        return "sapa_gath_mma_kernel"
+    if s == 2 and K in (3, 5) and dtype_name != "f64":
+        return "sapa_gath_kernel"
+    return "gath_generic_kernel"
+
+
+def expected_fused_backward(K, s, W, dtype_name):
+    wide = dtype_name in ("f16", "bf16")
+    tiled = s == 2 and K in (3, 5) and dtype_name != "f64"
+    if K == 5 and s == 2 and dtype_name != "f64" and _tensor_map_rows(W, wide):
+        stage1 = ["sapa_tma_fused_16_kernel<bwd>" if wide else "sapa_tma_fused_f32_kernel<bwd>"]
+    elif tiled:
+        stage1 = ["sapa_tile_kernel<bwd>"]
+    else:
+        stage1 = ["sim_generic_kernel", "softmax_bwd_generic_kernel", "agg_generic_kernel"]
+    return stage1 + [_gath(K, s, W, dtype_name)] * 2
+
+
+def expected_sim(K, s, W, dtype_name):
+    wide = dtype_name in ("f16", "bf16")
+    if K == 5 and s == 2 and dtype_name != "f64" and _tensor_map_rows(W, wide):
+        return ["sapa_tma_fused_16_kernel<sim>" if wide else "sapa_tma_fused_f32_kernel<sim>"]
+    if s == 2 and K in (3, 5) and dtype_name != "f64":
+        return ["sapa_tile_kernel<sim>"]
+    return ["sim_generic_kernel"]
+
+
+def expected_agg(K, s, W, dtype_name):
+    wide = dtype_name in ("f16", "bf16")
+    if K == 5 and s == 2 and dtype_name != "f64" and _tensor_map_rows(W, wide):
+        return ["sapa_tma_fused_16_kernel<agg>" if wide else "sapa_tma_fused_f32_kernel<agg>"]
+    if s == 2 and K in (3, 5) and dtype_name != "f64":
+        return ["sapa_tile_kernel<agg>"]
+    return ["agg_generic_kernel"]

@@ -1,0 +1,127 @@
+"""The benchmark configurations at FULL size against the CPU oracle (the oracle only ever sees the part of a
+configuration it can finish in seconds: one image of a batch, or a band of rows with the halo it depends on).
+
+config 2: B=8, C=256, d=64, 64^2 -> 128^2, 16-bit element types, forward and backward (float32 is in test_parity_gpu.py)
+config 3: SAPA-D, B=8, C=256, 4 groups x 9 points, offsets ~ N(0, 0.5^2): backward in float32 and forward in bfloat16
+config 5a: B=64, C=256, 128^2 -> 256^2, bfloat16 (the batch-sharded scaling workload)
+config 5b: B=1, C=256, 1024^2 -> 2048^2, bfloat16, as two row slabs with real halos (the row-sharded scaling workload);
+           its tensors pass 2^31 bytes, which is what the 64-bit indexing of the kernels is for.
+Tolerances: 1e-2 forward / 3e-2 backward for 16-bit types against the oracle on the rounded inputs, 2e-5 for float32
+gradients (norm-relative error max|a-b| / max|b|)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def sp():
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device")
+    import sapa_b200
+    return sapa_b200
+
+
+def host64(t):
+    return t.detach().double().cpu().numpy()
+
+
+def f32(t):
+    return t.detach().float().cpu().numpy()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_config2_16bit_full_size_vs_oracle(sp, oracle, dtype):
+    from sapa_b200 import _lib
+    B, d, C, H, W, K, s = 8, 64, 256, 64, 64, 5, 2
+    g = torch.Generator().manual_seed(1)
+    q, k, v, go = (torch.randn(*sh, generator=g).to(dtype) for sh in
+                   ((B, d, s * H, s * W), (B, d, H, W), (B, C, H, W), (B, C, s * H, s * W)))
+    want = oracle.sapa_forward(f32(q), f32(k), f32(v), K, s)                    # float32 oracle on the rounded inputs
+    wq, wk, wv = oracle.sapa_backward(f32(go), f32(q), f32(k), f32(v), K, s)
+    qd, kd, vd = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    out = sp.sapa_fused(qd, kd, vd, K, s)
+    torch.cuda.synchronize()
+    assert _lib.last_kernels() == ["sapa_tma_fused_16_kernel<fwd>"]
+    assert rel_err(host64(out), want) < 1e-2
+    fq, fk, fv = torch.autograd.grad(out, (qd, kd, vd), go.to(DEV))
+    torch.cuda.synchronize()
+    assert _lib.last_kernels() == ["sapa_tma_fused_16_kernel<bwd>", "sapa_gath_mma_kernel", "sapa_gath_mma_kernel"]
+    for got, ref in ((fq, wq), (fk, wk), (fv, wv)):
+        assert rel_err(host64(got), ref) < 3e-2
+
+
+def test_config3_full_size_backward_and_bf16_vs_oracle(sp, oracle):
+    B, Cq, C, H, W, P, G, s = 8, 64, 256, 64, 64, 9, 4, 2
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(B, Cq, s * H, s * W, generator=g)
+    k = torch.randn(B, Cq, H, W, generator=g)
+    v = torch.randn(B, C, H, W, generator=g)
+    off = torch.randn(B, G * P * 2, s * H, s * W, generator=g) * 0.5
+    go = torch.randn(B, C, s * H, s * W, generator=g)
+    img = 5
+    t = [x.to(DEV).requires_grad_() for x in (q, k, v, off)]
+    out = sp.deform_sapa_fused(*t, P, s, G)
+    grads = torch.autograd.grad(out, t, go.to(DEV))
+    one = [x[img:img + 1].numpy() for x in (q, k, v, off)]
+    want = oracle.deform_sapa_backward(go[img:img + 1].numpy(), *one, P, s, G)    # images are independent
+    for got, ref in zip(grads, want):
+        assert rel_err(host64(got[img:img + 1]), ref) < 2e-5
+    # bfloat16 forward and backward of the same image, against the float32 oracle on the rounded inputs
+    tb = [x[img:img + 1].to(torch.bfloat16) for x in (q, k, v, off)]
+    rb = [f32(x) for x in tb]
+    gob = go[img:img + 1].to(torch.bfloat16)
+    td = [x.to(DEV).requires_grad_() for x in tb]
+    outb = sp.deform_sapa_fused(*td, P, s, G)
+    assert rel_err(host64(outb), oracle.deform_sapa_forward(*rb, P, s, G)) < 1e-2
+    gb = torch.autograd.grad(outb, td, gob.to(DEV))
+    wb = oracle.deform_sapa_backward(f32(gob), *rb, P, s, G)
+    for got, ref in zip(gb, wb):
+        assert rel_err(host64(got), ref) < 3e-2
+
+
+def test_config5a_batch_of_64_bf16_one_image_vs_oracle(sp, oracle):
+    from sapa_b200.functions import fused_forward_raw
+    B, d, C, H, W, K, s = 64, 64, 256, 128, 128, 5, 2
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(B, d, s * H, s * W, generator=g, dtype=torch.bfloat16).to(DEV)
+    k = torch.randn(B, d, H, W, generator=g, dtype=torch.bfloat16).to(DEV)
+    v = torch.randn(B, C, H, W, generator=g, dtype=torch.bfloat16).to(DEV)
+    out, _ = fused_forward_raw(q, k, v, K, s, False)
+    for img in (0, 37, 63):      # first, one in the middle, last (the last image ends 3.2 GB into the output)
+        want = oracle.sapa_forward(f32(q[img:img + 1]), f32(k[img:img + 1]), f32(v[img:img + 1]), K, s)
+        assert rel_err(host64(out[img:img + 1]), want) < 1e-2
+
+
+def test_config5b_2048_square_row_slabs_with_real_halos_vs_oracle(sp, oracle):
+    """One 1024^2 -> 2048^2 image as two slabs of 512 low-res rows, each with the r = 2 halo rows of its neighbour (what
+    the halo exchange delivers) and zero rows at the image border; three bands of output rows are compared with the
+    oracle run on the rows they depend on: the top border, the slab boundary and the bottom border."""
+    from sapa_b200.functions import fused_forward_raw
+    B, d, C, H, W, K, s, r = 1, 64, 256, 1024, 1024, 5, 2, 2
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn(B, d, s * H, s * W, generator=g, dtype=torch.bfloat16).to(DEV)
+    k = torch.randn(B, d, H, W, generator=g, dtype=torch.bfloat16).to(DEV)
+    v = torch.randn(B, C, H, W, generator=g, dtype=torch.bfloat16).to(DEV)
+    kp, vp = (torch.nn.functional.pad(x, (0, 0, r, r)) for x in (k, v))
+    half = H // 2
+    slabs = []
+    for a in (0, half):
+        o, _ = fused_forward_raw(q[:, :, s * a:s * (a + half)].contiguous(), kp[:, :, a:a + half + 2 * r].contiguous(),
+                                 vp[:, :, a:a + half + 2 * r].contiguous(), K, s, False, halo=(r, r))
+        slabs.append(o)
+    out = torch.cat(slabs, dim=2)
+    assert out.shape == (B, C, s * H, s * W) and out.numel() * out.element_size() > 2 ** 31
+
+    def band(a, b):
+        lo, hi = max(a - r, 0), min(b + r, H)           # rows the band depends on (zero padding beyond the image)
+        want = oracle.sapa_forward(f32(q[:, :, s * lo:s * hi]), f32(k[:, :, lo:hi]), f32(v[:, :, lo:hi]), K, s)
+        return rel_err(host64(out[:, :, s * a:s * b]), want[:, :, s * (a - lo):s * (b - lo)])
+
+    assert band(0, 6) < 1e-2
+    assert band(half - 4, half + 4) < 1e-2
+    assert band(H - 6, H) < 1e-2

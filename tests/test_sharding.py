@@ -54,3 +54,66 @@ def test_row_halo_exchange_gloo(world, halo):
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, port, halo, ret), nprocs=world, join=True)
         assert dict(ret) == {r: True for r in range(world)}
+
+
+def _worker_uneven(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        H, W = 4, 5                                  # 4 rows over 3 ranks: shares (2, 1, 1), one below the halo of 2
+        rows = sharding.row_slice(H, world, rank)
+        key = torch.zeros(1, 2, rows.stop - rows.start, W)
+        try:
+            sharding.exchange_row_halo([key], 2)
+            ret[rank] = "no error"
+        except ValueError as exc:
+            ret[rank] = "ValueError" if "shares [2, 1, 1]" in str(exc) else str(exc)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_uneven_split_below_the_halo_raises_on_every_rank_together():
+    """A rank whose share is too small must not raise alone: its neighbour would wait in a receive for ever.  Every rank
+    sees every share and all raise the same error before any point-to-point operation is posted."""
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_uneven, args=(3, port, ret), nprocs=3, join=True)
+        assert dict(ret) == {0: "ValueError", 1: "ValueError", 2: "ValueError"}
+
+
+def _worker_resident(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(3)
+        H, W, r = 5 * world, 8, 2
+        key, value = torch.randn(1, 3, H, W, generator=g), torch.randn(1, 4, H, W, generator=g)
+        rows = sharding.row_slice(H, world, rank)
+        slab = sharding.RowSlab(1, 3, 4, rows.stop - rows.start, W, torch.float32, "cpu")
+        ok = True
+        for step in range(2):                        # the buffers are resident: a second step reuses them
+            slab.key.copy_(key[:, :, rows] + step)
+            slab.value.copy_(value[:, :, rows] - step)
+            sharding._exchange_into([slab.key_padded, slab.value_padded], r)
+            full_k = torch.nn.functional.pad(key + step, (0, 0, r, r))
+            full_v = torch.nn.functional.pad(value - step, (0, 0, r, r))
+            if rank == 0:                            # image border: the halo stays zero
+                full_k[:, :, :r], full_v[:, :, :r] = 0, 0
+            if rank == world - 1:
+                full_k[:, :, -r:], full_v[:, :, -r:] = 0, 0
+            ok = ok and torch.equal(slab.key_padded, full_k[:, :, rows.start:rows.stop + 2 * r]) and \
+                torch.equal(slab.value_padded, full_v[:, :, rows.start:rows.stop + 2 * r])
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_resident_slab_exchanges_only_its_halo_rows_in_place():
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_resident, args=(3, port, ret), nprocs=3, join=True)
+        assert dict(ret) == {0: True, 1: True, 2: True}
