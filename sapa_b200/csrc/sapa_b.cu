@@ -543,11 +543,6 @@ int launch_fused_mma(const void *q, const void *k, const void *v, void *out, voi
                      int rows, int ytop0, int dtype, cudaStream_t st);
 
 int tma_wait_timeout_flag();
-int cl_wait_timeout_flag();
-// float32 fused forward with channel-per-lane aggregation (sapa_cl.cu)
-bool fused_cl_supported(int W, int dtype);
-int launch_fused_cl(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
-                    int rows, int ytop0, int y_begin, int y_end, cudaStream_t st);
 int gath_wait_timeout_flag();
 // tensor-core transposed aggregation (sapa_gath_mma.cu)
 bool gath_mma_supported(int W, int dtype);
@@ -676,9 +671,9 @@ using namespace sapa;
 extern "C" {
 
 int sapa_wait_timeout_flags(void) {
-    const int a = tma_wait_timeout_flag(), b = gath_wait_timeout_flag(), c = cl_wait_timeout_flag();
-    if (a < 0 || b < 0 || c < 0) return -1;
-    return ((a || c) ? 1 : 0) | (b ? 2 : 0);
+    const int a = tma_wait_timeout_flag(), b = gath_wait_timeout_flag();
+    if (a < 0 || b < 0) return -1;
+    return (a ? 1 : 0) | (b ? 2 : 0);
 }
 
 int sapa_qk_forward(const void *query, const void *key, void *out, int B, int d, int H, int W, int K, int s, int dtype,
@@ -743,10 +738,6 @@ int sapa_fused_forward_slab_rows(const void *query, const void *key, const void 
     a.hi = query; a.lo1 = key; a.lo2 = value; a.out_hi = out; a.out_slots = attn;
     a.B = B; a.C1 = d; a.C2 = C; a.H = H; a.W = W; a.rows = halo_top + H + halo_bottom; a.ytop0 = halo_top;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (K == 5 && fused_cl_supported(W, dtype)) {
-        const int e = launch_fused_cl(query, key, value, out, attn, B, d, C, H, W, a.rows, a.ytop0, row_begin, row_end, st);
-        if (e != SAPA_ERR_UNSUPPORTED) return e;
-    }
     if (K == 5 && fused_tma_supported(W, dtype)) {
         const int e = launch_fused_tma(0, query, key, value, out, attn, nullptr, B, d, C, H, W, a.rows, a.ytop0, row_begin, row_end,
                                        dtype, st);

@@ -162,10 +162,15 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     const bool ok0 = (2 * t >= l) && (2 * t <= l + 4), ok1 = (2 * t + 1 >= l) && (2 * t + 1 <= l + 4);
 
     // swizzled byte offsets inside a 64-byte row
-    //   query A fragment: channel t (and t+4), pixel 8h+g        key B fragment: channel t (and t+4), cell g -> column 2+4h+g
+    //   query A fragment: channels ct, ct+2, pixel 8h+g          key B fragment: channels ct, ct+2, cell g -> column 2+4h+g
     //   value A fragment: channel g (and g+8), cells t and t+4 -> columns 2+4h+t, 6+4h+t
-    const int q_off0 = t * ROWB + swz(8 * h + g, t), q_off1 = (t + 4) * ROWB + swz(8 * h + g, t + 4);
-    const int k_off0 = t * ROWB + swz(2 + 4 * h + g, t), k_off1 = (t + 4) * ROWB + swz(2 + 4 * h + g, t + 4);
+    // k index t of a logit fragment reads channel ct = {0, 1, 4, 5}[t] of the 8-channel step and k index t + 4 reads ct + 2
+    // (the same permutation for query and key, so the sum over the 8 channels is unchanged): under the 64-byte swizzle
+    // channels 0, 1, 4, 5 start in four different 16-byte bank groups, which makes these loads conflict-free (with the
+    // identity order, channels t and t + 2 hit the same banks)
+    const int ct = (t & 1) + 4 * (t >> 1);
+    const int q_off0 = ct * ROWB + swz(8 * h + g, ct), q_off1 = (ct + 2) * ROWB + swz(8 * h + g, ct + 2);
+    const int k_off0 = ct * ROWB + swz(2 + 4 * h + g, ct), k_off1 = (ct + 2) * ROWB + swz(2 + 4 * h + g, ct + 2);
     const int v_offa = g * ROWB + swz(2 + 4 * h + t, g), v_offb = g * ROWB + swz(6 + 4 * h + t, g);
     //   output D fragment: channel g (and g+8), pixels 8h+2t, 8h+2t+1 of high-res rows 2*wrow, 2*wrow+1
     const int o_off = (2 * wrow) * (F_VCH * ROWB) + g * ROWB + swz(8 * h + 2 * t, g);

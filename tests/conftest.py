@@ -64,7 +64,7 @@ def expected_fused_forward(K, s, W, dtype_name):
     if s != 2 or K not in (3, 5) or dtype_name == "f64":
         return None                                   # no fused kernel: the separate ops run
     if K == 5 and dtype_name == "f32" and W % 4 == 0:
-        return ["sapa_cl_fused_f32_kernel"]
+        return ["sapa_tma_fused_f32_kernel<fwd>"]
     if K == 5 and wide and W % 8 == 0:
         return ["sapa_tma_fused_16_kernel<fwd>"]
     if K == 5 and (dtype_name == "f32" or W % 2 == 0):

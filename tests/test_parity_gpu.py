@@ -239,7 +239,7 @@ def test_sapa_b_config2_full_size_vs_oracle_float32(sp, oracle):
     wq, wk, wv = oracle.sapa_backward(go.numpy(), q.numpy(), k.numpy(), v.numpy(), K, s)
     qd, kd, vd = (t.to(DEV).requires_grad_() for t in (q, k, v))
     out = sp.sapa_fused(qd, kd, vd, K, s)
-    assert ran() == ["sapa_cl_fused_f32_kernel"]
+    assert ran() == ["sapa_tma_fused_f32_kernel<fwd>"]
     assert rel_err(host64(out), want) < 1e-5
     fq, fk, fv = grads(out, (qd, kd, vd), go.to(DEV))
     assert ran() == ["sapa_tma_fused_f32_kernel<bwd>", "sapa_gath_mma_kernel", "sapa_gath_mma_kernel"]
