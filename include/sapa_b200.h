@@ -194,6 +194,21 @@ int sapa_deform_fused_forward(const void *query, const void *key, const void *va
                               void *out, void *attn,
                               int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
 
+/* The same result as sapa_deform_fused_forward by way of the SAPA-B kernels, for s = 2 and float32: with offsets inside
+ * [-2, 2) low-res pixels every sampling point falls into the 5 x 5 window of the pixel's parent, so the logits are
+ * bilinear combinations of the dense 25-slot similarity of each group (one call of the sim kernel with the B x G
+ * groups as images) and the aggregation is the 5 x 5 aggregation with per-group window weights (one call of the agg
+ * kernel); a small kernel in between forms the softmax over the points and the window weights, and a last one adds
+ * the points that leave the window (any offset is handled, large ones just cost more).  About six times faster than
+ * sapa_deform_fused_forward at B=8, C=256, 64x64 -> 128x128.  `workspace` holds the dense similarity, the window
+ * weights and (when `attn` is NULL) the attention: sapa_deform_fused_forward_workspace() bytes (less the B*G*P*sH*sW
+ * elements of the attention when `attn` is given), 16-byte aligned, owned by the caller.  Other configurations return SAPA_ERR_UNSUPPORTED (the workspace query returns 0 for them).
+ * No counterpart in the reference. */
+size_t sapa_deform_fused_forward_workspace(int B, int H, int W, int P, int s, int G, int dtype);
+int sapa_deform_fused_forward_dense(const void *query, const void *key, const void *value, const void *offset,
+                                    void *out, void *attn, void *workspace, size_t workspace_bytes,
+                                    int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
+
 /* Gradients of sapa_deform_fused_forward with respect to query, key, value and offset from grad_out and the
  * attention map it saved, in one kernel: the chain DeformAVBackward -> softmax backward over the points ->
  * DeformQKBackward of the reference (deform_av_cuda_kernel.cu:230-292, sapa_deform.py:52, deform_qk_cuda_kernel.cu:

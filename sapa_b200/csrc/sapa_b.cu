@@ -600,8 +600,8 @@ static int check_common(const char *fn, int B, int C, int H, int W, int K, int s
 }
 
 
-// sim / agg / gath dispatchers (tiled when possible, else generic)
-static int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
+// sim / agg / gath dispatchers (tiled when possible, else generic); sim and agg also serve the dense path of SAPA-D
+int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
                    cudaStream_t st) {
     const bool al = all_aligned16(hi, lo, out);     // misaligned views take the scalar generic kernels
     if (al && K == 5 && s == 2 && fused_tma_supported(W, dtype)) {     // logit half of the TMA kernel
@@ -622,7 +622,7 @@ static int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int
     });
 }
 
-static int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
+int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
                    cudaStream_t st) {
     const bool al = all_aligned16(wt, lo, out);
     if (al && K == 5 && s == 2 && fused_tma_supported(W, dtype)) {     // aggregation half of the TMA kernel

@@ -259,6 +259,125 @@ __global__ void deform_bwd_kernel(const T *__restrict__ top, const T *__restrict
     }
 }
 
+// ---------------------------------------------------------------------------------- forward, dense-window path
+// With s = 2 and offsets inside [-2, 2) a sampling point's four corners lie in the 5 x 5 low-res window around the
+// pixel's parent - the window of SAPA-B.  Then both contractions of SAPA-D are SAPA-B contractions:
+//   logits:      sim_p = sum_c q_c * bilinear(key_c) = sum_corners w_corner * D[corner],  D[cell] = sum_c q_c key_c[cell]
+//                (D = the dense 25-slot similarity of the group's 16 channels, one call of the SAPA-B logit kernel with
+//                the B x G groups as images);
+//   aggregation: out_c = sum_p a_p * bilinear(value_c) = sum_cells Wd[cell] * value_c[cell],  Wd[cell] = sum of a_p * w_corner
+//                over the corners that land on the cell (one call of the SAPA-B aggregation kernel).
+// deform_window_kernel sits between the two: one thread per (image, group, pixel) turns D and the offsets into the
+// attention over the P points and the dense window weights Wd.  A point with a corner outside the window (|offset| >= 2)
+// is an "outlier": its logit is gathered directly here, it adds nothing to Wd, and deform_outlier_kernel adds its
+// contribution to the output afterwards (atomics; rare for learned offsets, but always correct).  Points outside the
+// image contribute exactly 0 to the logits and to the output, as in the reference.
+constexpr int WIN_THREADS = 128;
+
+template <typename A>
+__device__ __forceinline__ bool in_window(const Bilinear<A> &bl, A h, A w, int py, int px) {
+    const int h0 = (int)floor(h), w0 = (int)floor(w);
+    return bl.inside && h0 >= py - 2 && h0 + 1 <= py + 2 && w0 >= px - 2 && w0 + 1 <= px + 2;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(WIN_THREADS)
+deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ offset,
+                     const T *__restrict__ dense /* [B*G, 25, sH, sW] */, T *__restrict__ attn /* [B, G, P, sH, sW] */,
+                     T *__restrict__ window /* [B*G, 25, sH, sW] */, int B, int Cq, int H, int W, int P, int G) {
+    __shared__ float s_d[25][WIN_THREADS], s_w[25][WIN_THREADS];
+    const int sH = 2 * H, sW = 2 * W, gq = Cq / G;
+    const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
+    const int tx = threadIdx.x;
+    const long long total = (long long)B * G * hi;
+    for (long long i0 = (long long)blockIdx.x * WIN_THREADS; i0 < total; i0 += (long long)gridDim.x * WIN_THREADS) {
+        const long long i = i0 + tx;
+        const bool live = i < total;
+        const size_t pix = live ? (size_t)(i % hi) : 0;
+        const long long bg = live ? i / (long long)hi : 0;
+        const int g = (int)(bg % G), b = (int)(bg / G);
+        const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = qh >> 1, px = qw >> 1;
+        if (live) {
+#pragma unroll
+            for (int k = 0; k < 25; ++k) {
+                s_d[k][tx] = to_acc(dense[((size_t)bg * 25 + k) * hi + pix]);
+                s_w[k][tx] = 0.f;
+            }
+        }
+        float logit[MAXP], ph[MAXP], pw[MAXP];
+        float m = -INFINITY;
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p) {
+            logit[p] = 0.f; ph[p] = 0.f; pw[p] = 0.f;
+            if (live && p < P) {
+                const size_t o = ((size_t)(b * G + g) * P + p) * 2 * hi + pix;
+                const float w = float(px) + to_acc(offset[o]), h = float(py) + to_acc(offset[o + hi]);
+                ph[p] = h; pw[p] = w;
+                Bilinear<float> bl;
+                bl.setup(h, w, H, W);
+                float acc = 0.f;
+                if (in_window(bl, h, w, py, px)) {
+                    const int k00 = ((int)floorf(h) - py + 2) * 5 + ((int)floorf(w) - px + 2);
+                    acc = bl.w00 * s_d[k00][tx] + bl.w01 * s_d[k00 + 1][tx] + bl.w10 * s_d[k00 + 5][tx] + bl.w11 * s_d[k00 + 6][tx];
+                } else if (bl.inside) {       // outlier: gather the key directly
+                    const T *qp = query + ((size_t)b * Cq + (size_t)g * gq) * hi + pix;
+                    const T *kp = key + ((size_t)b * Cq + (size_t)g * gq) * lo;
+                    for (int c = 0; c < gq; ++c) acc += bl.sample(kp + (size_t)c * lo) * to_acc(qp[(size_t)c * hi]);
+                }
+                logit[p] = acc;
+                m = fmaxf(m, acc);
+            }
+        }
+        float z = 0.f;
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p)
+            if (p < P) { logit[p] = expf(logit[p] - m); z += logit[p]; }
+        const float inv = 1.f / z;
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p) {
+            if (live && p < P) {
+                const float a = logit[p] * inv;
+                attn[((size_t)(b * G + g) * P + p) * hi + pix] = from_acc<T>(a);
+                Bilinear<float> bl;
+                bl.setup(ph[p], pw[p], H, W);
+                if (in_window(bl, ph[p], pw[p], py, px)) {
+                    const int k00 = ((int)floorf(ph[p]) - py + 2) * 5 + ((int)floorf(pw[p]) - px + 2);
+                    s_w[k00][tx] += a * bl.w00; s_w[k00 + 1][tx] += a * bl.w01;
+                    s_w[k00 + 5][tx] += a * bl.w10; s_w[k00 + 6][tx] += a * bl.w11;
+                }
+            }
+        }
+        if (live) {
+#pragma unroll
+            for (int k = 0; k < 25; ++k) window[((size_t)bg * 25 + k) * hi + pix] = from_acc<T>(s_w[k][tx]);
+        }
+    }
+}
+
+// one thread per (image, group, point, pixel): adds a_p * bilinear(value_c) of the outlier points to the output
+template <typename T>
+__global__ void deform_outlier_kernel(const T *__restrict__ attn, const T *__restrict__ value, const T *__restrict__ offset,
+                                      T *__restrict__ out, int B, int C, int H, int W, int P, int G) {
+    const int sH = 2 * H, sW = 2 * W, gc = C / G;
+    const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
+    const long long total = (long long)B * G * P * hi;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const size_t pix = (size_t)(i % hi);
+        const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = qh >> 1, px = qw >> 1;
+        const long long k = i / (long long)hi;          // (b*G + g)*P + p
+        const float w = float(px) + to_acc(offset[(size_t)k * 2 * hi + pix]), h = float(py) + to_acc(offset[(size_t)k * 2 * hi + hi + pix]);
+        Bilinear<float> bl;
+        bl.setup(h, w, H, W);
+        if (!bl.inside || in_window(bl, h, w, py, px)) continue;
+        const long long bg = k / P;
+        const float a = to_acc(attn[i]);
+        const T *vp = value + (size_t)bg * gc * lo;
+        T *op = out + (size_t)bg * gc * hi + pix;
+        for (int c = 0; c < gc; ++c) atomicAdd(op + (size_t)c * hi, from_acc<T>(a * bl.sample(vp + (size_t)c * lo)));
+    }
+}
+
 // ---------------------------------------------------------------------------------- backward, fused
 // Gradients of out = deform_av(softmax_p(deform_qk(q, k, off)), v, off) in ONE kernel.  One thread per (image, group,
 // high-res pixel) walks the P points three times, with the per-point values parked in shared memory:
@@ -514,6 +633,62 @@ int sapa_deform_fused_backward(const void *grad_out, const void *query, const vo
             static_cast<scalar_t *>(grad_offset), B, Cq, C, H, W, P, s, G);
         return check_launch("deform_fused_bwd_kernel");
     });
+}
+
+}  // extern "C"
+
+// dispatchers of the SAPA-B logit and aggregation kernels (sapa_b.cu)
+namespace sapa {
+int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st);
+int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st);
+}
+
+extern "C" {
+
+size_t sapa_deform_fused_forward_workspace(int B, int H, int W, int P, int s, int G, int dtype) {
+    if (B <= 0 || H <= 0 || W <= 0 || P <= 0 || G <= 0 || s != 2 || dtype != SAPA_F32) return 0;
+    const size_t hi = (size_t)s * H * s * W;
+    return ((size_t)B * G * (25 + 25 + P) * hi) * dtype_size(dtype);
+}
+
+int sapa_deform_fused_forward_dense(const void *query, const void *key, const void *value, const void *offset, void *out,
+                                    void *attn, void *workspace, size_t workspace_bytes, int B, int Cq, int C, int H, int W,
+                                    int P, int s, int G, int dtype, void *stream) {
+    const char *fn = "sapa_deform_fused_forward_dense";
+    trace_reset();
+    if (int e = check_deform(fn, B, Cq, C, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset);
+    SAPA_CHECK_PTR(fn, out);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_fused_forward)", fn, MAXP);
+    const size_t hi = (size_t)s * H * s * W;
+    // the attention region of the workspace is only needed when the caller does not keep the attention itself
+    const size_t need = sapa_deform_fused_forward_workspace(B, H, W, P, s, G, dtype) -
+                        (attn != nullptr ? (size_t)B * G * P * hi * dtype_size(dtype) : 0);
+    SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
+                 "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float *dense = static_cast<float *>(workspace), *window = dense + (size_t)B * G * 25 * hi;
+    float *attn_buf = attn != nullptr ? static_cast<float *>(attn) : window + (size_t)B * G * 25 * hi;
+    // 1. dense 25-slot similarity of every group: the B x G groups are images of Cq / G channels
+    if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
+    // 2. attention over the points and dense window weights
+    {
+        const long long total = (long long)B * G * hi;
+        deform_window_kernel<float><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+            static_cast<const float *>(query), static_cast<const float *>(key), static_cast<const float *>(offset), dense,
+            attn_buf, window, B, Cq, H, W, P, G);
+        if (int e = check_launch("deform_window_kernel")) return e;
+    }
+    // 3. aggregation of every group's channels over the window
+    if (int e = run_agg(window, value, out, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
+    // 4. the points whose corners leave the window
+    {
+        const long long total = (long long)B * G * P * hi;
+        deform_outlier_kernel<float><<<grid_1d(total, 256), 256, 0, st>>>(
+            attn_buf, static_cast<const float *>(value), static_cast<const float *>(offset), static_cast<float *>(out), B, C, H, W, P, G);
+        return check_launch("deform_outlier_kernel");
+    }
 }
 
 }  // extern "C"

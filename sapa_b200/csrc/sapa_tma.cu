@@ -32,29 +32,16 @@ using namespace tmau;
 constexpr int ROWS = 4, COLS = 8;          // low-res tile of a CTA
 constexpr int HH = ROWS + 4;               // halo rows
 constexpr int HC = 16;                     // halo columns x0-4 .. x0+11 = one 64-byte row
-// float32 kernel: channels per stage and resident CTAs per SM are build-time tuning knobs
-#ifndef SAPA_F32_KCH
-#define SAPA_F32_KCH 16
-#endif
-#ifndef SAPA_F32_VCH
-#define SAPA_F32_VCH 32
-#endif
-#ifndef SAPA_F32_CTAS
-#define SAPA_F32_CTAS 2
-#endif
-constexpr int F_KCH = SAPA_F32_KCH;        // key / query channels per stage (multiple of 8)
-constexpr int F_VCH = SAPA_F32_VCH;        // value channels per stage (multiple of 16)
-#ifndef SAPA_F32_NSTAGE
-#define SAPA_F32_NSTAGE 4
-#endif
-constexpr int NSTAGE = SAPA_F32_NSTAGE;    // ring slots of 16 KB
+constexpr int F_KCH = 16;                  // key / query channels per stage (multiple of 8)
+constexpr int F_VCH = 32;                  // value channels per stage (multiple of 16)
+constexpr int NSTAGE = 4;                  // ring slots of 16 KB
 constexpr int NT = 2 * ROWS * 32;          // 8 warps: (row, 4-pixel half)
 constexpr int ROWB = HC * 4;               // 64 bytes
 constexpr int K_BYTES = HH * F_KCH * ROWB;   // 8192: key box [8 rows][16 ch][16 cols]
 constexpr int V_BYTES = HH * F_VCH * ROWB;   // 16384
 constexpr int SLOT_BYTES = V_BYTES > 2 * K_BYTES ? V_BYTES : 2 * K_BYTES;   // a key stage = key box + query box of K_BYTES each
 constexpr int O_BYTES = 2 * ROWS * F_VCH * ROWB;   // 16384: output box [8 hi rows][32 ch][16 hi cols], double-buffered
-constexpr int CTAS_PER_SM = SAPA_F32_CTAS;  // resident CTAs per SM the register budget is tuned for
+constexpr int CTAS_PER_SM = 2;             // resident CTAs per SM the register budget is tuned for
 
 __device__ int g_wait_timeout = 0;         // set when a bounded wait gave up (read by tma_wait_timeout_flag)
 // Dynamic tile scheduler of the persistent grid.  Every launch uses one of SCHED_SLOTS counter pairs (chosen
@@ -373,8 +360,6 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
                 for (int b = 0; b < F_VCH / 16; ++b)
 #pragma unroll
                     for (int r = 0; r < 2; ++r) mma_tf32(acc[b][r], ah[b], phi[r][dy][0], phi[r][dy][1]);
-                // (Folding the two correction terms into one bfloat16 m16n8k16 MMA was tried: the four extra
-                // float -> bfloat16 packs per fragment cost as much as the MMA they save, and the error grew to 4e-6.)
 #pragma unroll
                 for (int b = 0; b < F_VCH / 16; ++b)
 #pragma unroll
@@ -435,24 +420,12 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
 //     warp) and refilled by lane 0 of warp 0 whenever it finds one free; outputs go from registers to global memory.
 namespace h16 {
 constexpr int COLS = 8;                         // low-res columns of a CTA tile
-#ifndef SAPA_H16_NSTAGE
-#define SAPA_H16_NSTAGE 4                       // ring slots of 20 KB (a build-time tuning knob; 4 measured 2 % faster than 5)
-#endif
-constexpr int NSTAGE = SAPA_H16_NSTAGE;
+constexpr int NSTAGE = 4;                       // ring slots of 20 KB
 constexpr int NW = 2 * ROWS;                    // 8 warps
 constexpr int NT = NW * 32;
-#ifndef SAPA_H16_CTAS
-#define SAPA_H16_CTAS 2
-#endif
-constexpr int CTAS_PER_SM = SAPA_H16_CTAS;      // resident CTAs per SM the register budget is tuned for
-#ifndef SAPA_H16_KCH
-#define SAPA_H16_KCH 32                           // 2 k steps per stage: half as many logit stages (measured 4 % / 9 % faster
-#endif                                           // forward / backward than 16)
-constexpr int KCH = SAPA_H16_KCH;                // key / query channels per stage (k steps of 16 for m16n8k16)
-#ifndef SAPA_H16_VCH
-#define SAPA_H16_VCH 32
-#endif
-constexpr int VCH = SAPA_H16_VCH;                // value channels per stage (multiple of 16)
+constexpr int CTAS_PER_SM = 2;                  // resident CTAs per SM the register budget is tuned for
+constexpr int KCH = 32;                         // key / query channels per stage (k steps of 16 for m16n8k16)
+constexpr int VCH = 32;                         // value channels per stage (multiple of 16)
 constexpr int BC = 24;                          // key / value box columns
 constexpr int KROW = BC * 2;                    // 48 bytes
 constexpr int QROW = 32;                        // 16 high-res pixels
@@ -593,8 +566,8 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
     const int q_off = h16::K_BYTES + (2 * wrow + r) * (KCH * QROW) + row_a * QROW + (((chunk_a ^ (row_a >> 2)) & 1) << 4);
     // key (A of the logits, transposed): m0..m3 = (ch 0-7, col 0-7) (ch 0-7, col 8-15) (ch 8-15, col 0-7) (ch 8-15, col 8-15),
     // then m4, m5 = (ch 0-7, col 16-23) (ch 8-15, col 16-23).  The right pixel group's fragment is assembled from
-    // m1, m4, m3, m5: loading the shared middle columns a second time instead was measured slower (the kernel is
-    // short of shared-memory bandwidth, not of issue slots).
+    // m1, m4, m3, m5 (the shared middle columns are loaded once: the kernel is short of shared-memory bandwidth, not of
+    // issue slots).
     const int k_off = wrow * (KCH * KROW) + row_t * KROW + chunk_t * 16;
     const int k_off2 = wrow * (KCH * KROW) + row_a * KROW + 32;
     // value (A of the aggregation): m0..m3 = (ch 0-7, col 0-7) (ch 8-15, col 0-7) (ch 0-7, col 8-15) (ch 8-15, col 8-15),

@@ -148,8 +148,17 @@ class DeformSapaFusedFunction(Function):
         if deform_fused_supported(num_point, query.dtype):
             out = torch.empty((n, c, hq, wq), dtype=value.dtype, device=value.device)
             attn = torch.empty((n, groups, num_point, hq, wq), dtype=value.dtype, device=value.device) if need_grad else None
-            _lib.call("sapa_deform_fused_forward", value.device, query, key, value, offset, out, attn, n, cq, c, h, w,
-                      num_point, scale_factor, groups, _lib.dtype_code(value))
+            code = _lib.dtype_code(value)
+            nbytes = int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, code))
+            if nbytes:       # s = 2, float32: the dense-window path on the SAPA-B kernels
+                if attn is not None:
+                    nbytes -= attn.numel() * attn.element_size()      # the attention goes to its own tensor
+                workspace = torch.empty(nbytes, dtype=torch.uint8, device=value.device)
+                _lib.call("sapa_deform_fused_forward_dense", value.device, query, key, value, offset, out, attn, workspace,
+                          workspace.numel(), n, cq, c, h, w, num_point, scale_factor, groups, code)
+            else:
+                _lib.call("sapa_deform_fused_forward", value.device, query, key, value, offset, out, attn, n, cq, c, h, w,
+                          num_point, scale_factor, groups, code)
         else:
             attn = torch.softmax(DeformQKFunction.apply(query.detach(), key.detach(), offset.detach(), num_point,
                                                         scale_factor, groups), dim=2)
