@@ -198,11 +198,12 @@ int sapa_deform_fused_forward(const void *query, const void *key, const void *va
  * [-2, 2) low-res pixels every sampling point falls into the 5 x 5 window of the pixel's parent, so the logits are
  * bilinear combinations of the dense 25-slot similarity of each group (one call of the sim kernel with the B x G
  * groups as images) and the aggregation is the 5 x 5 aggregation with per-group window weights (one call of the agg
- * kernel); a small kernel in between forms the softmax over the points and the window weights, and a last one adds
- * the points that leave the window (any offset is handled, large ones just cost more).  About six times faster than
- * sapa_deform_fused_forward at B=8, C=256, 64x64 -> 128x128.  `workspace` holds the dense similarity, the window
- * weights and (when `attn` is NULL) the attention: sapa_deform_fused_forward_workspace() bytes (less the B*G*P*sH*sW
- * elements of the attention when `attn` is given), 16-byte aligned, owned by the caller.  Other configurations return SAPA_ERR_UNSUPPORTED (the workspace query returns 0 for them).
+ * kernel); a small kernel in between forms the softmax over the points and the window weights and lists the points
+ * that leave the window, and a last one adds the listed points to the output with atomics (any offset is handled,
+ * large ones just cost more).  Several times faster than sapa_deform_fused_forward at B=8, C=256, 64x64 -> 128x128.
+ * `workspace` holds the dense similarity, the window weights and the list: sapa_deform_fused_forward_workspace()
+ * bytes, 16-byte aligned, owned by the caller.  `attn` (optional) receives the attention over the points.  Other
+ * configurations return SAPA_ERR_UNSUPPORTED (the workspace query returns 0 for them).
  * No counterpart in the reference. */
 size_t sapa_deform_fused_forward_workspace(int B, int H, int W, int P, int s, int G, int dtype);
 int sapa_deform_fused_forward_dense(const void *query, const void *key, const void *value, const void *offset,

@@ -268,58 +268,94 @@ __global__ void deform_bwd_kernel(const T *__restrict__ top, const T *__restrict
 //   aggregation: out_c = sum_p a_p * bilinear(value_c) = sum_cells Wd[cell] * value_c[cell],  Wd[cell] = sum of a_p * w_corner
 //                over the corners that land on the cell (one call of the SAPA-B aggregation kernel).
 // deform_window_kernel sits between the two: one thread per (image, group, pixel) turns D and the offsets into the
-// attention over the P points and the dense window weights Wd.  A point with a corner outside the window (|offset| >= 2)
-// is an "outlier": its logit is gathered directly here, it adds nothing to Wd, and deform_outlier_kernel adds its
-// contribution to the output afterwards (atomics; rare for learned offsets, but always correct).  Points outside the
-// image contribute exactly 0 to the logits and to the output, as in the reference.
+// attention over the P points and the dense window weights Wd, all in registers (the bilinear weights of a point are
+// written as a 5-vector per axis with two non-zero entries, so that no register array is indexed dynamically).  A point
+// with a corner outside the window (|offset| >= 2) is an "outlier": its logit is gathered directly here, it adds
+// nothing to Wd, and it is appended to a list from which deform_outlier_kernel adds its contribution to the output
+// afterwards (atomics; rare for learned offsets, but always correct).  Points outside the image contribute exactly 0 to
+// the logits and to the output, as in the reference.
 constexpr int WIN_THREADS = 128;
 
-template <typename A>
-__device__ __forceinline__ bool in_window(const Bilinear<A> &bl, A h, A w, int py, int px) {
-    const int h0 = (int)floor(h), w0 = (int)floor(w);
-    return bl.inside && h0 >= py - 2 && h0 + 1 <= py + 2 && w0 >= px - 2 && w0 + 1 <= px + 2;
-}
+struct OutlierTap {
+    unsigned int k;      // (image * G + group) * P + point
+    unsigned int pix;    // high-res pixel
+    float a;             // attention weight of the point
+    unsigned int pad;
+};
+
+// Position of a sampling point relative to the window of its pixel: r0 / c0 = window row / column of the upper-left
+// corner, lh / lw the fractional parts; `dense` = all four corners are window cells, `inside` = the reference's guard.
+struct WindowTap {
+    int r0, c0;
+    float lh, lw;
+    bool inside, dense;
+    __device__ __forceinline__ void setup(float h, float w, int H, int W, int py, int px) {
+        inside = (h > -1.f) && (h < float(H)) && (w > -1.f) && (w < float(W));
+        const float fh = floorf(h), fw = floorf(w);
+        lh = h - fh; lw = w - fw;
+        r0 = (int)fh - (py - 2); c0 = (int)fw - (px - 2);
+        dense = inside && r0 >= 0 && r0 <= 3 && c0 >= 0 && c0 <= 3;
+    }
+    __device__ __forceinline__ void axis(float (&v)[5], int i0, float l) const {
+#pragma unroll
+        for (int r = 0; r < 5; ++r) v[r] = (r == i0) ? 1.f - l : (r == i0 + 1) ? l : 0.f;
+    }
+};
 
 template <typename T>
-__global__ void __launch_bounds__(WIN_THREADS)
+__global__ void __launch_bounds__(WIN_THREADS, 4)
 deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ offset,
-                     const T *__restrict__ dense /* [B*G, 25, sH, sW] */, T *__restrict__ attn /* [B, G, P, sH, sW] */,
-                     T *__restrict__ window /* [B*G, 25, sH, sW] */, int B, int Cq, int H, int W, int P, int G) {
-    __shared__ float s_d[25][WIN_THREADS], s_w[25][WIN_THREADS];
+                     const T *__restrict__ dense /* [B*G, 25, sH, sW] */, T *__restrict__ attn /* [B, G, P, sH, sW] or null */,
+                     T *__restrict__ window /* [B*G, 25, sH, sW] */, OutlierTap *__restrict__ taps,
+                     unsigned int *__restrict__ tap_count, int B, int Cq, int H, int W, int P, int G) {
     const int sH = 2 * H, sW = 2 * W, gq = Cq / G;
     const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
-    const int tx = threadIdx.x;
+    const int lane = threadIdx.x & 31;
     const long long total = (long long)B * G * hi;
     for (long long i0 = (long long)blockIdx.x * WIN_THREADS; i0 < total; i0 += (long long)gridDim.x * WIN_THREADS) {
-        const long long i = i0 + tx;
+        const long long i = i0 + threadIdx.x;
         const bool live = i < total;
         const size_t pix = live ? (size_t)(i % hi) : 0;
         const long long bg = live ? i / (long long)hi : 0;
         const int g = (int)(bg % G), b = (int)(bg / G);
         const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = qh >> 1, px = qw >> 1;
-        if (live) {
+        float d[25], oh[MAXP], ow[MAXP];
 #pragma unroll
-            for (int k = 0; k < 25; ++k) {
-                s_d[k][tx] = to_acc(dense[((size_t)bg * 25 + k) * hi + pix]);
-                s_w[k][tx] = 0.f;
-            }
-        }
-        float logit[MAXP], ph[MAXP], pw[MAXP];
-        float m = -INFINITY;
+        for (int k = 0; k < 25; ++k) d[k] = live ? to_acc(__ldcs(dense + ((size_t)bg * 25 + k) * hi + pix)) : 0.f;
 #pragma unroll
         for (int p = 0; p < MAXP; ++p) {
-            logit[p] = 0.f; ph[p] = 0.f; pw[p] = 0.f;
+            oh[p] = 0.f; ow[p] = 0.f;
             if (live && p < P) {
-                const size_t o = ((size_t)(b * G + g) * P + p) * 2 * hi + pix;
-                const float w = float(px) + to_acc(offset[o]), h = float(py) + to_acc(offset[o + hi]);
-                ph[p] = h; pw[p] = w;
-                Bilinear<float> bl;
-                bl.setup(h, w, H, W);
+                const size_t o = ((size_t)bg * P + p) * 2 * hi + pix;
+                ow[p] = float(px) + to_acc(__ldg(offset + o));
+                oh[p] = float(py) + to_acc(__ldg(offset + o + hi));
+            }
+        }
+        float logit[MAXP];
+        float m = -INFINITY;
+        unsigned int outliers = 0;
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p) {
+            logit[p] = 0.f;
+            if (live && p < P) {
+                WindowTap t;
+                t.setup(oh[p], ow[p], H, W, py, px);
                 float acc = 0.f;
-                if (in_window(bl, h, w, py, px)) {
-                    const int k00 = ((int)floorf(h) - py + 2) * 5 + ((int)floorf(w) - px + 2);
-                    acc = bl.w00 * s_d[k00][tx] + bl.w01 * s_d[k00 + 1][tx] + bl.w10 * s_d[k00 + 5][tx] + bl.w11 * s_d[k00 + 6][tx];
-                } else if (bl.inside) {       // outlier: gather the key directly
+                if (t.dense) {
+                    float vy[5], vx[5];
+                    t.axis(vy, t.r0, t.lh);
+                    t.axis(vx, t.c0, t.lw);
+#pragma unroll
+                    for (int r = 0; r < 5; ++r) {
+                        float row = 0.f;
+#pragma unroll
+                        for (int c = 0; c < 5; ++c) row += vx[c] * d[r * 5 + c];
+                        acc += vy[r] * row;
+                    }
+                } else if (t.inside) {        // outlier: gather the key directly
+                    outliers |= 1u << p;
+                    Bilinear<float> bl;
+                    bl.setup(oh[p], ow[p], H, W);
                     const T *qp = query + ((size_t)b * Cq + (size_t)g * gq) * hi + pix;
                     const T *kp = key + ((size_t)b * Cq + (size_t)g * gq) * lo;
                     for (int c = 0; c < gq; ++c) acc += bl.sample(kp + (size_t)c * lo) * to_acc(qp[(size_t)c * hi]);
@@ -334,47 +370,80 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
             if (p < P) { logit[p] = expf(logit[p] - m); z += logit[p]; }
         const float inv = 1.f / z;
 #pragma unroll
+        for (int k = 0; k < 25; ++k) d[k] = 0.f;        // from here on: the window weights
+#pragma unroll
         for (int p = 0; p < MAXP; ++p) {
             if (live && p < P) {
                 const float a = logit[p] * inv;
-                attn[((size_t)(b * G + g) * P + p) * hi + pix] = from_acc<T>(a);
-                Bilinear<float> bl;
-                bl.setup(ph[p], pw[p], H, W);
-                if (in_window(bl, ph[p], pw[p], py, px)) {
-                    const int k00 = ((int)floorf(ph[p]) - py + 2) * 5 + ((int)floorf(pw[p]) - px + 2);
-                    s_w[k00][tx] += a * bl.w00; s_w[k00 + 1][tx] += a * bl.w01;
-                    s_w[k00 + 5][tx] += a * bl.w10; s_w[k00 + 6][tx] += a * bl.w11;
+                logit[p] = a;
+                if (attn != nullptr) attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(a);
+                WindowTap t;
+                t.setup(oh[p], ow[p], H, W, py, px);
+                if (t.dense) {
+                    float vy[5], vx[5];
+                    t.axis(vy, t.r0, t.lh);
+                    t.axis(vx, t.c0, t.lw);
+#pragma unroll
+                    for (int r = 0; r < 5; ++r) {
+                        const float ay = a * vy[r];
+#pragma unroll
+                        for (int c = 0; c < 5; ++c) d[r * 5 + c] += ay * vx[c];
+                    }
                 }
             }
         }
         if (live) {
 #pragma unroll
-            for (int k = 0; k < 25; ++k) window[((size_t)bg * 25 + k) * hi + pix] = from_acc<T>(s_w[k][tx]);
+            for (int k = 0; k < 25; ++k) window[((size_t)bg * 25 + k) * hi + pix] = from_acc<T>(d[k]);
+        }
+        // append this warp's outlier points to the list: one counter update per warp
+        const unsigned int any = __ballot_sync(0xffffffffu, outliers != 0);
+        if (any != 0) {
+            const int mine = __popc(outliers);
+            int incl = mine;
+#pragma unroll
+            for (int sft = 1; sft < 32; sft <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, sft);
+                if (lane >= sft) incl += up;
+            }
+            const int warp_total = __shfl_sync(0xffffffffu, incl, 31);
+            unsigned int base = 0;
+            if (lane == 0) base = atomicAdd(tap_count, (unsigned int)warp_total);
+            base = __shfl_sync(0xffffffffu, base, 0);
+            unsigned int at = base + (unsigned int)(incl - mine);
+#pragma unroll
+            for (int p = 0; p < MAXP; ++p)
+                if (outliers & (1u << p)) {
+                    OutlierTap t;
+                    t.k = (unsigned int)(bg * P + p); t.pix = (unsigned int)pix; t.a = logit[p]; t.pad = 0;
+                    taps[at++] = t;
+                }
         }
     }
 }
 
-// one thread per (image, group, point, pixel): adds a_p * bilinear(value_c) of the outlier points to the output
+// Adds a_p * bilinear(value_c) of the listed outlier points to the output: eight threads per point share its sampling
+// set-up and take every eighth channel of the group.
 template <typename T>
-__global__ void deform_outlier_kernel(const T *__restrict__ attn, const T *__restrict__ value, const T *__restrict__ offset,
-                                      T *__restrict__ out, int B, int C, int H, int W, int P, int G) {
-    const int sH = 2 * H, sW = 2 * W, gc = C / G;
-    const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
-    const long long total = (long long)B * G * P * hi;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const size_t pix = (size_t)(i % hi);
-        const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = qh >> 1, px = qw >> 1;
-        const long long k = i / (long long)hi;          // (b*G + g)*P + p
-        const float w = float(px) + to_acc(offset[(size_t)k * 2 * hi + pix]), h = float(py) + to_acc(offset[(size_t)k * 2 * hi + hi + pix]);
+__global__ void deform_outlier_kernel(const OutlierTap *__restrict__ taps, const unsigned int *__restrict__ tap_count,
+                                      const T *__restrict__ value, const T *__restrict__ offset, T *__restrict__ out,
+                                      int C, int H, int W, int P, int G) {
+    const int sW = 2 * W, gc = C / G;
+    const size_t hi = (size_t)(2 * H) * sW, lo = (size_t)H * W;
+    const unsigned int n = *tap_count;
+    const int sub = threadIdx.x & 7;
+    for (unsigned int e = (blockIdx.x * blockDim.x + threadIdx.x) >> 3; e < n; e += (gridDim.x * blockDim.x) >> 3) {
+        const OutlierTap t = taps[e];
+        const size_t pix = t.pix;
+        const int px = (int)(pix % sW) >> 1, py = (int)(pix / sW) >> 1;
+        const float w = float(px) + to_acc(__ldg(offset + (size_t)t.k * 2 * hi + pix));
+        const float h = float(py) + to_acc(__ldg(offset + (size_t)t.k * 2 * hi + hi + pix));
         Bilinear<float> bl;
         bl.setup(h, w, H, W);
-        if (!bl.inside || in_window(bl, h, w, py, px)) continue;
-        const long long bg = k / P;
-        const float a = to_acc(attn[i]);
-        const T *vp = value + (size_t)bg * gc * lo;
-        T *op = out + (size_t)bg * gc * hi + pix;
-        for (int c = 0; c < gc; ++c) atomicAdd(op + (size_t)c * hi, from_acc<T>(a * bl.sample(vp + (size_t)c * lo)));
+        const size_t bg = t.k / (unsigned int)P;
+        const T *vp = value + bg * gc * lo;
+        T *op = out + bg * gc * hi + pix;
+        for (int c = sub; c < gc; c += 8) atomicAdd(op + (size_t)c * hi, from_acc<T>(t.a * bl.sample(vp + (size_t)c * lo)));
     }
 }
 
@@ -648,7 +717,9 @@ extern "C" {
 size_t sapa_deform_fused_forward_workspace(int B, int H, int W, int P, int s, int G, int dtype) {
     if (B <= 0 || H <= 0 || W <= 0 || P <= 0 || G <= 0 || s != 2 || dtype != SAPA_F32) return 0;
     const size_t hi = (size_t)s * H * s * W;
-    return ((size_t)B * G * (25 + 25 + P) * hi) * dtype_size(dtype);
+    if ((size_t)B * G * P >= 0xffffffffull || hi >= 0xffffffffull) return 0;       // the outlier list indexes with 32 bits
+    // dense similarity + window weights, the outlier list (worst case: every point) and its counter
+    return (size_t)B * G * 50 * hi * dtype_size(dtype) + (size_t)B * G * P * hi * sizeof(OutlierTap) + 16;
 }
 
 int sapa_deform_fused_forward_dense(const void *query, const void *key, const void *value, const void *offset, void *out,
@@ -659,36 +730,37 @@ int sapa_deform_fused_forward_dense(const void *query, const void *key, const vo
     if (int e = check_deform(fn, B, Cq, C, H, W, P, s, G, dtype)) return e;
     SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset);
     SAPA_CHECK_PTR(fn, out);
-    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32, SAPA_ERR_UNSUPPORTED,
+    const size_t need = sapa_deform_fused_forward_workspace(B, H, W, P, s, G, dtype);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
                  "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_fused_forward)", fn, MAXP);
-    const size_t hi = (size_t)s * H * s * W;
-    // the attention region of the workspace is only needed when the caller does not keep the attention itself
-    const size_t need = sapa_deform_fused_forward_workspace(B, H, W, P, s, G, dtype) -
-                        (attn != nullptr ? (size_t)B * G * P * hi * dtype_size(dtype) : 0);
     SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
                  "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
+    const size_t hi = (size_t)s * H * s * W;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     float *dense = static_cast<float *>(workspace), *window = dense + (size_t)B * G * 25 * hi;
-    float *attn_buf = attn != nullptr ? static_cast<float *>(attn) : window + (size_t)B * G * 25 * hi;
+    OutlierTap *taps = reinterpret_cast<OutlierTap *>(window + (size_t)B * G * 25 * hi);
+    unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * P * hi);
+    if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
+        set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
+        return SAPA_ERR_LAUNCH;
+    }
     // 1. dense 25-slot similarity of every group: the B x G groups are images of Cq / G channels
     if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
-    // 2. attention over the points and dense window weights
+    // 2. attention over the points, dense window weights, list of the points that leave the window
     {
         const long long total = (long long)B * G * hi;
         deform_window_kernel<float><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
             static_cast<const float *>(query), static_cast<const float *>(key), static_cast<const float *>(offset), dense,
-            attn_buf, window, B, Cq, H, W, P, G);
+            static_cast<float *>(attn), window, taps, tap_count, B, Cq, H, W, P, G);
         if (int e = check_launch("deform_window_kernel")) return e;
     }
     // 3. aggregation of every group's channels over the window
     if (int e = run_agg(window, value, out, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
-    // 4. the points whose corners leave the window
-    {
-        const long long total = (long long)B * G * P * hi;
-        deform_outlier_kernel<float><<<grid_1d(total, 256), 256, 0, st>>>(
-            attn_buf, static_cast<const float *>(value), static_cast<const float *>(offset), static_cast<float *>(out), B, C, H, W, P, G);
-        return check_launch("deform_outlier_kernel");
-    }
+    // 4. the listed points (the count is only known on the device: a fixed grid strides over the list)
+    deform_outlier_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, static_cast<const float *>(value),
+                                                          static_cast<const float *>(offset), static_cast<float *>(out),
+                                                          C, H, W, P, G);
+    return check_launch("deform_outlier_kernel");
 }
 
 }  // extern "C"

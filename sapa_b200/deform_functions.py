@@ -151,8 +151,6 @@ class DeformSapaFusedFunction(Function):
             code = _lib.dtype_code(value)
             nbytes = int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, code))
             if nbytes:       # s = 2, float32: the dense-window path on the SAPA-B kernels
-                if attn is not None:
-                    nbytes -= attn.numel() * attn.element_size()      # the attention goes to its own tensor
                 workspace = torch.empty(nbytes, dtype=torch.uint8, device=value.device)
                 _lib.call("sapa_deform_fused_forward_dense", value.device, query, key, value, offset, out, attn, workspace,
                           workspace.numel(), n, cq, c, h, w, num_point, scale_factor, groups, code)
