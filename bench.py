@@ -641,13 +641,34 @@ def main():
         with torch.no_grad():
             ys_fixed = [p(f) for p, f in zip(proj, feats)]
         ms_p, ms_u = time_path(pyramid, 10), time_path(upsampling_only, 10)
+        for m in ups:
+            m.fuse_projection = False
+        ms_u_torch = time_path(upsampling_only, 10)
         pyr_pix = PB * (32 * 32 + 64 * 64 + 128 * 128)
-        paths["decoder_pyramid_bf16"] = {"ms": ms_p, "ms_sapa_modules_only": ms_u, "batch": PB,
-                                         "mpix_per_s": pyr_pix / (ms_u * 1e-3) / 1e6,
-                                         "note": "three chained SAPA modules incl. GroupNorm and 1x1 projections (torch kernels); "
-                                                 "ms = with the four 256-channel feature projections, mpix_per_s = upsampled pixels of "
-                                                 "the three levels / ms_sapa_modules_only"}
+        paths["decoder_pyramid_bf16"] = {"ms": ms_p, "ms_sapa_modules_only": ms_u, "ms_sapa_modules_torch_projections": ms_u_torch,
+                                         "batch": PB, "mpix_per_s": pyr_pix / (ms_u * 1e-3) / 1e6,
+                                         "note": "three chained SAPA modules: GroupNorm + 1x1 query / key projections as one tensor-core "
+                                                 "GEMM each (sapa_project_forward) and the fused attention kernel; "
+                                                 "ms_sapa_modules_torch_projections = the same with torch's GroupNorm and convolution; "
+                                                 "ms = with the four 256-channel feature projections (torch), mpix_per_s = upsampled pixels "
+                                                 "of the three levels / ms_sapa_modules_only"}
         del feats, proj, ups, ys_fixed
+        # GroupNorm(32) + 1x1 projection of the guidance features to the query at the cfg2 shapes: statistics pass, fold,
+        # tcgen05 GEMM.  Bytes: x is read twice (the statistics must be complete before the first output), out written once.
+        from sapa_b200.projection import project
+        xg = torch.randn(B_, C_, s * H_, s * W_, device=device).to(dtype)
+        gn = torch.nn.GroupNorm(32, C_).to(device, dtype)
+        cv = torch.nn.Conv2d(C_, d_, 1).to(device, dtype)
+        with torch.no_grad():
+            ms_g = time_path(lambda: project(xg, gn, cv), 10)
+            ms_t = time_path(lambda: cv(gn(xg)), 10)
+        bytes_g = (2 * xg.numel() + B_ * d_ * hi) * esize
+        paths["projection_groupnorm_1x1"] = {"ms": ms_g, "ms_torch_groupnorm_conv": ms_t, "launches": 3, "algorithmic_bytes": bytes_g,
+                                             "achieved_gbs": bytes_g / (ms_g * 1e-3) / 1e9,
+                                             "roofline_frac": bytes_g / (ms_g * 1e-3) / 1e9 / peak_gbs,
+                                             "kernels": sapa_b200._lib.last_kernels(),
+                                             "config": {"B": B_, "C": C_, "d": d_, "pixels": hi, "groups": 32}}
+        del xg, gn, cv
         paths["reference_cuda_ext"] = reference_cuda_ext_times(wl, device, time_path)
 
     # ---- BASELINE config 5 at this N: batch-sharded and row-sharded bfloat16 forward, strong scaling ----

@@ -62,6 +62,7 @@ int sapa_abi_version(void);
 /* The TMA kernels never spin without a limit: a wait on a shared-memory barrier that gives up (which only a
  * malfunction can cause) makes the kernel return early and sets a flag on the device.  This reads the flags of the
  * current device: 0 = no wait ever gave up, bit 0 = fused forward / backward stage 1, bit 1 = gradient gather,
+ * bit 2 = projection GEMM,
  * -1 = the flags could not be read.  Reading a raised flag clears it and resets the tile schedulers of that kernel
  * family (a CTA that gave up leaves its scheduler counters dirty), so the library is usable again afterwards.
  * It synchronises the device; meant for tests and for diagnosing wrong results, not for the hot path.
@@ -209,6 +210,22 @@ size_t sapa_deform_fused_forward_workspace(int B, int H, int W, int P, int s, in
 int sapa_deform_fused_forward_dense(const void *query, const void *key, const void *value, const void *offset,
                                     void *out, void *attn, void *workspace, size_t workspace_bytes,
                                     int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
+
+/* GroupNorm followed by the 1 x 1 projection that produces the query or the key (reference: sapa_base.py:27-34,
+ * sapa_deform.py:35-42 - `self.q(self.norm_y(y))`, `self.k(self.norm_x(x))`), forward only:
+ *   out[b, j, p] = bias[j] + sum_c weight[j, c] * (gamma[c] * (x[b, c, p] - mean[b, g(c)]) * rstd[b, g(c)] + beta[c])
+ * x [B, C, HW], weight [d, C], bias [d] or NULL, gamma / beta [C], out [B, d, HW]; `groups` = number of GroupNorm groups
+ * (32 in the reference modules), 0 = no normalisation (gamma, beta ignored; `norm=False`).  The statistics take one pass
+ * over x, the normalisation is folded into per-image weights, and the product runs as one tcgen05 GEMM that reads x once
+ * more: the normalised tensor is never written.  float32 is evaluated as a three-term tf32 product (float32 accuracy).
+ * `workspace`: sapa_project_workspace() bytes, 256-byte aligned, owned by the caller.  Needs d % 16 == 0, d <= 256,
+ * HW * esize and C * esize multiples of 16 and, with groups > 0, C % groups == 0; otherwise SAPA_ERR_UNSUPPORTED (the
+ * workspace query returns 0) and the caller uses its own GroupNorm + convolution.  No counterpart in the reference's
+ * extensions (the reference runs these as torch modules). */
+size_t sapa_project_workspace(int B, int C, int HW, int d, int groups, int dtype);
+int sapa_project_forward(const void *x, const void *gamma, const void *beta, const void *weight, const void *bias, void *out,
+                         void *workspace, size_t workspace_bytes, int B, int C, int HW, int d, int groups, float eps,
+                         int dtype, void *stream);
 
 /* Gradients of sapa_deform_fused_forward with respect to query, key, value and offset from grad_out and the
  * attention map it saved, in one kernel: the chain DeformAVBackward -> softmax backward over the points ->

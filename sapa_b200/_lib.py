@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("SAPA_B200_LIB") or os.path.join(_HERE, "libsapa_b200.
 SAPA_F32, SAPA_F16, SAPA_BF16, SAPA_F64 = 0, 1, 2, 3
 _DTYPE_CODE = {torch.float32: SAPA_F32, torch.float16: SAPA_F16, torch.bfloat16: SAPA_BF16, torch.float64: SAPA_F64}
 SAPA_ERR_UNSUPPORTED = -5
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 _lib = None
 
@@ -38,10 +38,11 @@ _SIGNATURES = {
     "sapa_deform_av_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_fused_forward": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_fused_forward_dense": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "sapa_project_forward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, ctypes.c_float, _i, _vp],
     "sapa_deform_fused_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
 }
 EXPORTS = sorted(list(_SIGNATURES) + ["sapa_last_error", "sapa_last_kernels", "sapa_abi_version", "sapa_fused_backward_workspace",
-                                           "sapa_deform_fused_forward_workspace",
+                                           "sapa_deform_fused_forward_workspace", "sapa_project_workspace",
                                            "sapa_fused_backward_static_capacity", "sapa_wait_timeout_flags"])
 
 
@@ -74,6 +75,8 @@ def lib() -> ctypes.CDLL:
     handle.sapa_fused_backward_workspace.restype = ctypes.c_size_t
     handle.sapa_deform_fused_forward_workspace.argtypes = [_i, _i, _i, _i, _i, _i, _i]
     handle.sapa_deform_fused_forward_workspace.restype = ctypes.c_size_t
+    handle.sapa_project_workspace.argtypes = [_i, _i, _i, _i, _i, _i]
+    handle.sapa_project_workspace.restype = ctypes.c_size_t
     handle.sapa_fused_backward_static_capacity.argtypes = []
     handle.sapa_fused_backward_static_capacity.restype = ctypes.c_size_t
     handle.sapa_wait_timeout_flags.argtypes = []

@@ -56,6 +56,6 @@ const char *sapa_last_kernels(void) {
     return sapa::g_kernels_copy;
 }
 
-int sapa_abi_version(void) { return 2; }
+int sapa_abi_version(void) { return 3; }
 
 }  // extern "C"

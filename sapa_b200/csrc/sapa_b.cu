@@ -543,6 +543,7 @@ int launch_fused_mma(const void *q, const void *k, const void *v, void *out, voi
                      int rows, int ytop0, int dtype, cudaStream_t st);
 
 int tma_wait_timeout_flag();
+int proj_wait_timeout_flag();
 int gath_wait_timeout_flag();
 // tensor-core transposed aggregation (sapa_gath_mma.cu)
 bool gath_mma_supported(int W, int dtype);
@@ -671,9 +672,9 @@ using namespace sapa;
 extern "C" {
 
 int sapa_wait_timeout_flags(void) {
-    const int a = tma_wait_timeout_flag(), b = gath_wait_timeout_flag();
-    if (a < 0 || b < 0) return -1;
-    return (a ? 1 : 0) | (b ? 2 : 0);
+    const int a = tma_wait_timeout_flag(), b = gath_wait_timeout_flag(), c = proj_wait_timeout_flag();
+    if (a < 0 || b < 0 || c < 0) return -1;
+    return (a ? 1 : 0) | (b ? 2 : 0) | (c ? 4 : 0);
 }
 
 int sapa_qk_forward(const void *query, const void *key, void *out, int B, int d, int H, int W, int K, int s, int dtype,

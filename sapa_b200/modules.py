@@ -13,6 +13,7 @@ import torch.nn.functional as F
 
 from .deform_functions import deform_av, deform_qk, deform_sapa_fused
 from .functions import av, qk, sapa_fused
+from .projection import project, project_supported
 
 
 def _init_projection(module: nn.Module) -> None:
@@ -35,9 +36,24 @@ def _common_dtype(*tensors):
     autocast type.  Outside autocast the tensors pass through untouched (mismatches are then reported by the op).
     The reference modules have no autocast handling (sapa_base.py:26-40, sapa_deform.py:34-53)."""
     if tensors[0].is_cuda and torch.is_autocast_enabled():
-        dtype = torch.get_autocast_gpu_dtype()
+        dtype = torch.get_autocast_dtype("cuda")
         return tuple(t.to(dtype) for t in tensors)
     return tensors
+
+
+def _projected(x, norm, conv, fuse):
+    """``conv(norm(x))``.  With ``fuse`` and no gradient to record, GroupNorm and the 1x1 convolution run as one
+    tensor-core GEMM (``sapa_project_forward``); training, CPU tensors and shapes that kernel does not take use the torch
+    modules."""
+    if fuse and x.is_cuda:
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or conv.weight.requires_grad or
+                                                  (norm is not None and norm.weight.requires_grad))
+        if not needs_grad:
+            if torch.is_autocast_enabled():
+                x = x.to(torch.get_autocast_dtype("cuda"))
+            if project_supported(x, norm, conv):
+                return project(x, norm, conv)
+    return conv(norm(x)) if norm is not None else conv(x)
 
 
 class SAPA(nn.Module):
@@ -49,6 +65,7 @@ class SAPA(nn.Module):
         dim_x = dim_y if dim_x is None else dim_x
         self.up_factor, self.up_kernel_size, self.embedding_dim = up_factor, up_kernel_size, embedding_dim
         self.norm, self.impl = norm, _check_impl(impl)
+        self.fuse_projection = impl == "fused"      # set to False to keep torch's GroupNorm + convolution at inference too
         if norm:
             self.norm_y = nn.GroupNorm(32, dim_y)
             self.norm_x = nn.GroupNorm(32, dim_x)
@@ -57,9 +74,10 @@ class SAPA(nn.Module):
         self.apply(_init_projection)
 
     def forward(self, y, x):
-        x_normed, y_normed = (self.norm_x(x), self.norm_y(y)) if self.norm else (x, y)
         # the value is the un-normalised x; only the key is computed from the normalised one
-        return self.attention(self.q(y_normed), self.k(x_normed), x)
+        q = _projected(y, self.norm_y if self.norm else None, self.q, self.fuse_projection)
+        k = _projected(x, self.norm_x if self.norm else None, self.k, self.fuse_projection)
+        return self.attention(q, k, x)
 
     def attention(self, q, k, v):
         q, k, v = _common_dtype(q, k, v)
@@ -79,6 +97,7 @@ class SAPADeform(nn.Module):
         self.up_factor, self.num_point, self.groups = up_factor, num_point, groups
         self.embedding_dim, self.high_offset = embedding_dim, high_offset
         self.norm, self.impl = norm, _check_impl(impl)
+        self.fuse_projection = impl == "fused"
         if norm:
             self.norm_y = nn.GroupNorm(32, dim_y)
             self.norm_x = nn.GroupNorm(32, dim_x)
@@ -89,9 +108,9 @@ class SAPADeform(nn.Module):
         self.apply(_init_projection)
 
     def forward(self, y, x):
-        x_normed, y_normed = (self.norm_x(x), self.norm_y(y)) if self.norm else (x, y)
-        q, k = self.q(y_normed), self.k(x_normed)
-        raw = self.offset(x_normed)
+        q = _projected(y, self.norm_y if self.norm else None, self.q, self.fuse_projection)
+        k = _projected(x, self.norm_x if self.norm else None, self.k, self.fuse_projection)
+        raw = self.offset(self.norm_x(x) if self.norm else x)
         if self.high_offset:   # one offset per high-res pixel, unpacked from channels
             offset = F.pixel_shuffle(raw, upscale_factor=self.up_factor)
         else:                  # every high-res pixel of a parent shares the parent's offset
