@@ -62,6 +62,9 @@ def test_projection_matches_groupnorm_plus_conv(sp, shape, dtype, tol):
     from sapa_b200.projection import project, project_supported
     B, C, H, W, d, groups, bias, mean = shape
     x, norm, conv, ref = _case(B, C, H, W, d, groups, dtype, bias, mean)
+    if (H * W * x.element_size()) % 16 != 0:          # a pixel row of the tensor map must be a multiple of 16 bytes
+        assert not project_supported(x, norm, conv)
+        return
     assert project_supported(x, norm, conv)
     out = project(x, norm, conv)
     torch.cuda.synchronize()
