@@ -631,25 +631,33 @@ def main():
                     x = m(ys[level], x)
                 return x
 
+        def upsampling_chain(ys):
+            x = ys[3]
+            for level, m in zip((2, 1, 0), ups):
+                x = m(ys[level], x)
+            return x
+
         def upsampling_only():
             with torch.no_grad():
-                x = ys_fixed[3]
-                for level, m in zip((2, 1, 0), ups):
-                    x = m(ys_fixed[level], x)
-                return x
+                return upsampling_chain(ys_fixed)
 
         with torch.no_grad():
             ys_fixed = [p(f) for p, f in zip(proj, feats)]
         ms_p, ms_u = time_path(pyramid, 10), time_path(upsampling_only, 10)
+        graphed = sapa_b200.GraphedForward(lambda *ys: upsampling_chain(ys), ys_fixed)
+        ms_g_u = time_path(lambda: graphed(*graphed.inputs), 10)      # inputs already in the captured buffers: replay only
+        del graphed
         for m in ups:
             m.fuse_projection = False
         ms_u_torch = time_path(upsampling_only, 10)
         pyr_pix = PB * (32 * 32 + 64 * 64 + 128 * 128)
-        paths["decoder_pyramid_bf16"] = {"ms": ms_p, "ms_sapa_modules_only": ms_u, "ms_sapa_modules_torch_projections": ms_u_torch,
+        paths["decoder_pyramid_bf16"] = {"ms": ms_p, "ms_sapa_modules_only": ms_u, "ms_sapa_modules_graph_replay": ms_g_u,
+                                         "ms_sapa_modules_torch_projections": ms_u_torch,
                                          "batch": PB, "mpix_per_s": pyr_pix / (ms_u * 1e-3) / 1e6,
                                          "note": "three chained SAPA modules: GroupNorm + 1x1 query / key projections as one tensor-core "
                                                  "GEMM each (sapa_project_forward) and the fused attention kernel; "
-                                                 "ms_sapa_modules_torch_projections = the same with torch's GroupNorm and convolution; "
+                                                 "ms_sapa_modules_graph_replay = the same captured once into a CUDA graph (GraphedForward) and replayed; "
+                                                 "ms_sapa_modules_torch_projections = eager with torch's GroupNorm and convolution; "
                                                  "ms = with the four 256-channel feature projections (torch), mpix_per_s = upsampled pixels "
                                                  "of the three levels / ms_sapa_modules_only"}
         del feats, proj, ups, ys_fixed

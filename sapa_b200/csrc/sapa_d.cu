@@ -302,12 +302,17 @@ struct WindowTap {
     }
 };
 
-template <typename T>
+// NP = number of points known at compile time (0: read P at run time, up to MAXP).  The P points are walked ONCE with a
+// running maximum (the window weights collected so far are rescaled when the maximum grows), so the bilinear set-up of
+// a point is computed once.
+template <typename T, int NP>
 __global__ void __launch_bounds__(WIN_THREADS, 4)
 deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ offset,
                      const T *__restrict__ dense /* [B*G, 25, sH, sW] */, T *__restrict__ attn /* [B, G, P, sH, sW] or null */,
                      T *__restrict__ window /* [B*G, 25, sH, sW] */, OutlierTap *__restrict__ taps,
-                     unsigned int *__restrict__ tap_count, int B, int Cq, int H, int W, int P, int G) {
+                     unsigned int *__restrict__ tap_count, int B, int Cq, int H, int W, int P_runtime, int G) {
+    constexpr int PMAX = NP > 0 ? NP : MAXP;
+    const int P = NP > 0 ? NP : P_runtime;
     const int sH = 2 * H, sW = 2 * W, gq = Cq / G;
     const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
     const int lane = threadIdx.x & 31;
@@ -319,32 +324,33 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
         const long long bg = live ? i / (long long)hi : 0;
         const int g = (int)(bg % G), b = (int)(bg / G);
         const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = qh >> 1, px = qw >> 1;
-        float d[25], oh[MAXP], ow[MAXP];
+        float d[25], wd[25], oh[PMAX], ow[PMAX], logit[PMAX];
+        const T *dp = dense + (size_t)bg * 25 * hi + pix;
 #pragma unroll
-        for (int k = 0; k < 25; ++k) d[k] = live ? to_acc(__ldcs(dense + ((size_t)bg * 25 + k) * hi + pix)) : 0.f;
-#pragma unroll
-        for (int p = 0; p < MAXP; ++p) {
-            oh[p] = 0.f; ow[p] = 0.f;
-            if (live && p < P) {
-                const size_t o = ((size_t)bg * P + p) * 2 * hi + pix;
-                ow[p] = float(px) + to_acc(__ldg(offset + o));
-                oh[p] = float(py) + to_acc(__ldg(offset + o + hi));
-            }
+        for (int k = 0; k < 25; ++k) {
+            d[k] = live ? to_acc(__ldcs(dp + (size_t)k * hi)) : 0.f;
+            wd[k] = 0.f;
         }
-        float logit[MAXP];
-        float m = -INFINITY;
+        const T *offp = offset + (size_t)bg * P * 2 * hi + pix;
+#pragma unroll
+        for (int p = 0; p < PMAX; ++p) {
+            const bool on = live && p < P;
+            ow[p] = on ? float(px) + to_acc(__ldg(offp + (size_t)(2 * p) * hi)) : 0.f;
+            oh[p] = on ? float(py) + to_acc(__ldg(offp + (size_t)(2 * p + 1) * hi)) : 0.f;
+        }
+        float m = -INFINITY, z = 0.f;
         unsigned int outliers = 0;
 #pragma unroll
-        for (int p = 0; p < MAXP; ++p) {
+        for (int p = 0; p < PMAX; ++p) {
             logit[p] = 0.f;
             if (live && p < P) {
                 WindowTap t;
                 t.setup(oh[p], ow[p], H, W, py, px);
+                float vy[5], vx[5];
+                t.axis(vy, t.r0, t.lh);
+                t.axis(vx, t.c0, t.lw);
                 float acc = 0.f;
                 if (t.dense) {
-                    float vy[5], vx[5];
-                    t.axis(vy, t.r0, t.lh);
-                    t.axis(vx, t.c0, t.lw);
 #pragma unroll
                     for (int r = 0; r < 5; ++r) {
                         float row = 0.f;
@@ -361,40 +367,35 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
                     for (int c = 0; c < gq; ++c) acc += bl.sample(kp + (size_t)c * lo) * to_acc(qp[(size_t)c * hi]);
                 }
                 logit[p] = acc;
-                m = fmaxf(m, acc);
-            }
-        }
-        float z = 0.f;
+                if (acc > m) {                // new running maximum: bring what was collected so far to the new scale
+                    const float f = __expf(m - acc);      // 0 on the first point (m = -inf)
+                    z *= f;
 #pragma unroll
-        for (int p = 0; p < MAXP; ++p)
-            if (p < P) { logit[p] = expf(logit[p] - m); z += logit[p]; }
-        const float inv = 1.f / z;
-#pragma unroll
-        for (int k = 0; k < 25; ++k) d[k] = 0.f;        // from here on: the window weights
-#pragma unroll
-        for (int p = 0; p < MAXP; ++p) {
-            if (live && p < P) {
-                const float a = logit[p] * inv;
-                logit[p] = a;
-                if (attn != nullptr) attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(a);
-                WindowTap t;
-                t.setup(oh[p], ow[p], H, W, py, px);
+                    for (int k = 0; k < 25; ++k) wd[k] *= f;
+                    m = acc;
+                }
+                const float e = __expf(acc - m);
+                z += e;
                 if (t.dense) {
-                    float vy[5], vx[5];
-                    t.axis(vy, t.r0, t.lh);
-                    t.axis(vx, t.c0, t.lw);
 #pragma unroll
                     for (int r = 0; r < 5; ++r) {
-                        const float ay = a * vy[r];
+                        const float ey = e * vy[r];
 #pragma unroll
-                        for (int c = 0; c < 5; ++c) d[r * 5 + c] += ay * vx[c];
+                        for (int c = 0; c < 5; ++c) wd[r * 5 + c] += ey * vx[c];
                     }
                 }
             }
         }
+        const float inv = 1.f / z;
         if (live) {
+            T *wp = window + (size_t)bg * 25 * hi + pix;
 #pragma unroll
-            for (int k = 0; k < 25; ++k) window[((size_t)bg * 25 + k) * hi + pix] = from_acc<T>(d[k]);
+            for (int k = 0; k < 25; ++k) wp[(size_t)k * hi] = from_acc<T>(wd[k] * inv);
+        }
+#pragma unroll
+        for (int p = 0; p < PMAX; ++p) {
+            logit[p] = __expf(logit[p] - m) * inv;        // the attention weight of the point
+            if (live && p < P && attn != nullptr) attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(logit[p]);
         }
         // append this warp's outlier points to the list: one counter update per warp
         const unsigned int any = __ballot_sync(0xffffffffu, outliers != 0);
@@ -412,7 +413,7 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
             base = __shfl_sync(0xffffffffu, base, 0);
             unsigned int at = base + (unsigned int)(incl - mine);
 #pragma unroll
-            for (int p = 0; p < MAXP; ++p)
+            for (int p = 0; p < PMAX; ++p)
                 if (outliers & (1u << p)) {
                     OutlierTap t;
                     t.k = (unsigned int)(bg * P + p); t.pix = (unsigned int)pix; t.a = logit[p]; t.pad = 0;
@@ -749,9 +750,14 @@ int sapa_deform_fused_forward_dense(const void *query, const void *key, const vo
     // 2. attention over the points, dense window weights, list of the points that leave the window
     {
         const long long total = (long long)B * G * hi;
-        deform_window_kernel<float><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-            static_cast<const float *>(query), static_cast<const float *>(key), static_cast<const float *>(offset), dense,
-            static_cast<float *>(attn), window, taps, tap_count, B, Cq, H, W, P, G);
+        const float *q = static_cast<const float *>(query), *k = static_cast<const float *>(key), *o = static_cast<const float *>(offset);
+        const int grid = grid_1d(total, WIN_THREADS);
+        if (P == 9)          // the 3 x 3 points of the reference modules' default
+            deform_window_kernel<float, 9><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, static_cast<float *>(attn), window, taps, tap_count,
+                                                                       B, Cq, H, W, P, G);
+        else
+            deform_window_kernel<float, 0><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, static_cast<float *>(attn), window, taps, tap_count,
+                                                                       B, Cq, H, W, P, G);
         if (int e = check_launch("deform_window_kernel")) return e;
     }
     // 3. aggregation of every group's channels over the window

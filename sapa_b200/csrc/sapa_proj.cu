@@ -11,13 +11,15 @@
 //
 // GEMM kernel (tcgen05 / TMEM; one CTA per SM, 128-pixel tiles):
 //   D[128 px x d] (+)= A[128 px x k] * B[k x d],  A = x^T (pixels contiguous in NCHW: an "MN-major" operand), B = W' (K-major)
-//   * warp 4 (one lane): TMA producer.  A stage = 128 px x (128 B / esize) channels of x as boxes of one 128-byte pixel
+//   * warp 4 (one lane): TMA producer of the activations, warp 6 (one lane): TMA producer of the W' blocks.  A stage =
+//     128 px x (128 B / esize) channels of x as boxes of one 128-byte pixel
 //     row per channel (128-byte swizzle: exactly the canonical MN-major operand layout; 16-byte chunks for 16-bit types,
 //     32-byte chunks for tf32) plus the
 //     matching d x 128 B block of W' (canonical K-major layout).
-//   * float32 only, warps 6-9: 3xTF32 split.  The tensor core reads tf32 (the upper 19 bits); the product is evaluated as
+//   * float32 only, warps 7-10: 3xTF32 split.  The tensor core reads tf32 (the upper 19 bits); the product is evaluated as
 //     hi*hi + lo*hi + hi*lo with hi = x & 0xffffe000, lo = x - hi (exact), which gives float32 accuracy (1e-6).  The
-//     warps rewrite the stage in place as hi and write lo to the stage's second buffer; W' arrives already split.
+//     warps copy a landed ring slot into an operand slot as hi and lo and release the ring slot at once (so up to
+//     128 KB of loads stay in flight per SM whatever the MMAs do); W' arrives already split.
 //   * warp 5 (one lane): issues tcgen05.mma (M = 128, N = d, K = 32 bytes) into one of two TMEM accumulators, frees a
 //     stage with tcgen05.commit, signals the epilogue with another commit.
 //   * warps 0-3: epilogue.  tcgen05.ld (lane = pixel, column = output channel), add bias', store: for a fixed output
@@ -37,10 +39,10 @@ namespace proj {
 using namespace tmau;
 
 constexpr int TILE_PX = 128;
-constexpr int EPI_WARPS = 4, TMA_WARP = 4, MMA_WARP = 5, SPLIT_WARP0 = 6, SPLIT_WARPS = 4;
+constexpr int EPI_WARPS = 4, TMA_WARP = 4, MMA_WARP = 5, W_WARP = 6, SPLIT_WARP0 = 7, SPLIT_WARPS = 4;
 constexpr int THREADS = (SPLIT_WARP0 + SPLIT_WARPS) * 32;
 constexpr int Y_STAGE = 16384;           // bytes of activations per stage: 128 px x (128 B / esize) channels
-constexpr int MAX_STAGES = 6;
+constexpr int MAX_SLOTS = 8;              // per ring
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int STAT_THREADS = 256, MAX_SPLIT = 64, MAX_GROUPS = 256;
 
@@ -51,7 +53,7 @@ struct Args {
     CUtensorMap whi_map, wlo_map;   // (channel, output channel, 1, image), box = 128 bytes of channels x d rows
     const float *bias;              // folded bias [images or 1][d]
     void *out;                      // [B][d][HW]
-    int B, C, HW, d, w_per_image, tiles_per_image, total_tiles, kblocks, nstage, tmem_cols;
+    int B, C, HW, d, w_per_image, tiles_per_image, total_tiles, kblocks, nx, no, tmem_cols;
 };
 
 // ---------------------------------------------------------------------------------- tcgen05 wrappers
@@ -108,6 +110,10 @@ __device__ __forceinline__ void store_out(__half *p, float v) { *p = __float2hal
 __device__ __forceinline__ void store_out(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 
 // ---------------------------------------------------------------------------------- the GEMM kernel
+// Shared memory: an activation ring (NX slots of 16 KB, filled by TMA) and an operand ring (NO slots).  16-bit types:
+// the tensor core reads the activations straight from their ring slot and an operand slot holds only the W' block.
+// float32: an operand slot holds the split activations (hi, lo) and the W' blocks (hi, lo); the split warps move a
+// landed slot into it and hand the ring slot back at once, so the loads in flight do not wait for the MMAs.
 template <typename T>
 __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid_constant__ Args a) {
     constexpr bool F32 = sizeof(T) == 4;
@@ -122,21 +128,27 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
     constexpr unsigned A_ATOM = F32 ? 512u : 1024u, A_LAYOUT = F32 ? LAYOUT_SW128_BASE32 : LAYOUT_SW128;
 
     extern __shared__ unsigned char smem_dyn[];
-    const unsigned ring = ((unsigned)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
-    const int d = a.d, nstage = a.nstage;
+    const unsigned xring = ((unsigned)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
+    const int d = a.d;
+    const unsigned nx = (unsigned)a.nx, no = (unsigned)a.no;
     const unsigned w_bytes = (unsigned)d * 128u;
-    const unsigned w_ofs = F32 ? 2u * Y_STAGE : (unsigned)Y_STAGE;
-    const unsigned stage_bytes = w_ofs + (F32 ? 2u : 1u) * w_bytes;
-    const unsigned bars = ring + (unsigned)nstage * stage_bytes;
-    const unsigned full0 = bars, ready0 = bars + 8 * MAX_STAGES, empty0 = bars + 16 * MAX_STAGES;
-    const unsigned tfull0 = bars + 24 * MAX_STAGES, tempty0 = tfull0 + 16, tmem_slot = tempty0 + 16;
+    const unsigned w_ofs = F32 ? 2u * Y_STAGE : 0u;                       // W' blocks inside an operand slot
+    const unsigned op_bytes = w_ofs + (F32 ? 2u : 1u) * w_bytes;
+    const unsigned opring = xring + nx * (unsigned)Y_STAGE;
+    const unsigned bars = opring + no * op_bytes;
+    const unsigned xfull0 = bars, xempty0 = bars + 8 * MAX_SLOTS, ready0 = bars + 16 * MAX_SLOTS, wfull0 = bars + 24 * MAX_SLOTS;
+    const unsigned oempty0 = bars + 32 * MAX_SLOTS, tfull0 = bars + 40 * MAX_SLOTS, tempty0 = tfull0 + 16, tmem_slot = tempty0 + 16;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int i = 0; i < nstage; ++i) {
-            mbar_init(full0 + 8 * i, 1);
+        for (unsigned i = 0; i < nx; ++i) {
+            mbar_init(xfull0 + 8 * i, 1);
+            mbar_init(xempty0 + 8 * i, F32 ? SPLIT_WARPS * 32 : 1);
+        }
+        for (unsigned i = 0; i < no; ++i) {
             mbar_init(ready0 + 8 * i, SPLIT_WARPS * 32);
-            mbar_init(empty0 + 8 * i, 1);
+            mbar_init(wfull0 + 8 * i, 1);
+            mbar_init(oempty0 + 8 * i, 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(tfull0 + 8 * i, 1);
@@ -157,21 +169,33 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
     const int tpi = a.tiles_per_image, kblocks = a.kblocks;
     bool ok = true;
 
-    if (warp == TMA_WARP) {
+    if (warp == TMA_WARP) {            // activations: global -> ring
         if (lane == 0) {
             unsigned it = 0;
-            const unsigned tx = (unsigned)Y_STAGE + (F32 ? 2u : 1u) * w_bytes;
             for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
-                const int bi = tile / tpi, b = a.B - 1 - bi, px0 = (tile - bi * tpi) * TILE_PX, wb = a.w_per_image ? b : 0;
+                const int bi = tile / tpi, b = a.B - 1 - bi, px0 = (tile - bi * tpi) * TILE_PX;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const unsigned s = it % (unsigned)nstage, ph = (it / (unsigned)nstage) & 1u;
-                    if (!mbar_wait_bounded(empty0 + 8 * s, ph ^ 1u)) { ok = false; break; }
-                    const unsigned stage = ring + s * stage_bytes, full = full0 + 8 * s;
-                    mbar_expect_tx(full, (int)tx);
+                    const unsigned r = it % nx, rph = (it / nx) & 1u;
+                    if (!mbar_wait_bounded(xempty0 + 8 * r, rph ^ 1u)) { ok = false; break; }
+                    const unsigned slot = xring + r * (unsigned)Y_STAGE, full = xfull0 + 8 * r;
+                    mbar_expect_tx(full, Y_STAGE);
 #pragma unroll
-                    for (int j = 0; j < NBOX; ++j) tma_load_4d(stage + j * A_BOX, &a.x_map, full, px0 + j * PXG, kb * KCH, 0, b);
-                    tma_load_4d(stage + w_ofs, &a.whi_map, full, kb * KCH, 0, 0, wb);
-                    if (F32) tma_load_4d(stage + w_ofs + w_bytes, &a.wlo_map, full, kb * KCH, 0, 0, wb);
+                    for (int j = 0; j < NBOX; ++j) tma_load_4d(slot + j * A_BOX, &a.x_map, full, px0 + j * PXG, kb * KCH, 0, b);
+                }
+            }
+        }
+    } else if (warp == W_WARP) {       // W' blocks: global (L2 resident) -> operand ring
+        if (lane == 0) {
+            unsigned it = 0;
+            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
+                const int bi = tile / tpi, b = a.B - 1 - bi, wb = a.w_per_image ? b : 0;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const unsigned o = it % no, oph = (it / no) & 1u;
+                    if (!mbar_wait_bounded(oempty0 + 8 * o, oph ^ 1u)) { ok = false; break; }
+                    const unsigned slot = opring + o * op_bytes + w_ofs, full = wfull0 + 8 * o;
+                    mbar_expect_tx(full, (int)((F32 ? 2u : 1u) * w_bytes));
+                    tma_load_4d(slot, &a.whi_map, full, kb * KCH, 0, 0, wb);
+                    if (F32) tma_load_4d(slot + w_bytes, &a.wlo_map, full, kb * KCH, 0, 0, wb);
                 }
             }
         }
@@ -186,25 +210,28 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + buf * (unsigned)d;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const unsigned s = it % (unsigned)nstage, ph = (it / (unsigned)nstage) & 1u;
-                    if (!mbar_wait_bounded((F32 ? ready0 : full0) + 8 * s, ph)) { ok = false; break; }
+                    const unsigned r = it % nx, rph = (it / nx) & 1u, o = it % no, oph = (it / no) & 1u;
+                    if (!mbar_wait_bounded((F32 ? ready0 + 8 * o : xfull0 + 8 * r), F32 ? oph : rph) ||
+                        !mbar_wait_bounded(wfull0 + 8 * o, oph)) { ok = false; break; }
                     tc_fence_after();
-                    const unsigned stage = ring + s * stage_bytes;
+                    const unsigned op = opring + o * op_bytes;
+                    const unsigned act = F32 ? op : xring + r * (unsigned)Y_STAGE;
 #pragma unroll
                     for (int ks = 0; ks < KSTEPS; ++ks) {
-                        const uint64_t a_hi = smem_desc(stage + ks * A_KSTEP, A_BOX, A_ATOM, A_LAYOUT);
-                        const uint64_t b_hi = smem_desc(stage + w_ofs + ks * 32, 16, 1024, LAYOUT_SW128);
+                        const uint64_t a_hi = smem_desc(act + ks * A_KSTEP, A_BOX, A_ATOM, A_LAYOUT);
+                        const uint64_t b_hi = smem_desc(op + w_ofs + ks * 32, 16, 1024, LAYOUT_SW128);
                         tc_mma<F32>(d_tmem, a_hi, b_hi, idesc, (kb | ks) != 0 ? 1u : 0u);
                         if (F32) {
-                            const uint64_t a_lo = smem_desc(stage + Y_STAGE + ks * A_KSTEP, A_BOX, A_ATOM, A_LAYOUT);
-                            const uint64_t b_lo = smem_desc(stage + w_ofs + w_bytes + ks * 32, 16, 1024, LAYOUT_SW128);
+                            const uint64_t a_lo = smem_desc(act + Y_STAGE + ks * A_KSTEP, A_BOX, A_ATOM, A_LAYOUT);
+                            const uint64_t b_lo = smem_desc(op + w_ofs + w_bytes + ks * 32, 16, 1024, LAYOUT_SW128);
                             tc_mma<F32>(d_tmem, a_lo, b_hi, idesc, 1u);
                             tc_mma<F32>(d_tmem, a_hi, b_lo, idesc, 1u);
                         }
                     }
-                    tc_commit(empty0 + 8 * s);          // the stage is free once these MMAs have read it
+                    if (!F32) tc_commit(xempty0 + 8 * r);   // the activation slot is free once these MMAs have read it
+                    tc_commit(oempty0 + 8 * o);             // and so is the operand slot
                 }
-                if (ok) tc_commit(tfull0 + 8 * buf);    // the accumulator is complete once all MMAs so far are done
+                if (ok) tc_commit(tfull0 + 8 * buf);        // the accumulator is complete once all MMAs so far are done
             }
         }
     } else if (warp >= SPLIT_WARP0) {
@@ -213,21 +240,22 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
             unsigned it = 0;
             for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const unsigned s = it % (unsigned)nstage, ph = (it / (unsigned)nstage) & 1u;
-                    if (!mbar_wait_bounded(full0 + 8 * s, ph)) { ok = false; break; }
-                    const unsigned stage = ring + s * stage_bytes;
+                    const unsigned r = it % nx, rph = (it / nx) & 1u, o = it % no, oph = (it / no) & 1u;
+                    if (!mbar_wait_bounded(xfull0 + 8 * r, rph) || !mbar_wait_bounded(oempty0 + 8 * o, oph ^ 1u)) { ok = false; break; }
+                    const unsigned src = xring + r * (unsigned)Y_STAGE, dst = opring + o * op_bytes;
 #pragma unroll
                     for (int i = 0; i < Y_STAGE / 16 / (SPLIT_WARPS * 32); ++i) {
-                        const unsigned at = stage + (unsigned)(i * SPLIT_WARPS * 32 + st) * 16u;
+                        const unsigned off = (unsigned)(i * SPLIT_WARPS * 32 + st) * 16u;
                         unsigned v0, v1, v2, v3;
-                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(at) : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(at), "r"(v0 & TF32_MASK), "r"(v1 & TF32_MASK),
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(src + off) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst + off), "r"(v0 & TF32_MASK), "r"(v1 & TF32_MASK),
                                      "r"(v2 & TF32_MASK), "r"(v3 & TF32_MASK) : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(at + Y_STAGE), "r"(tf32_lo(v0)), "r"(tf32_lo(v1)),
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst + Y_STAGE + off), "r"(tf32_lo(v0)), "r"(tf32_lo(v1)),
                                      "r"(tf32_lo(v2)), "r"(tf32_lo(v3)) : "memory");
                     }
+                    mbar_arrive(xempty0 + 8 * r);                                    // the ring slot can be refilled
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes -> tensor-core reads
-                    mbar_arrive(ready0 + 8 * s);
+                    mbar_arrive(ready0 + 8 * o);
                 }
             }
         }
@@ -367,7 +395,8 @@ __global__ void __launch_bounds__(STAT_THREADS) gn_fold_kernel(const double2 *__
 
 // ---------------------------------------------------------------------------------- host side
 struct Plan {
-    int esize, nsplit, nimg, nstage, tmem_cols;
+    int esize, nsplit, nimg, nx, no, tmem_cols;
+    size_t smem;
     size_t partial_ofs, whi_ofs, wlo_ofs, bias_ofs, total;
 };
 
@@ -380,10 +409,13 @@ static bool make_plan(Plan &p, int B, int C, int HW, int d, int groups, int dtyp
     if (B <= 0 || C <= 0 || HW <= 0 || d < 16 || d > 256 || d % 16 != 0) return false;
     if (((size_t)HW * p.esize) % 16 != 0 || ((size_t)C * p.esize) % 16 != 0) return false;     // tensor-map strides
     if (groups < 0 || groups > MAX_GROUPS || (groups > 0 && (C % groups != 0 || ((size_t)(C / groups) * HW) % 4 != 0))) return false;
-    const size_t stage = (p.esize == 4 ? 2 * (size_t)Y_STAGE : (size_t)Y_STAGE) + (p.esize == 4 ? 2 : 1) * (size_t)d * 128;
+    // operand slots: split activations + W' blocks (float32), W' block only (16-bit); the rest goes to the activation ring
+    const size_t op = p.esize == 4 ? 2 * (size_t)Y_STAGE + 2 * (size_t)d * 128 : (size_t)d * 128;
     const size_t fixed = 1024 + 64 * 8;      // alignment slack + barriers
-    p.nstage = (int)std::min<size_t>(MAX_STAGES, (SMEM_LIMIT - fixed) / stage);
-    if (p.nstage < 2) return false;
+    p.no = p.esize == 4 ? 2 : 4;
+    if (fixed + p.no * op + 2 * (size_t)Y_STAGE > SMEM_LIMIT) return false;
+    p.nx = (int)std::min<size_t>(MAX_SLOTS, (SMEM_LIMIT - fixed - p.no * op) / Y_STAGE);
+    p.smem = fixed + p.no * op + (size_t)p.nx * Y_STAGE;
     p.tmem_cols = 32;
     while (p.tmem_cols < 2 * d) p.tmem_cols *= 2;
     p.nimg = groups > 0 ? B : 1;
@@ -429,9 +461,8 @@ static int run_project(const Plan &p, const void *x, const void *gamma, const vo
     a.tiles_per_image = (HW + TILE_PX - 1) / TILE_PX;
     a.total_tiles = a.tiles_per_image * B;
     a.kblocks = (C + KCH - 1) / KCH;
-    a.nstage = p.nstage; a.tmem_cols = p.tmem_cols;
-    const size_t stage = (sizeof(T) == 4 ? 2 * (size_t)Y_STAGE : (size_t)Y_STAGE) + (sizeof(T) == 4 ? 2 : 1) * (size_t)d * 128;
-    const size_t smem = 1024 + p.nstage * stage + 64 * 8;
+    a.nx = p.nx; a.no = p.no; a.tmem_cols = p.tmem_cols;
+    const size_t smem = p.smem;
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
