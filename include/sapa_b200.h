@@ -70,6 +70,10 @@ int sapa_abi_version(void);
  * graphs holding these kernels must not overlap each other on one device (ordinary launches on other streams may
  * overlap them freely).  No counterpart in the reference. */
 int sapa_wait_timeout_flags(void);
+/* Self-test of that mechanism: launches one small kernel whose bounded wait is certain to give up (it waits a few
+ * dozen tries on a barrier that nothing signals, then raises the flag and returns normally; nothing hangs or faults).
+ * Afterwards sapa_wait_timeout_flags() reports bit 0 once, and the library works as before. */
+int sapa_selftest_wait_timeout(void *stream);
 
 /* ------------------------------------------------------------------ SAPA-B, separate ops ------------- */
 
@@ -210,6 +214,18 @@ size_t sapa_deform_fused_forward_workspace(int B, int H, int W, int P, int s, in
 int sapa_deform_fused_forward_dense(const void *query, const void *key, const void *value, const void *offset,
                                     void *out, void *attn, void *workspace, size_t workspace_bytes,
                                     int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
+
+/* Backward of sapa_fused_forward_slab for one row slab (multi-GPU row sharding; no counterpart in the reference).
+ * grad_out / query / attn are the slab's own rows; key / value are the padded slabs of the forward
+ * [B, *, halo_top + H + halo_bottom, W]; grad_query [B, d, sH, sW]; grad_key / grad_value come out in the same padded
+ * frame as key / value: rows [halo_top, halo_top + H) are the slab's contribution to its own rows, the halo rows its
+ * contribution to the neighbouring slabs' edge rows - the caller sends those to the neighbours and adds what it
+ * receives to its own first / last rows.  Workspace as for sapa_fused_backward (sized for the slab).  Needs K = 5,
+ * s = 2 and rows of 16 bytes (SAPA_ERR_UNSUPPORTED otherwise).  Deterministic. */
+int sapa_fused_backward_slab(const void *grad_out, const void *query, const void *key, const void *value, const void *attn,
+                             void *grad_query, void *grad_key, void *grad_value, void *workspace, size_t workspace_bytes,
+                             int B, int d, int C, int H, int W, int halo_top, int halo_bottom, int K, int s, int dtype,
+                             void *stream);
 
 /* GroupNorm followed by the 1 x 1 projection that produces the query or the key (reference: sapa_base.py:27-34,
  * sapa_deform.py:35-42 - `self.q(self.norm_y(y))`, `self.k(self.norm_x(x))`), forward only:

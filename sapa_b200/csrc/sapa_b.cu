@@ -544,10 +544,12 @@ int launch_fused_mma(const void *q, const void *k, const void *v, void *out, voi
 
 int tma_wait_timeout_flag();
 int proj_wait_timeout_flag();
+int launch_wait_selftest(cudaStream_t st);
 int gath_wait_timeout_flag();
 // tensor-core transposed aggregation (sapa_gath_mma.cu)
 bool gath_mma_supported(int W, int dtype);
-int launch_gath_mma(const void *hi, const void *wt, void *out, int B, int C, int H, int W, int dtype, cudaStream_t st);
+int launch_gath_mma(const void *hi, const void *wt, void *out, int B, int C, int H, int W, int top, int bottom, int dtype,
+                    cudaStream_t st);
 
 static bool tiled_supported(int K, int s, int dtype) {
     return dtype != SAPA_F64 && s == 2 && (K == 5 || K == 3);
@@ -648,7 +650,7 @@ static int run_gath(const void *hi, const void *wt, void *out, int B, int Cc, in
                     cudaStream_t st) {
     const bool al = all_aligned16(hi, wt, out);
     if (al && K == 5 && s == 2 && gath_mma_supported(W, dtype)) {
-        const int e = launch_gath_mma(hi, wt, out, B, Cc, H, W, dtype, st);
+        const int e = launch_gath_mma(hi, wt, out, B, Cc, H, W, 0, 0, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
     if (al && tiled_supported(K, s, dtype)) {
@@ -675,6 +677,11 @@ int sapa_wait_timeout_flags(void) {
     const int a = tma_wait_timeout_flag(), b = gath_wait_timeout_flag(), c = proj_wait_timeout_flag();
     if (a < 0 || b < 0 || c < 0) return -1;
     return (a ? 1 : 0) | (b ? 2 : 0) | (c ? 4 : 0);
+}
+
+int sapa_selftest_wait_timeout(void *stream) {
+    trace_reset();
+    return launch_wait_selftest(static_cast<cudaStream_t>(stream));
 }
 
 int sapa_qk_forward(const void *query, const void *key, void *out, int B, int d, int H, int W, int K, int s, int dtype,
@@ -815,6 +822,37 @@ int sapa_fused_backward(const void *grad_out, const void *query, const void *key
     }
     if (int e = run_gath(query, dS, grad_key, B, d, H, W, K, s, dtype, st)) return e;       // dKey = gath(Q, dS)
     return run_gath(grad_out, attn, grad_value, B, C, H, W, K, s, dtype, st);               // dV = gath(dOut, A)
+}
+
+// Backward of sapa_fused_forward_slab for one row slab.  The slab's pixels reach `halo_top` / `halo_bottom` rows of key
+// and value that belong to the neighbouring slabs, so the key / value gradients come out in the padded frame: rows
+// [halo_top, halo_top + H) are this slab's own contribution to its own rows, the halo rows are its contribution to the
+// neighbours' edge rows (the caller sends them there and adds what it receives to its own edge rows).
+int sapa_fused_backward_slab(const void *grad_out, const void *query, const void *key, const void *value, const void *attn,
+                             void *grad_query, void *grad_key, void *grad_value, void *workspace, size_t workspace_bytes,
+                             int B, int d, int C, int H, int W, int halo_top, int halo_bottom, int K, int s, int dtype,
+                             void *stream) {
+    const char *fn = "sapa_fused_backward_slab";
+    trace_reset();
+    if (int e = check_common(fn, B, d, H, W, K, s, dtype)) return e;
+    SAPA_REQUIRE(C > 0 && halo_top >= 0 && halo_bottom >= 0, SAPA_ERR_ARGUMENT, "%s: C must be positive, halos non-negative", fn);
+    SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value);
+    SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, grad_query); SAPA_CHECK_PTR(fn, grad_key); SAPA_CHECK_PTR(fn, grad_value);
+    const size_t need = sapa_fused_backward_workspace(B, H, W, K, s, dtype);
+    SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
+                 "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
+    SAPA_REQUIRE(K == 5 && s == 2 && fused_tma_supported(W, dtype) && gath_mma_supported(W, dtype) &&
+                 all_aligned16(grad_out, query, key, value, attn, grad_query, grad_key, grad_value), SAPA_ERR_UNSUPPORTED,
+                 "%s: needs K = 5, s = 2, rows of 16 bytes and 16-byte aligned tensors", fn);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    void *dS = workspace;
+    const int rows = halo_top + H + halo_bottom;
+    // dA = sim(dOut, value slab) -> softmax backward -> dS; dQ = agg(dS, key slab)
+    if (int e = launch_fused_tma(1, grad_out, value, key, grad_query, const_cast<void *>(attn), dS, B, C, d, H, W, rows, halo_top,
+                                 0, H, dtype, st))
+        return e;
+    if (int e = launch_gath_mma(query, dS, grad_key, B, d, H, W, halo_top, halo_bottom, dtype, st)) return e;
+    return launch_gath_mma(grad_out, attn, grad_value, B, C, H, W, halo_top, halo_bottom, dtype, st);
 }
 
 // ------------------------------------------------------------------ backward without any allocation

@@ -43,8 +43,10 @@ __device__ unsigned g_ctas_done[SCHED_SLOTS];
 
 struct Args {
     const void *wt;        // [B, 25, 2H, 2W] window weights (attention map or logit gradients)
-    void *out;             // [B, C, H, W]
-    int B, C, H, W;
+    void *out;             // [B, C, top + H + bottom, W]
+    int B, C, H, W;        // H = low-res rows covered by the high-res inputs
+    int top, Hout;         // row-slab form: the output has `top` extra rows above and Hout = top + H + bottom rows in all
+                           // (the cells of the neighbouring slabs that this slab's pixels reach); 0 and H otherwise
     int tiles_x, tiles_y;
     int sched_slot;
 };
@@ -143,7 +145,7 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
                 p_n = claimed;
             }
             mbar_expect_tx(bar, G::BOX_BYTES);
-            tma_load_4d(ring_addr + p_slot * G::BOX_BYTES, &xmap, bar, 2 * p_x0 - 8, p_it * NCH, 2 * (p_y0 - 2), p_n);
+            tma_load_4d(ring_addr + p_slot * G::BOX_BYTES, &xmap, bar, 2 * p_x0 - 8, p_it * NCH, 2 * (p_y0 - a.top - 2), p_n);
             ++p_issued;
             if (++p_it == nst) { p_it = 0; ++p_ti; }
             if (++p_slot == NSTAGE) { p_slot = 0; p_phase ^= 1; }
@@ -188,16 +190,16 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
             x0 = (tile % a.tiles_x) * COLS; tile /= a.tiles_x;
             const int y0 = (tile % a.tiles_y) * ROWS; tile /= a.tiles_y;
             n = tile;
-            y = y0 + wy;
-            store_ok = y < a.H && x0 + 2 * t < a.W;
-            o_ptr = static_cast<T *>(a.out) + ((size_t)n * a.C + g) * a.H * a.W + (size_t)y * a.W + x0 + 2 * t;
+            y = y0 + wy;                  // output row in the (padded) output frame; the input frame is `top` rows further up
+            store_ok = y < a.Hout && x0 + 2 * t < a.W;
+            o_ptr = static_cast<T *>(a.out) + ((size_t)n * a.C + g) * a.Hout * a.W + (size_t)y * a.W + x0 + 2 * t;
             // weights of the tile: parent row yp = y - 2 + j uses window row 4 - j; the parent of box pixel b is
             // x0 - 4 + b/2 and reaches column x0 + g through window column g + 6 - b/2
             const T *wimg = static_cast<const T *>(a.wt) + (size_t)n * 25 * hi_plane;
 #pragma unroll
             for (int j = 0; j < 5; ++j) {
-                const int yp = y - 2 + j, hy = 2 * yp + r;
-                const bool row_in = yp >= 0 && yp < a.H && y < a.H && x0 + g < a.W;
+                const int yp = y - a.top - 2 + j, hy = 2 * yp + r;
+                const bool row_in = yp >= 0 && yp < a.H && y < a.Hout && x0 + g < a.W;
 #pragma unroll
                 for (int kg = 0; kg < 3; ++kg) {
                     if constexpr (F32) {
@@ -288,11 +290,11 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
                 if (store_ok) {
-                    T *o = o_ptr + (size_t)(c0 + 16 * b) * a.H * a.W;
+                    T *o = o_ptr + (size_t)(c0 + 16 * b) * a.Hout * a.W;
 #pragma unroll
                     for (int half = 0; half < 2; ++half)
                         if (c0 + 16 * b + 8 * half + g < a.C) {
-                            T *oh = o + (size_t)(8 * half) * a.H * a.W;
+                            T *oh = o + (size_t)(8 * half) * a.Hout * a.W;
                             if constexpr (F32) *reinterpret_cast<float2 *>(oh) = make_float2(acc[b][0][2 * half], acc[b][0][2 * half + 1]);
                             else *reinterpret_cast<unsigned *>(oh) = pack_pair(T(), acc[b][0][2 * half], acc[b][0][2 * half + 1]);
                         }
@@ -309,7 +311,7 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
 static std::atomic<unsigned> g_next_sched_slot{0}, g_next_captured_slot{0};
 
 template <typename T>
-static int launch(const void *hi, const void *wt, void *out, int B, int C, int H, int W, cudaStream_t st) {
+static int launch(const void *hi, const void *wt, void *out, int B, int C, int H, int W, int top, int bottom, cudaStream_t st) {
     using G = Geo<T>;
     const char *name = "sapa_gath_mma_kernel";
     CUtensorMap xmap;
@@ -322,9 +324,9 @@ static int launch(const void *hi, const void *wt, void *out, int B, int C, int H
         return SAPA_ERR_UNSUPPORTED;
     }
     Args a{};
-    a.wt = wt; a.out = out; a.B = B; a.C = C; a.H = H; a.W = W;
+    a.wt = wt; a.out = out; a.B = B; a.C = C; a.H = H; a.W = W; a.top = top; a.Hout = top + H + bottom;
     a.tiles_x = ceil_div(W, COLS);
-    a.tiles_y = ceil_div(H, ROWS);
+    a.tiles_y = ceil_div(a.Hout, ROWS);
     const long long nblocks = (long long)B * a.tiles_x * a.tiles_y;
     if (nblocks > 0x7fffffffLL) {
         set_error("too many tiles");
@@ -358,10 +360,12 @@ bool gath_mma_supported(int W, int dtype) {
 }
 
 // Returns SAPA_ERR_UNSUPPORTED when the tensor map cannot be built (the caller then uses the FP32-pipe kernel).
-int launch_gath_mma(const void *hi, const void *wt, void *out, int B, int C, int H, int W, int dtype, cudaStream_t st) {
-    if (dtype == SAPA_F32) return gmma::launch<float>(hi, wt, out, B, C, H, W, st);
-    if (dtype == SAPA_F16) return gmma::launch<__half>(hi, wt, out, B, C, H, W, st);
-    if (dtype == SAPA_BF16) return gmma::launch<__nv_bfloat16>(hi, wt, out, B, C, H, W, st);
+// `top` / `bottom`: extra output rows above / below the H rows under the inputs (row-slab backward), 0 otherwise.
+int launch_gath_mma(const void *hi, const void *wt, void *out, int B, int C, int H, int W, int top, int bottom, int dtype,
+                    cudaStream_t st) {
+    if (dtype == SAPA_F32) return gmma::launch<float>(hi, wt, out, B, C, H, W, top, bottom, st);
+    if (dtype == SAPA_F16) return gmma::launch<__half>(hi, wt, out, B, C, H, W, top, bottom, st);
+    if (dtype == SAPA_BF16) return gmma::launch<__nv_bfloat16>(hi, wt, out, B, C, H, W, top, bottom, st);
     return SAPA_ERR_UNSUPPORTED;
 }
 

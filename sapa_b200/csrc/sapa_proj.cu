@@ -42,7 +42,16 @@ constexpr int TILE_PX = 128;
 constexpr int EPI_WARPS = 4, TMA_WARP = 4, MMA_WARP = 5, W_WARP = 6, SPLIT_WARP0 = 7, SPLIT_WARPS = 4;
 constexpr int THREADS = (SPLIT_WARP0 + SPLIT_WARPS) * 32;
 constexpr int Y_STAGE = 16384;           // bytes of activations per stage: 128 px x (128 B / esize) channels
-constexpr int MAX_SLOTS = 8;              // per ring
+#ifndef SAPA_PROJ_MAX_SLOTS
+#define SAPA_PROJ_MAX_SLOTS 8
+#endif
+#ifndef SAPA_PROJ_NO_F32
+#define SAPA_PROJ_NO_F32 2
+#endif
+#ifndef SAPA_PROJ_NO_16
+#define SAPA_PROJ_NO_16 4
+#endif
+constexpr int MAX_SLOTS = 8;              // per ring (barrier layout)
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int STAT_THREADS = 256, MAX_SPLIT = 64, MAX_GROUPS = 256;
 
@@ -412,9 +421,9 @@ static bool make_plan(Plan &p, int B, int C, int HW, int d, int groups, int dtyp
     // operand slots: split activations + W' blocks (float32), W' block only (16-bit); the rest goes to the activation ring
     const size_t op = p.esize == 4 ? 2 * (size_t)Y_STAGE + 2 * (size_t)d * 128 : (size_t)d * 128;
     const size_t fixed = 1024 + 64 * 8;      // alignment slack + barriers
-    p.no = p.esize == 4 ? 2 : 4;
+    p.no = p.esize == 4 ? SAPA_PROJ_NO_F32 : SAPA_PROJ_NO_16;
     if (fixed + p.no * op + 2 * (size_t)Y_STAGE > SMEM_LIMIT) return false;
-    p.nx = (int)std::min<size_t>(MAX_SLOTS, (SMEM_LIMIT - fixed - p.no * op) / Y_STAGE);
+    p.nx = (int)std::min<size_t>(SAPA_PROJ_MAX_SLOTS, (SMEM_LIMIT - fixed - p.no * op) / Y_STAGE);
     p.smem = fixed + p.no * op + (size_t)p.nx * Y_STAGE;
     p.tmem_cols = 32;
     while (p.tmem_cols < 2 * d) p.tmem_cols *= 2;

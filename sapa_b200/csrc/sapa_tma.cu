@@ -929,6 +929,25 @@ int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void
 #undef SAPA_TMA_LAUNCH16
 }
 
+// One CTA waits, with a short limit, on a shared-memory barrier that nothing ever signals: the bounded wait gives up,
+// the kernel raises g_wait_timeout exactly as the production kernels would and returns normally.
+__global__ void sapa_wait_selftest_kernel(int tries) {
+    __shared__ __align__(8) unsigned long long bar;
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(&bar);
+    if (threadIdx.x == 0) {
+        tmau::mbar_init(addr, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        bool done = false;
+        for (int i = 0; i < tries && !done; ++i) done = tmau::mbar_try_wait(addr, 0);
+        if (!done) atomicExch(&tma::g_wait_timeout, 1);
+    }
+}
+
+int launch_wait_selftest(cudaStream_t st) {
+    sapa_wait_selftest_kernel<<<1, 32, 0, st>>>(64);
+    return check_launch("sapa_wait_selftest_kernel");
+}
+
 // 1 if a bounded mbarrier wait of the TMA kernels gave up on the current device since the last query (synchronises the
 // device).  A CTA that gives up leaves without taking part in the last-CTA reset of its scheduler pair, so a raised
 // flag also means that pair may be dirty: reading a raised flag clears it and zeroes every scheduler pair.

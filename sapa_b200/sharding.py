@@ -34,6 +34,8 @@ def check_row_split(local_rows: int, halo: int, group=None) -> None:
     """Every rank must own at least ``halo`` rows (a halo comes from the direct neighbour only).  The decision is
     taken from the shares of ALL ranks, so that either every rank raises or none does: a rank that raised alone
     would leave its neighbour waiting in a receive."""
+    if not dist.is_initialized():
+        return
     world = dist.get_world_size(group)
     if world == 1 or halo == 0:
         return
@@ -82,6 +84,44 @@ def _exchange_into(padded, halo: int, group=None) -> None:
         c0 += c
 
 
+def _reduce_halo_grads(padded, halo: int, group=None) -> None:
+    """Backward counterpart of :func:`_exchange_into` for gradients in the padded frame ``[B, C_i, halo + Hl + halo, W]``:
+    the halo rows hold this rank's contribution to the neighbours' edge rows.  They are sent to the neighbours (one
+    message each) and what arrives from them is added to this rank's own first / last ``halo`` rows, in place."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    if halo == 0 or world == 1:
+        return
+    first = padded[0]
+    B, _, Hp, W = first.shape
+    Hl = Hp - 2 * halo
+    chans = [t.size(1) for t in padded]
+    ctot = sum(chans)
+    to_global = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
+
+    def pack(lo: int) -> torch.Tensor:
+        return torch.cat([t[:, :, lo:lo + halo, :] for t in padded], dim=1).contiguous()
+
+    ops, from_up, from_down = [], None, None
+    if rank > 0:
+        from_up = first.new_empty((B, ctot, halo, W))
+        ops.append(dist.P2POp(dist.isend, pack(0), to_global(rank - 1), group))           # my top halo -> its last rows
+        ops.append(dist.P2POp(dist.irecv, from_up, to_global(rank - 1), group))
+    if rank < world - 1:
+        from_down = first.new_empty((B, ctot, halo, W))
+        ops.append(dist.P2POp(dist.isend, pack(halo + Hl), to_global(rank + 1), group))   # my bottom halo -> its first rows
+        ops.append(dist.P2POp(dist.irecv, from_down, to_global(rank + 1), group))
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    c0 = 0
+    for p, c in zip(padded, chans):
+        if from_up is not None:
+            p[:, :, halo:2 * halo, :] += from_up[:, c0:c0 + c]
+        if from_down is not None:
+            p[:, :, Hl:Hl + halo, :] += from_down[:, c0:c0 + c]
+        c0 += c
+
+
 def exchange_row_halo(tensors, halo: int, group=None):
     """Pad each local slab [B,C,Hl,W] to [B,C,halo+Hl+halo,W] with rows of the neighbouring ranks.
 
@@ -112,7 +152,12 @@ class RowSlab:
          unpack into the halo rows of the padded buffers),
       2. computes, on the caller's stream, the output rows whose windows stay inside the rank's own rows,
       3. waits for the exchange and computes the top and bottom bands.
-    The result equals the matching rows of the unsharded ``sapa_fused`` bit for bit.  Forward only.
+    The result equals the matching rows of the unsharded ``sapa_fused`` bit for bit.
+
+    :meth:`backward` (after a ``forward(..., keep_attn=True)``) returns the gradients of the rank's query, key and value
+    rows: the slab backward kernel produces the key / value gradients in the padded frame, the halo rows (this rank's
+    contribution to its neighbours' edge rows) travel to the neighbours and what arrives is added to the rank's own
+    edge rows - a 2 x r row reduction per step.
     """
 
     BAND = 4          # low-res rows per border band (a multiple of the kernels' tile heights, >= the halo)
@@ -133,17 +178,24 @@ class RowSlab:
         self.value = self.value_padded[:, :, self.halo:self.halo + local_rows, :]
         self._side = torch.cuda.Stream(device=device) if torch.device(device).type == "cuda" else None
         self._halo_done = torch.cuda.Event() if self._side is not None else None
+        self.attn = None            # [B, K*K, s*Hl, s*W] of the last forward(keep_attn=True)
 
     def _launch(self, query, out, row_begin, row_end):
         from . import _lib
-        return _lib.call("sapa_fused_forward_slab_rows", out.device, query, self.key_padded, self.value_padded, out, None,
+        return _lib.call("sapa_fused_forward_slab_rows", out.device, query, self.key_padded, self.value_padded, out, self.attn,
                          self.B, self.d, self.C, self.Hl, self.W, self.halo, self.halo, row_begin, row_end, self.K, self.s,
                          _lib.dtype_code(out), allow_unsupported=True)
 
-    def forward(self, query, out=None):
-        """``query`` [B, d, s*Hl, s*W] -> ``out`` [B, C, s*Hl, s*W] (allocated when not given)."""
+    def forward(self, query, out=None, keep_attn=False):
+        """``query`` [B, d, s*Hl, s*W] -> ``out`` [B, C, s*Hl, s*W] (allocated when not given).  ``keep_attn`` stores the
+        attention map of the slab for :meth:`backward`."""
         from . import _lib
         s, Hl = self.s, self.Hl
+        if keep_attn and self.attn is None:
+            self.attn = torch.empty((self.B, self.K * self.K, s * Hl, s * self.W), dtype=self.value_padded.dtype,
+                                    device=self.value_padded.device)
+        elif not keep_attn:
+            self.attn = None
         if out is None:
             out = torch.empty((self.B, self.C, s * Hl, s * self.W), dtype=self.value_padded.dtype, device=query.device)
         query = _lib.aligned(query.contiguous())
@@ -168,6 +220,28 @@ class RowSlab:
         if status != 0:
             raise RuntimeError("sapa_fused_forward_slab_rows: " + _lib.lib().sapa_last_error().decode("utf-8", "replace"))
         return out
+
+
+    def backward(self, grad_out, query):
+        """Gradients ``(grad_query, grad_key, grad_value)`` of this rank's rows from ``grad_out`` [B, C, s*Hl, s*W]; needs
+        the attention map of ``forward(query, keep_attn=True)`` and the same key / value still in the slab."""
+        from . import _lib
+        if self.attn is None:
+            raise RuntimeError("RowSlab.backward needs forward(..., keep_attn=True) first")
+        query, grad_out = _lib.aligned(query.contiguous()), _lib.aligned(grad_out.contiguous())
+        code = _lib.dtype_code(grad_out)
+        grad_query = torch.empty_like(query)
+        grad_key = torch.empty_like(self.key_padded)
+        grad_value = torch.empty_like(self.value_padded)
+        nbytes = _lib.fused_backward_workspace(self.B, self.Hl, self.W, self.K, self.s, code)
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=grad_out.device)
+        _lib.call("sapa_fused_backward_slab", grad_out.device, grad_out, query, self.key_padded, self.value_padded, self.attn,
+                  grad_query, grad_key, grad_value, workspace, nbytes, self.B, self.d, self.C, self.Hl, self.W, self.halo,
+                  self.halo, self.K, self.s, code)
+        if dist.is_initialized():
+            _reduce_halo_grads([grad_key, grad_value], self.halo, self.group)
+        own = slice(self.halo, self.halo + self.Hl)
+        return grad_query, grad_key[:, :, own, :], grad_value[:, :, own, :]
 
 
 def sapa_fused_row_sharded(query, key, value, kernel_size=5, scale_factor=2, group=None):

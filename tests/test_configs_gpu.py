@@ -125,3 +125,43 @@ def test_config5b_2048_square_row_slabs_with_real_halos_vs_oracle(sp, oracle):
     assert band(0, 6) < 1e-2
     assert band(half - 4, half + 4) < 1e-2
     assert band(H - 6, H) < 1e-2
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_row_slab_backward_of_two_slabs_sums_to_the_unsharded_gradients(dtype, tol):
+    """sapa_fused_backward_slab on the two halves of an image (halos copied from the other half, as the exchange would):
+    grad_query of each half equals the unsharded rows bit for bit; the key / value gradients, with the halo rows of each
+    half added to the other half's edge rows, equal the unsharded gradients to rounding."""
+    import sapa_b200
+    from sapa_b200 import _lib, sharding
+    dev = torch.device("cuda:0")
+    B, d, C, H, W, K, s, r = 2, 32, 48, 24, 40, 5, 2, 2
+    g = torch.Generator().manual_seed(23)
+    q, k, v, go = (torch.randn(*sh, generator=g).to(dev, dtype) for sh in
+                   ((B, d, s * H, s * W), (B, d, H, W), (B, C, H, W), (B, C, s * H, s * W)))
+    qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+    gq, gk, gv = torch.autograd.grad(sapa_b200.sapa_fused(qf, kf, vf, K, s), (qf, kf, vf), go)
+    kp, vp = (torch.nn.functional.pad(t, (0, 0, r, r)) for t in (k, v))
+    sum_k, sum_v = torch.zeros_like(kp, dtype=torch.float32), torch.zeros_like(vp, dtype=torch.float32)
+    hl = H // 2
+    for half in range(2):
+        rows, hi = slice(half * hl, (half + 1) * hl), slice(s * half * hl, s * (half + 1) * hl)
+        slab = sharding.RowSlab(B, d, C, hl, W, dtype, dev, K, s)
+        slab.key_padded.copy_(kp[:, :, half * hl:half * hl + hl + 2 * r])
+        slab.value_padded.copy_(vp[:, :, half * hl:half * hl + hl + 2 * r])
+        ql = q[:, :, hi].contiguous()
+        out = slab.forward(ql, keep_attn=True)
+        code = _lib.dtype_code(ql)
+        mq = torch.empty_like(ql)
+        mk, mv = torch.empty_like(slab.key_padded), torch.empty_like(slab.value_padded)
+        nb = _lib.fused_backward_workspace(B, hl, W, K, s, code)
+        ws = torch.empty(nb, dtype=torch.uint8, device=dev)
+        _lib.call("sapa_fused_backward_slab", dev, go[:, :, hi].contiguous(), ql, slab.key_padded, slab.value_padded, slab.attn,
+                  mq, mk, mv, ws, nb, B, d, C, hl, W, r, r, K, s, code)
+        assert _lib.last_kernels() == [f"sapa_tma_fused_{'f32' if dtype == torch.float32 else '16'}_kernel<bwd>",
+                                       "sapa_gath_mma_kernel", "sapa_gath_mma_kernel"]
+        assert torch.equal(mq, gq[:, :, hi])
+        sum_k[:, :, half * hl:half * hl + hl + 2 * r] += mk.float()
+        sum_v[:, :, half * hl:half * hl + hl + 2 * r] += mv.float()
+    for got, want in ((sum_k[:, :, r:r + H], gk), (sum_v[:, :, r:r + H], gv)):
+        assert float((got - want.float()).abs().max()) <= tol * float(want.float().abs().max())

@@ -35,7 +35,25 @@ def _worker(rank, world, port, dtype_name, ret):
         mine = sharding.sapa_fused_row_sharded(q[:, :, s * rows.start:s * rows.stop].contiguous(),
                                                k[:, :, rows].contiguous(), v[:, :, rows].contiguous(), K, s)
         torch.cuda.synchronize()
-        ret[rank] = bool(torch.equal(mine, full[:, :, s * rows.start:s * rows.stop]))
+        ok = bool(torch.equal(mine, full[:, :, s * rows.start:s * rows.stop]))
+        # backward of the row-sharded op: the rank's rows of the unsharded gradients (the edge rows of the key / value
+        # gradients are sums over two ranks, so they agree to rounding, everything else bit for bit)
+        go = torch.randn(B, C, s * H, s * W, generator=g).to(dev, dtype)
+        qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+        gq, gk, gv = torch.autograd.grad(sapa_b200.sapa_fused(qf, kf, vf, K, s), (qf, kf, vf), go)
+        slab = sharding.RowSlab(B, d, C, rows.stop - rows.start, W, dtype, dev, K, s)
+        slab.key.copy_(k[:, :, rows]); slab.value.copy_(v[:, :, rows])
+        hi = slice(s * rows.start, s * rows.stop)
+        ql = q[:, :, hi].contiguous()
+        slab.forward(ql, keep_attn=True)
+        mq, mk, mv = slab.backward(go[:, :, hi].contiguous(), ql)
+        torch.cuda.synchronize()
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+
+        def close(a, b):
+            return float((a.float() - b.float()).abs().max()) <= tol * float(b.float().abs().max())
+        ok = ok and bool(torch.equal(mq, gq[:, :, hi])) and close(mk, gk[:, :, rows]) and close(mv, gv[:, :, rows])
+        ret[rank] = ok
     finally:
         dist.destroy_process_group()
 

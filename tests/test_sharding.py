@@ -117,3 +117,39 @@ def test_resident_slab_exchanges_only_its_halo_rows_in_place():
         ret = mgr.dict()
         mp.spawn(_worker_resident, args=(3, port, ret), nprocs=3, join=True)
         assert dict(ret) == {0: True, 1: True, 2: True}
+
+
+def _worker_reduce(rank, world, port, halo, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # Every rank holds gradient contributions in its padded frame; the sum over the ranks, each placed at its
+        # position in the padded full image, is what the reduction must reproduce on the ranks' own rows.
+        H, W, hl = 4 * world, 3, 4
+        g = torch.Generator().manual_seed(11)
+        contrib = [[torch.randn(2, c, hl + 2 * halo, W, generator=g) for c in (3, 5)] for _ in range(world)]
+        mine = [t.clone() for t in contrib[rank]]
+        sharding._reduce_halo_grads(mine, halo)
+        ok = True
+        for ti, c in enumerate((3, 5)):
+            full = torch.zeros(2, c, H + 2 * halo, W)
+            for r in range(world):
+                full[:, :, r * hl:r * hl + hl + 2 * halo] += contrib[r][ti]
+            want = full[:, :, halo + rank * hl:halo + rank * hl + hl]
+            got = mine[ti][:, :, halo:halo + hl]
+            ok = ok and bool(torch.allclose(got, want, atol=1e-6))
+        ret[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,halo", [(2, 2), (3, 2), (3, 1)])
+def test_halo_gradient_reduction_gloo(world, halo):
+    """Backward of the halo exchange: halo rows of the padded gradients go to the neighbours and are added to their edge
+    rows; the ranks' own rows then hold the sum of every rank's contribution."""
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_reduce, args=(world, port, halo, ret), nprocs=world, join=True)
+        assert dict(ret) == {r: True for r in range(world)}

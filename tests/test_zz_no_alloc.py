@@ -63,3 +63,23 @@ def test_static_scratch_rejects_problems_beyond_its_capacity():
     t = torch.zeros(16, device=DEV)                           # never touched: the size check comes first
     with pytest.raises(RuntimeError, match="built-in buffer"):
         _lib.call("sapa_fused_backward_static", t.device, t, t, t, t, t, t, t, t, B, d, C, H, W, K, s, 0)
+
+
+def test_zzz_bounded_wait_gives_up_and_the_library_recovers():
+    """A kernel whose bounded barrier wait runs out (a barrier that nothing signals, a limit of a few dozen tries) raises
+    the device flag and returns; reading the flag clears it, and the next fused forward is correct."""
+    import torch
+    import sapa_b200
+    from sapa_b200 import _lib
+    dev = torch.device("cuda:0")
+    assert _lib.wait_timeout_flags(dev) == 0
+    _lib.call("sapa_selftest_wait_timeout", dev)
+    assert _lib.last_kernels() == ["sapa_wait_selftest_kernel"]
+    assert _lib.wait_timeout_flags(dev) == 1          # bit 0: the tensor-map kernels' flag
+    assert _lib.wait_timeout_flags(dev) == 0          # reading cleared it (and reset the tile schedulers)
+    g = torch.Generator().manual_seed(5)
+    q, k, v = torch.randn(1, 16, 16, 32, generator=g), torch.randn(1, 16, 8, 16, generator=g), torch.randn(1, 32, 8, 16, generator=g)
+    out = sapa_b200.sapa_fused(q.to(dev), k.to(dev), v.to(dev), 5, 2)
+    ref = sapa_b200.av(torch.softmax(sapa_b200.qk(q.to(dev), k.to(dev), 5, 2), dim=1), v.to(dev), 5, 2)
+    assert _lib.wait_timeout_flags(dev) == 0
+    assert float((out - ref).abs().max()) < 1e-5
