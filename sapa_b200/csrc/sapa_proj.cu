@@ -42,16 +42,8 @@ constexpr int TILE_PX = 128;
 constexpr int EPI_WARPS = 4, TMA_WARP = 4, MMA_WARP = 5, W_WARP = 6, SPLIT_WARP0 = 7, SPLIT_WARPS = 4;
 constexpr int THREADS = (SPLIT_WARP0 + SPLIT_WARPS) * 32;
 constexpr int Y_STAGE = 16384;           // bytes of activations per stage: 128 px x (128 B / esize) channels
-#ifndef SAPA_PROJ_MAX_SLOTS
-#define SAPA_PROJ_MAX_SLOTS 8
-#endif
-#ifndef SAPA_PROJ_NO_F32
-#define SAPA_PROJ_NO_F32 2
-#endif
-#ifndef SAPA_PROJ_NO_16
-#define SAPA_PROJ_NO_16 4
-#endif
-constexpr int MAX_SLOTS = 8;              // per ring (barrier layout)
+constexpr int MAX_SLOTS = 8;              // slots per ring
+constexpr int OP_SLOTS_F32 = 2, OP_SLOTS_16 = 4;     // operand ring depth (deeper rings measured no faster)
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int STAT_THREADS = 256, MAX_SPLIT = 64, MAX_GROUPS = 256;
 
@@ -302,20 +294,28 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
 }
 
 // ---------------------------------------------------------------------------------- GroupNorm statistics and the fold
-template <typename T> __device__ __forceinline__ void load4(const T *p, float (&v)[4]);
-template <> __device__ __forceinline__ void load4<float>(const float *p, float (&v)[4]) {
-    const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+// one 16-byte load: 4 float32 or 8 16-bit elements, widened to float
+template <typename T> struct Vec16 { static constexpr int N = 16 / (int)sizeof(T); };
+__device__ __forceinline__ void load16(const float *p, float (&v)[4]) {
+    const float4 t = __ldcs(reinterpret_cast<const float4 *>(p));
     v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
 }
-template <> __device__ __forceinline__ void load4<__half>(const __half *p, float (&v)[4]) {
-    const uint2 t = __ldg(reinterpret_cast<const uint2 *>(p));
-    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&t.x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&t.y));
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+__device__ __forceinline__ void load16(const __half *p, float (&v)[8]) {
+    const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(p));
+    const unsigned w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+        v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
 }
-template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16 *p, float (&v)[4]) {
-    const uint2 t = __ldg(reinterpret_cast<const uint2 *>(p));
-    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
-    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+__device__ __forceinline__ void load16(const __nv_bfloat16 *p, float (&v)[8]) {
+    const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(p));
+    const unsigned w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
 }
 
 __device__ __forceinline__ double block_sum(double v, double *scratch) {
@@ -332,25 +332,32 @@ __device__ __forceinline__ double block_sum(double v, double *scratch) {
 }
 
 // grid (nsplit, B * groups): block (s, bg) sums its slice of the n = (C / groups) * HW contiguous elements of group bg
+// (16-byte loads, four in flight per thread; float partial sums of at most 32 elements, float64 beyond)
 template <typename T>
 __global__ void __launch_bounds__(STAT_THREADS) gn_partial_kernel(const T *__restrict__ x, double2 *__restrict__ partial, long long n, int nsplit) {
+    constexpr int VN = Vec16<T>::N;
     __shared__ double scratch[STAT_THREADS / 32];
     const T *base = x + (size_t)blockIdx.y * n;
-    const long long quads = n / 4, per = (quads + nsplit - 1) / nsplit;
-    const long long q0 = blockIdx.x * per, q1 = min(quads, q0 + per);
+    const long long vecs = n / VN, per = (vecs + nsplit - 1) / nsplit;
+    const long long q0 = blockIdx.x * per, q1 = min(vecs, q0 + per);
     double s = 0, ss = 0;
     for (long long q = q0 + threadIdx.x; q < q1; q += 4 * STAT_THREADS) {
-        float fs = 0.f, fss = 0.f;
+        float v[4][VN];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const long long qq = q + (long long)u * STAT_THREADS;
             if (qq < q1) {
-                float v[4];
-                load4(base + qq * 4, v);
-                fs += (v[0] + v[1]) + (v[2] + v[3]);
-                fss += (v[0] * v[0] + v[1] * v[1]) + (v[2] * v[2] + v[3] * v[3]);
+                load16(base + qq * VN, v[u]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VN; ++i) v[u][i] = 0.f;
             }
         }
+        float fs = 0.f, fss = 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int i = 0; i < VN; ++i) { fs += v[u][i]; fss += v[u][i] * v[u][i]; }
         s += fs; ss += fss;
     }
     const double ts = block_sum(s, scratch), tss = block_sum(ss, scratch);
@@ -417,13 +424,13 @@ static bool make_plan(Plan &p, int B, int C, int HW, int d, int groups, int dtyp
     p.esize = (int)dtype_size(dtype);
     if (B <= 0 || C <= 0 || HW <= 0 || d < 16 || d > 256 || d % 16 != 0) return false;
     if (((size_t)HW * p.esize) % 16 != 0 || ((size_t)C * p.esize) % 16 != 0) return false;     // tensor-map strides
-    if (groups < 0 || groups > MAX_GROUPS || (groups > 0 && (C % groups != 0 || ((size_t)(C / groups) * HW) % 4 != 0))) return false;
+    if (groups < 0 || groups > MAX_GROUPS || (groups > 0 && (C % groups != 0 || ((size_t)(C / groups) * HW * p.esize) % 16 != 0))) return false;
     // operand slots: split activations + W' blocks (float32), W' block only (16-bit); the rest goes to the activation ring
     const size_t op = p.esize == 4 ? 2 * (size_t)Y_STAGE + 2 * (size_t)d * 128 : (size_t)d * 128;
     const size_t fixed = 1024 + 64 * 8;      // alignment slack + barriers
-    p.no = p.esize == 4 ? SAPA_PROJ_NO_F32 : SAPA_PROJ_NO_16;
+    p.no = p.esize == 4 ? OP_SLOTS_F32 : OP_SLOTS_16;
     if (fixed + p.no * op + 2 * (size_t)Y_STAGE > SMEM_LIMIT) return false;
-    p.nx = (int)std::min<size_t>(SAPA_PROJ_MAX_SLOTS, (SMEM_LIMIT - fixed - p.no * op) / Y_STAGE);
+    p.nx = (int)std::min<size_t>(MAX_SLOTS, (SMEM_LIMIT - fixed - p.no * op) / Y_STAGE);
     p.smem = fixed + p.no * op + (size_t)p.nx * Y_STAGE;
     p.tmem_cols = 32;
     while (p.tmem_cols < 2 * d) p.tmem_cols *= 2;

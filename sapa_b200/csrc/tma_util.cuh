@@ -123,7 +123,8 @@ inline int &last_encode_result() {
 
 // 4-D map over a dense NCHW tensor seen as (x, channel, y, image); box = box_w columns x box_ch channels x box_rows rows
 inline bool make_nchw_map(CUtensorMap *map, const void *base, int width, int height, int channels, int images, int box_w,
-                          int box_ch, int box_rows, CUtensorMapDataType type, int esize, CUtensorMapSwizzle swizzle) {
+                          int box_ch, int box_rows, CUtensorMapDataType type, int esize, CUtensorMapSwizzle swizzle,
+                          CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
     EncodeTiledFn encode = encode_tiled_fn();
     if (encode == nullptr) return false;
     const cuuint64_t dims[4] = {(cuuint64_t)width, (cuuint64_t)channels, (cuuint64_t)height, (cuuint64_t)images};
@@ -132,14 +133,14 @@ inline bool make_nchw_map(CUtensorMap *map, const void *base, int width, int hei
     const cuuint32_t box[4] = {(cuuint32_t)box_w, (cuuint32_t)box_ch, (cuuint32_t)box_rows, 1u};
     const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
     CUresult r = encode(map, type, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        swizzle, promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_ERROR_INVALID_CONTEXT) {
         // The encoder is a driver entry point and wants a current context.  A thread that has made no runtime call
         // yet (PyTorch's autograd worker running a backward is the usual case) has none bound: cudaFree(nullptr) is
         // the runtime's no-op that binds the device's primary context to the calling thread.  Then once more.
         cudaFree(nullptr);
         r = encode(map, type, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }
     last_encode_result() = (int)r;
     return r == CUDA_SUCCESS;
