@@ -10,18 +10,23 @@
 // activation tensor of the unfused sequence (one write + one read of the size of x) never exists.
 //
 // GEMM kernel (tcgen05 / TMEM; one CTA per SM, 128-pixel tiles):
-//   D[128 px x d] (+)= A[128 px x k] * B[k x d],  A = x^T (pixels contiguous in NCHW: an "MN-major" operand), B = W' (K-major)
+//   D[128 px x d] (+)= A[128 px x k] * B[k x d],  A = x^T, B = W' (K-major: channels contiguous)
 //   * warp 4 (one lane): TMA producer of the activations, warp 6 (one lane): TMA producer of the W' blocks.  A stage =
-//     128 px x (128 B / esize) channels of x as boxes of one 128-byte pixel
-//     row per channel (128-byte swizzle: exactly the canonical MN-major operand layout; 16-byte chunks for 16-bit types,
-//     32-byte chunks for tf32) plus the
+//     128 px x (128 B / esize) channels of x as boxes of one 128-byte pixel row per channel (128-byte swizzle) plus the
 //     matching d x 128 B block of W' (canonical K-major layout).
-//   * float32 only, warps 7-10: 3xTF32 split.  The tensor core reads tf32 (the upper 19 bits); the product is evaluated as
-//     hi*hi + lo*hi + hi*lo with hi = x & 0xffffe000, lo = x - hi (exact), which gives float32 accuracy (1e-6).  The
-//     warps copy a landed ring slot into an operand slot as hi and lo and release the ring slot at once (so up to
-//     128 KB of loads stay in flight per SM whatever the MMAs do); W' arrives already split.
+//   * 16-bit types: the landed boxes ARE the canonical operand layout for an operand whose M dimension is the contiguous
+//     one ("MN-major"), and the tensor core reads them in place.
+//   * float32, warps 7-14: 3xTF32 split AND transposition.  The tensor core reads tf32 (the upper 19 bits); the product
+//     is evaluated as hi*hi + lo*hi + hi*lo with hi = x & 0xffffe000, lo = x - hi (exact): float32 accuracy (1e-6).  The
+//     warps read a landed ring slot (lane = channel, 16 bytes = 4 pixels) and write hi and lo into an operand slot as
+//     K-major rows (row = pixel, 128 bytes = the stage's 32 channels, 128-byte swizzle): both sides are free of bank
+//     conflicts and the ring slot is released at once.  (The landed boxes can also be fed as an MN-major tf32 operand:
+//     that needs the 128-byte swizzle of 32-byte chunks - CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, descriptor layout type 1,
+//     4-row atoms; with the ordinary swizzle the product is wrong.  It was built first, is as accurate and measured the
+//     same speed.)  W' arrives already split.
 //   * warp 5 (one lane): issues tcgen05.mma (M = 128, N = d, K = 32 bytes) into one of two TMEM accumulators, frees a
-//     stage with tcgen05.commit, signals the epilogue with another commit.
+//     stage with tcgen05.commit, signals the epilogue with another commit.  Its own instruction latency is on the
+//     critical path (one thread, 12 MMAs per float32 stage): ring positions and descriptors advance by additions only.
 //   * warps 0-3: epilogue.  tcgen05.ld (lane = pixel, column = output channel), add bias', store: for a fixed output
 //     channel the 32 lanes of a warp write 32 consecutive pixels.  Runs under the MMAs of the next tile.
 // Tiles walk the images from the last to the first: the statistics pass has just read them in ascending order, so the
@@ -39,7 +44,7 @@ namespace proj {
 using namespace tmau;
 
 constexpr int TILE_PX = 128;
-constexpr int EPI_WARPS = 4, TMA_WARP = 4, MMA_WARP = 5, W_WARP = 6, SPLIT_WARP0 = 7, SPLIT_WARPS = 4;
+constexpr int EPI_WARPS = 4, TMA_WARP = 4, MMA_WARP = 5, W_WARP = 6, SPLIT_WARP0 = 7, SPLIT_WARPS = 8;
 constexpr int THREADS = (SPLIT_WARP0 + SPLIT_WARPS) * 32;
 constexpr int Y_STAGE = 16384;           // bytes of activations per stage: 128 px x (128 B / esize) channels
 constexpr int MAX_SLOTS = 8;              // slots per ring
@@ -73,14 +78,20 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
+// One tcgen05.mma.  The 64-bit shared-memory descriptors are passed as their low words (start address and leading
+// offset; the part that changes from instruction to instruction) plus the high word all operands of this kernel share:
+// the issuing thread is a single thread whose own instruction latency bounds the MMA rate, so it must spend only a
+// handful of instructions per MMA.
 template <bool TF32>
-__device__ __forceinline__ void tc_mma(unsigned d_tmem, uint64_t a_desc, uint64_t b_desc, unsigned idesc, unsigned accumulate) {
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned a_lo, unsigned b_lo, unsigned desc_hi, unsigned idesc, unsigned accumulate) {
     if (TF32)
-        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n"
-                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        asm volatile("{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %5, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+                     " tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n}\n"
+                     ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
     else
-        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        asm volatile("{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %5, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+                     " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}\n"
+                     ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 // 16 consecutive accumulator columns of this thread's lane
 __device__ __forceinline__ void tc_ld16(unsigned taddr, unsigned (&r)[16]) {
@@ -91,14 +102,15 @@ __device__ __forceinline__ void tc_ld16(unsigned taddr, unsigned (&r)[16]) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
-// Shared-memory matrix descriptor: start address, leading and stride byte offsets in 16-byte units, descriptor version 1
-// (bits 46-47), layout type in bits 61-63: 2 = 128-byte swizzle of 16-byte chunks (8-row atoms of 1 KB), 1 = 128-byte
-// swizzle of 32-byte chunks (4-row atoms of 512 B) - the only layout the tensor core takes for a tf32 operand whose
-// M / N dimension is the contiguous one.  Atoms are aligned to their size.
-constexpr unsigned LAYOUT_SW128 = 2, LAYOUT_SW128_BASE32 = 1;
-__device__ __forceinline__ uint64_t smem_desc(unsigned addr, unsigned leading_bytes, unsigned stride_bytes, unsigned layout) {
-    return (uint64_t)((addr & 0x3ffffu) >> 4) | ((uint64_t)(leading_bytes >> 4) << 16) | ((uint64_t)(stride_bytes >> 4) << 32) |
-           (1ull << 46) | ((uint64_t)layout << 61);
+// Shared-memory matrix descriptor (64 bits).  Low word: start address (bits 0-13) and leading byte offset (bits 16-29),
+// both in 16-byte units.  High word: stride byte offset in 16-byte units (bits 0-13 = descriptor bits 32-45), descriptor
+// version 1 (bit 14 = bit 46), layout type 2 = 128-byte swizzle of 16-byte chunks (bits 29-31 = bits 61-63; 8-row atoms
+// of 1 KB, aligned to 1 KB).  Every operand of this kernel has a stride of 1 KB between its 8-row atoms, so they all
+// share one high word.  (Layout type 1, the 128-byte swizzle of 32-byte chunks with 4-row atoms, is what a tf32 operand
+// needs when its M / N dimension is the contiguous one; it is not used any more, see the header.)
+constexpr unsigned DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ unsigned desc_lo(unsigned addr, unsigned leading_bytes) {
+    return ((addr & 0x3ffffu) >> 4) | ((leading_bytes >> 4) << 16);
 }
 
 template <typename T> struct UmmaFormat;
@@ -124,9 +136,8 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
     constexpr int KSTEPS = 4;                        // one tcgen05.mma covers 32 bytes of channels: 8 (tf32) or 16 (16-bit)
     constexpr unsigned A_BOX = KCH * 128;            // bytes of one activation box = distance between 128-byte pixel groups
     constexpr unsigned A_KSTEP = A_BOX / KSTEPS;     // KCH / 4 channels further down the box
-    // activation operand (pixels contiguous): 16-bit types use 8-channel atoms under the plain 128-byte swizzle, tf32 needs
-    // 4-channel atoms under the 32-byte-chunk variant; the tensor map of x is encoded with the matching swizzle
-    constexpr unsigned A_ATOM = F32 ? 512u : 1024u, A_LAYOUT = F32 ? LAYOUT_SW128_BASE32 : LAYOUT_SW128;
+    // activation operand: 16-bit types are read where TMA put them (pixels contiguous, 8-channel atoms, 128-byte swizzle);
+    // float32 is rewritten by the split warps as K-major rows (one pixel = 128 bytes of channels, 8-pixel atoms)
 
     extern __shared__ unsigned char smem_dyn[];
     const unsigned xring = ((unsigned)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
@@ -202,35 +213,36 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
         }
     } else if (warp == MMA_WARP) {
         if (lane == 0) {
-            const unsigned idesc = (1u << 4) | (UmmaFormat<T>::code << 7) | (UmmaFormat<T>::code << 10) | (1u << 15) |
+            const unsigned idesc = (1u << 4) | (UmmaFormat<T>::code << 7) | (UmmaFormat<T>::code << 10) | (F32 ? 0u : (1u << 15)) |
                                    ((unsigned)(d >> 3) << 17) | ((unsigned)(TILE_PX >> 4) << 24);
-            unsigned it = 0, ti = 0;
+            // low descriptor words per ring slot are base + slot * pitch; a K step adds a constant (all in 16-byte units)
+            const unsigned a_base = F32 ? desc_lo(opring, 16) : desc_lo(xring, A_BOX);
+            const unsigned a_pitch = (F32 ? op_bytes : (unsigned)Y_STAGE) >> 4, a_kstep = (F32 ? 32u : A_KSTEP) >> 4;
+            const unsigned b_base = desc_lo(opring + w_ofs, 16), b_pitch = op_bytes >> 4;
+            unsigned r = 0, rph = 0, o = 0, oph = 0, ti = 0;
             for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++ti) {
                 const unsigned buf = ti & 1u, tph = (ti >> 1) & 1u;
                 if (!mbar_wait_bounded(tempty0 + 8 * buf, tph ^ 1u)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + buf * (unsigned)d;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const unsigned r = it % nx, rph = (it / nx) & 1u, o = it % no, oph = (it / no) & 1u;
+                for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait_bounded((F32 ? ready0 + 8 * o : xfull0 + 8 * r), F32 ? oph : rph) ||
                         !mbar_wait_bounded(wfull0 + 8 * o, oph)) { ok = false; break; }
                     tc_fence_after();
-                    const unsigned op = opring + o * op_bytes;
-                    const unsigned act = F32 ? op : xring + r * (unsigned)Y_STAGE;
+                    const unsigned a0 = a_base + (F32 ? o : r) * a_pitch, b0 = b_base + o * b_pitch;
 #pragma unroll
                     for (int ks = 0; ks < KSTEPS; ++ks) {
-                        const uint64_t a_hi = smem_desc(act + ks * A_KSTEP, A_BOX, A_ATOM, A_LAYOUT);
-                        const uint64_t b_hi = smem_desc(op + w_ofs + ks * 32, 16, 1024, LAYOUT_SW128);
-                        tc_mma<F32>(d_tmem, a_hi, b_hi, idesc, (kb | ks) != 0 ? 1u : 0u);
+                        const unsigned first = (ks != 0 || kb != 0) ? 1u : 0u;
+                        tc_mma<F32>(d_tmem, a0 + ks * a_kstep, b0 + ks * 2u, DESC_HI, idesc, first);
                         if (F32) {
-                            const uint64_t a_lo = smem_desc(act + Y_STAGE + ks * A_KSTEP, A_BOX, A_ATOM, A_LAYOUT);
-                            const uint64_t b_lo = smem_desc(op + w_ofs + w_bytes + ks * 32, 16, 1024, LAYOUT_SW128);
-                            tc_mma<F32>(d_tmem, a_lo, b_hi, idesc, 1u);
-                            tc_mma<F32>(d_tmem, a_hi, b_lo, idesc, 1u);
+                            tc_mma<F32>(d_tmem, a0 + (Y_STAGE >> 4) + ks * a_kstep, b0 + ks * 2u, DESC_HI, idesc, 1u);          // lo * hi
+                            tc_mma<F32>(d_tmem, a0 + ks * a_kstep, b0 + (w_bytes >> 4) + ks * 2u, DESC_HI, idesc, 1u);          // hi * lo
                         }
                     }
                     if (!F32) tc_commit(xempty0 + 8 * r);   // the activation slot is free once these MMAs have read it
                     tc_commit(oempty0 + 8 * o);             // and so is the operand slot
+                    if (++r == nx) { r = 0; rph ^= 1u; }
+                    if (++o == no) { o = 0; oph ^= 1u; }
                 }
                 if (ok) tc_commit(tfull0 + 8 * buf);        // the accumulator is complete once all MMAs so far are done
             }
@@ -244,15 +256,21 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
                     const unsigned r = it % nx, rph = (it / nx) & 1u, o = it % no, oph = (it / no) & 1u;
                     if (!mbar_wait_bounded(xfull0 + 8 * r, rph) || !mbar_wait_bounded(oempty0 + 8 * o, oph ^ 1u)) { ok = false; break; }
                     const unsigned src = xring + r * (unsigned)Y_STAGE, dst = opring + o * op_bytes;
+                    // item = (pixel group j, channel c = lane, 16-byte chunk q = 4 pixels): two warps per pixel group
+                    const int sw = st >> 5, c = st & 31, j = sw >> 1;
 #pragma unroll
-                    for (int i = 0; i < Y_STAGE / 16 / (SPLIT_WARPS * 32); ++i) {
-                        const unsigned off = (unsigned)(i * SPLIT_WARPS * 32 + st) * 16u;
-                        unsigned v0, v1, v2, v3;
-                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(src + off) : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst + off), "r"(v0 & TF32_MASK), "r"(v1 & TF32_MASK),
-                                     "r"(v2 & TF32_MASK), "r"(v3 & TF32_MASK) : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst + Y_STAGE + off), "r"(tf32_lo(v0)), "r"(tf32_lo(v1)),
-                                     "r"(tf32_lo(v2)), "r"(tf32_lo(v3)) : "memory");
+                    for (int i = 0; i < 4; ++i) {
+                        const int q = (sw & 1) * 4 + i;
+                        unsigned v[4];
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                                     : "r"(src + (unsigned)j * A_BOX + (unsigned)c * 128u + (unsigned)((q ^ (c & 7)) << 4)) : "memory");
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int p = 32 * j + 4 * q + e;            // pixel = operand row
+                            const unsigned at = dst + (unsigned)p * 128u + (unsigned)((((c >> 2) ^ (p & 7)) << 4) | ((c & 3) << 2));
+                            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(at), "r"(v[e] & TF32_MASK) : "memory");
+                            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(at + Y_STAGE), "r"(tf32_lo(v[e])) : "memory");
+                        }
                     }
                     mbar_arrive(xempty0 + 8 * r);                                    // the ring slot can be refilled
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes -> tensor-core reads
@@ -466,7 +484,7 @@ static int run_project(const Plan &p, const void *x, const void *gamma, const vo
 
     Args a;
     if (!make_nchw_map(&a.x_map, x, HW, 1, C, B, KCH, KCH, 1, type, (int)sizeof(T),
-                       sizeof(T) == 4 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B) ||
+                       CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_nchw_map(&a.whi_map, whi, C, 1, d, p.nimg, KCH, d, 1, type, (int)sizeof(T), CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_nchw_map(&a.wlo_map, sizeof(T) == 4 ? wlo : whi, C, 1, d, p.nimg, KCH, d, 1, type, (int)sizeof(T), CU_TENSOR_MAP_SWIZZLE_128B)) {
         set_error("sapa_project_forward: tensor map creation failed (CUresult %d)", last_encode_result());
