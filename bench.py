@@ -612,6 +612,19 @@ def main():
                                          "achieved_gbs": bytes_d / (ms_d * 1e-3) / 1e9, "roofline_frac": bytes_d / (ms_d * 1e-3) / 1e9 / peak_gbs,
                                          "mpix_per_s": pix_per_step_rank / (ms_d * 1e-3) / 1e6,
                                          "config": {"groups": G_, "points": P_, "offset_sigma": 0.5}}
+        # SAPA-D fused backward at the same shapes (one kernel: both scatters, softmax gradient, summed offset gradient)
+        qd, kd, vd, od = (x.detach().clone().requires_grad_() for x in (t["q"], t["k"], t["v"], off))
+        out_d = sapa_b200.deform_sapa_fused(qd, kd, vd, od, P_, s, G_)
+        ms_db = time_path(lambda: torch.autograd.grad(out_d, (qd, kd, vd, od), g_out, retain_graph=True), 10)
+        bytes_db = (B_ * C_ * hi + 2 * (B_ * d_ * hi + B_ * d_ * H_ * W_ + B_ * C_ * H_ * W_) + 2 * (2 * B_ * G_ * P_ * hi)
+                    + B_ * G_ * P_ * hi) * esize
+        paths["sapa_d_fused_backward"] = {"ms": ms_db, "algorithmic_bytes": bytes_db, "achieved_gbs": bytes_db / (ms_db * 1e-3) / 1e9,
+                                          "roofline_frac": bytes_db / (ms_db * 1e-3) / 1e9 / peak_gbs,
+                                          "kernels": sapa_b200._lib.last_kernels(),
+                                          "note": "torch.autograd.grad through deform_sapa_fused: sapa_deform_fused_backward plus the casts of "
+                                                  "its float32 accumulation buffers; bytes = dOut, attention read; q, k, v, offsets read and "
+                                                  "their gradients written"}
+        del qd, kd, vd, od, out_d
         del t, off, g_out, attn_b
         # Decoder pyramid (stand-in wiring, random init, forward only, bf16, B = 16): features of 64 / 128 / 320 / 512
         # channels at 128^2 / 64^2 / 32^2 / 16^2, each projected to 256 channels by a 1x1 convolution, then three

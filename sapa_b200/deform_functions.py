@@ -149,11 +149,24 @@ class DeformSapaFusedFunction(Function):
             out = torch.empty((n, c, hq, wq), dtype=value.dtype, device=value.device)
             attn = torch.empty((n, groups, num_point, hq, wq), dtype=value.dtype, device=value.device) if need_grad else None
             code = _lib.dtype_code(value)
-            nbytes = int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, code))
-            if nbytes:       # s = 2, float32: the dense-window path on the SAPA-B kernels
+            # s = 2: the dense-window path on the SAPA-B kernels.  It computes in float32; 16-bit tensors are widened for
+            # it and the results narrowed again (seven small casts against a 4x faster kernel chain).
+            f32 = _lib.SAPA_F32
+            nbytes = int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, f32))
+            if nbytes and value.dtype == torch.float32:
                 workspace = torch.empty(nbytes, dtype=torch.uint8, device=value.device)
                 _lib.call("sapa_deform_fused_forward_dense", value.device, query, key, value, offset, out, attn, workspace,
                           workspace.numel(), n, cq, c, h, w, num_point, scale_factor, groups, code)
+            elif nbytes:
+                workspace = torch.empty(nbytes, dtype=torch.uint8, device=value.device)
+                out32 = torch.empty(out.shape, dtype=torch.float32, device=value.device)
+                attn32 = torch.empty(attn.shape, dtype=torch.float32, device=value.device) if attn is not None else None
+                _lib.call("sapa_deform_fused_forward_dense", value.device, query.float(), key.float(), value.float(),
+                          offset.float(), out32, attn32, workspace, workspace.numel(), n, cq, c, h, w, num_point, scale_factor,
+                          groups, f32)
+                out.copy_(out32)
+                if attn is not None:
+                    attn.copy_(attn32)
             else:
                 _lib.call("sapa_deform_fused_forward", value.device, query, key, value, offset, out, attn, n, cq, c, h, w,
                           num_point, scale_factor, groups, code)

@@ -244,14 +244,35 @@ class RowSlab:
         return grad_query, grad_key[:, :, own, :], grad_value[:, :, own, :]
 
 
+class _RowShardedFused(torch.autograd.Function):
+    """Differentiable form of the row-sharded op: forward = halo exchange + slab kernel, backward = slab backward +
+    reduction of the halo-row gradients across the neighbouring ranks."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, kernel_size, scale_factor, group):
+        slab = RowSlab(key.size(0), key.size(1), value.size(1), key.size(2), key.size(3), value.dtype, value.device,
+                       kernel_size, scale_factor, group)
+        slab.key.copy_(key)
+        slab.value.copy_(value)
+        need_grad = any(ctx.needs_input_grad[:3])
+        out = slab.forward(query, keep_attn=need_grad)
+        if need_grad:
+            ctx.slab = slab
+            ctx.save_for_backward(query)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (query,) = ctx.saved_tensors
+        grad_query, grad_key, grad_value = ctx.slab.backward(grad_out, query)
+        return grad_query, grad_key.contiguous(), grad_value.contiguous(), None, None, None
+
+
 def sapa_fused_row_sharded(query, key, value, kernel_size=5, scale_factor=2, group=None):
-    """Fused SAPA-B forward on this rank's row slab (one-shot form: builds a :class:`RowSlab` and copies key / value in).
+    """Fused SAPA-B on this rank's row slab (one-shot form: builds a :class:`RowSlab` and copies key / value in).
 
     ``query`` [B,d,s*Hl,s*W], ``key`` [B,d,Hl,W], ``value`` [B,C,Hl,W] hold the rank's rows of one larger
-    image; the result equals the same rows of the unsharded ``sapa_fused``.  Forward only.
+    image; the result equals the same rows of the unsharded ``sapa_fused``, and so do the gradients (every rank must
+    run the backward pass: it exchanges halo-row gradients with the neighbours).
     """
-    slab = RowSlab(key.size(0), key.size(1), value.size(1), key.size(2), key.size(3), value.dtype, value.device,
-                   kernel_size, scale_factor, group)
-    slab.key.copy_(key)
-    slab.value.copy_(value)
-    return slab.forward(query)
+    return _RowShardedFused.apply(query, key, value, kernel_size, scale_factor, group)

@@ -53,6 +53,12 @@ def _worker(rank, world, port, dtype_name, ret):
         def close(a, b):
             return float((a.float() - b.float()).abs().max()) <= tol * float(b.float().abs().max())
         ok = ok and bool(torch.equal(mq, gq[:, :, hi])) and close(mk, gk[:, :, rows]) and close(mv, gv[:, :, rows])
+        # the same through autograd
+        ql2, kl2, vl2 = (t.clone().requires_grad_() for t in (ql, k[:, :, rows].contiguous(), v[:, :, rows].contiguous()))
+        aq, ak, av = torch.autograd.grad(sharding.sapa_fused_row_sharded(ql2, kl2, vl2, K, s), (ql2, kl2, vl2),
+                                         go[:, :, hi].contiguous())
+        torch.cuda.synchronize()
+        ok = ok and bool(torch.equal(aq, mq)) and bool(torch.equal(ak, mk)) and bool(torch.equal(av, mv))
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
