@@ -215,6 +215,19 @@ int sapa_deform_fused_forward_dense(const void *query, const void *key, const vo
                                     void *out, void *attn, void *workspace, size_t workspace_bytes,
                                     int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
 
+/* The same gradients as sapa_deform_fused_backward by way of the SAPA-B kernels, for s = 2 and float32 (the backward
+ * counterpart of sapa_deform_fused_forward_dense): two similarity launches (Q x Key and dOut x Value per group), one
+ * per-pixel kernel (softmax backward over the points, logit-gradient and weight windows, offset gradients), one
+ * aggregation launch (dQ) and two gather launches (dKey, dV) - deterministic for every point inside the 5 x 5 window;
+ * the points outside it are listed and added by a last kernel with atomics.  All four gradients are float32 tensors of
+ * the shapes of their inputs and are overwritten.  `workspace`: sapa_deform_fused_backward_workspace() bytes, 16-byte
+ * aligned.  Other configurations: SAPA_ERR_UNSUPPORTED (the workspace query returns 0).  No counterpart in the reference. */
+size_t sapa_deform_fused_backward_workspace(int B, int H, int W, int P, int s, int G, int dtype);
+int sapa_deform_fused_backward_dense(const void *grad_out, const void *query, const void *key, const void *value,
+                                     const void *offset, const void *attn, void *grad_query, void *grad_key, void *grad_value,
+                                     void *grad_offset, void *workspace, size_t workspace_bytes, int B, int Cq, int C, int H,
+                                     int W, int P, int s, int G, int dtype, void *stream);
+
 /* Backward of sapa_fused_forward_slab for one row slab (multi-GPU row sharding; no counterpart in the reference).
  * grad_out / query / attn are the slab's own rows; key / value are the padded slabs of the forward
  * [B, *, halo_top + H + halo_bottom, W]; grad_query [B, d, sH, sW]; grad_key / grad_value come out in the same padded

@@ -41,10 +41,11 @@ _SIGNATURES = {
     "sapa_deform_fused_forward_dense": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_selftest_wait_timeout": [_vp],
     "sapa_project_forward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, ctypes.c_float, _i, _vp],
+    "sapa_deform_fused_backward_dense": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "sapa_deform_fused_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
 }
 EXPORTS = sorted(list(_SIGNATURES) + ["sapa_last_error", "sapa_last_kernels", "sapa_abi_version", "sapa_fused_backward_workspace",
-                                           "sapa_deform_fused_forward_workspace", "sapa_project_workspace",
+                                           "sapa_deform_fused_forward_workspace", "sapa_deform_fused_backward_workspace", "sapa_project_workspace",
                                            "sapa_fused_backward_static_capacity", "sapa_wait_timeout_flags"])
 
 
@@ -77,6 +78,8 @@ def lib() -> ctypes.CDLL:
     handle.sapa_fused_backward_workspace.restype = ctypes.c_size_t
     handle.sapa_deform_fused_forward_workspace.argtypes = [_i, _i, _i, _i, _i, _i, _i]
     handle.sapa_deform_fused_forward_workspace.restype = ctypes.c_size_t
+    handle.sapa_deform_fused_backward_workspace.argtypes = [_i, _i, _i, _i, _i, _i, _i]
+    handle.sapa_deform_fused_backward_workspace.restype = ctypes.c_size_t
     handle.sapa_project_workspace.argtypes = [_i, _i, _i, _i, _i, _i]
     handle.sapa_project_workspace.restype = ctypes.c_size_t
     handle.sapa_fused_backward_static_capacity.argtypes = []

@@ -646,8 +646,8 @@ int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int
     });
 }
 
-static int run_gath(const void *hi, const void *wt, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
-                    cudaStream_t st) {
+int run_gath(const void *hi, const void *wt, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
+             cudaStream_t st) {
     const bool al = all_aligned16(hi, wt, out);
     if (al && K == 5 && s == 2 && gath_mma_supported(W, dtype)) {
         const int e = launch_gath_mma(hi, wt, out, B, Cc, H, W, 0, 0, dtype, st);

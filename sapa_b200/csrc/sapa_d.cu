@@ -448,6 +448,229 @@ __global__ void deform_outlier_kernel(const OutlierTap *__restrict__ taps, const
     }
 }
 
+// ---------------------------------------------------------------------------------- backward, dense-window path
+// The forward identities read backwards (B_p = the 25-vector of bilinear weights of point p, vy (x) vx):
+//   dWd[cell]   = sum_c dOut_c * value_c[cell]              = sim(dOut, value) per group           (SAPA-B logit kernel)
+//   dA_p        = sum_cells B_p[cell] * dWd[cell];   dS_p = A_p * (dA_p - sum_q A_q dA_q)           (softmax over the points)
+//   dD[cell]    = sum_p dS_p * B_p[cell],  Wd[cell] = sum_p A_p * B_p[cell]
+//   dQ = agg(dD, key),  dKey = gath(Q, dD),  dV = gath(dOut, Wd)  per group                         (SAPA-B kernels, no atomics)
+//   d offset_p  = A_p * (dB_p . dWd) + dS_p * (dB_p . D),   dB_p/dh = dvy (x) vx,  dB_p/dw = vy (x) dvx
+// deform_window_bwd_kernel does the per-pixel part (one thread per (image, group, pixel), everything in registers).
+// Points that leave the window are listed with their A_p and dS_p; deform_outlier_bwd_kernel adds their gradients
+// afterwards (atomics on dQ, dKey, dV; it owns their offset gradients).
+struct OutlierGrad {
+    unsigned int k;      // (image * G + group) * P + point
+    unsigned int pix;    // high-res pixel
+    float a;             // attention weight of the point
+    float ds;            // gradient of its logit
+};
+
+__device__ __forceinline__ void axis_derivative(float (&v)[5], int i0) {
+#pragma unroll
+    for (int r = 0; r < 5; ++r) v[r] = (r == i0 + 1) ? 1.f : (r == i0) ? -1.f : 0.f;
+}
+
+template <typename T, int NP>
+__global__ void __launch_bounds__(WIN_THREADS, 3)
+deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ value, const T *__restrict__ offset,
+                         const T *__restrict__ attn, const T *__restrict__ dense /* D [B*G, 25, hi] */,
+                         const T *__restrict__ dwin /* dWd [B*G, 25, hi] */, T *__restrict__ ddense /* dD, out */,
+                         T *__restrict__ window /* Wd, out */, T *__restrict__ grad_offset, OutlierGrad *__restrict__ taps,
+                         unsigned int *__restrict__ tap_count, int B, int C, int H, int W, int P_runtime, int G) {
+    constexpr int PMAX = NP > 0 ? NP : MAXP;
+    const int P = NP > 0 ? NP : P_runtime;
+    const int sH = 2 * H, sW = 2 * W, gc = C / G;
+    const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
+    const int lane = threadIdx.x & 31;
+    const long long total = (long long)B * G * hi;
+    for (long long i0 = (long long)blockIdx.x * WIN_THREADS; i0 < total; i0 += (long long)gridDim.x * WIN_THREADS) {
+        const long long i = i0 + threadIdx.x;
+        const bool live = i < total;
+        const size_t pix = live ? (size_t)(i % hi) : 0;
+        const long long bg = live ? i / (long long)hi : 0;
+        const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = qh >> 1, px = qw >> 1;
+        float d[25], w[25], oh[PMAX], ow[PMAX], at[PMAX];
+        const T *dp = dense + (size_t)bg * 25 * hi + pix, *wp = dwin + (size_t)bg * 25 * hi + pix;
+#pragma unroll
+        for (int k = 0; k < 25; ++k) {
+            d[k] = live ? to_acc(__ldcs(dp + (size_t)k * hi)) : 0.f;
+            w[k] = live ? to_acc(__ldcs(wp + (size_t)k * hi)) : 0.f;
+        }
+        const T *offp = offset + (size_t)bg * P * 2 * hi + pix, *ap = attn + (size_t)bg * P * hi + pix;
+#pragma unroll
+        for (int p = 0; p < PMAX; ++p) {
+            const bool on = live && p < P;
+            ow[p] = on ? float(px) + to_acc(__ldg(offp + (size_t)(2 * p) * hi)) : 0.f;
+            oh[p] = on ? float(py) + to_acc(__ldg(offp + (size_t)(2 * p + 1) * hi)) : 0.f;
+            at[p] = on ? to_acc(__ldg(ap + (size_t)p * hi)) : 0.f;
+        }
+        // ---- pass 1: dA_p and the four bilinear forms of the offset gradients
+        float da[PMAX], gh1[PMAX], gw1[PMAX], gh2[PMAX], gw2[PMAX];
+        float dot = 0.f;
+        unsigned int outliers = 0;
+#pragma unroll
+        for (int p = 0; p < PMAX; ++p) {
+            da[p] = 0.f; gh1[p] = 0.f; gw1[p] = 0.f; gh2[p] = 0.f; gw2[p] = 0.f;
+            if (live && p < P) {
+                WindowTap t;
+                t.setup(oh[p], ow[p], H, W, py, px);
+                if (t.dense) {
+                    float vy[5], vx[5], dvy[5], dvx[5];
+                    t.axis(vy, t.r0, t.lh);
+                    t.axis(vx, t.c0, t.lw);
+                    axis_derivative(dvy, t.r0);
+                    axis_derivative(dvx, t.c0);
+                    float acc_a = 0.f, acc_h1 = 0.f, acc_h2 = 0.f;
+                    float zw[5] = {0.f, 0.f, 0.f, 0.f, 0.f}, zd[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int r = 0; r < 5; ++r) {
+                        float uw = 0.f, ud = 0.f;
+#pragma unroll
+                        for (int c = 0; c < 5; ++c) {
+                            uw += vx[c] * w[r * 5 + c];
+                            ud += vx[c] * d[r * 5 + c];
+                            zw[c] += vy[r] * w[r * 5 + c];
+                            zd[c] += vy[r] * d[r * 5 + c];
+                        }
+                        acc_a += vy[r] * uw;
+                        acc_h1 += dvy[r] * uw;
+                        acc_h2 += dvy[r] * ud;
+                    }
+                    float acc_w1 = 0.f, acc_w2 = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 5; ++c) { acc_w1 += dvx[c] * zw[c]; acc_w2 += dvx[c] * zd[c]; }
+                    da[p] = acc_a; gh1[p] = acc_h1; gh2[p] = acc_h2; gw1[p] = acc_w1; gw2[p] = acc_w2;
+                } else if (t.inside) {        // outlier: dA by direct gather
+                    outliers |= 1u << p;
+                    Bilinear<float> bl;
+                    bl.setup(oh[p], ow[p], H, W);
+                    const T *gp = grad_out + (size_t)bg * gc * hi + pix, *vp = value + (size_t)bg * gc * lo;
+                    float acc = 0.f;
+                    for (int c = 0; c < gc; ++c) acc += bl.sample(vp + (size_t)c * lo) * to_acc(gp[(size_t)c * hi]);
+                    da[p] = acc;
+                }
+                dot += at[p] * da[p];
+            }
+        }
+        // ---- pass 2: logit gradients, dD, Wd (d[] and w[] become the accumulators), offset gradients
+#pragma unroll
+        for (int k = 0; k < 25; ++k) { d[k] = 0.f; w[k] = 0.f; }
+        T *gop = grad_offset + (size_t)bg * P * 2 * hi + pix;
+#pragma unroll
+        for (int p = 0; p < PMAX; ++p) {
+            if (live && p < P) {
+                const float a = at[p], ds = a * (da[p] - dot);
+                da[p] = ds;
+                WindowTap t;
+                t.setup(oh[p], ow[p], H, W, py, px);
+                if (t.dense) {
+                    float vy[5], vx[5];
+                    t.axis(vy, t.r0, t.lh);
+                    t.axis(vx, t.c0, t.lw);
+#pragma unroll
+                    for (int r = 0; r < 5; ++r) {
+                        const float sy = ds * vy[r], ay = a * vy[r];
+#pragma unroll
+                        for (int c = 0; c < 5; ++c) { d[r * 5 + c] += sy * vx[c]; w[r * 5 + c] += ay * vx[c]; }
+                    }
+                }
+                if (!(outliers & (1u << p))) {      // the list kernel writes the offset gradients of the outliers
+                    gop[(size_t)(2 * p) * hi] = from_acc<T>(a * gw1[p] + ds * gw2[p]);
+                    gop[(size_t)(2 * p + 1) * hi] = from_acc<T>(a * gh1[p] + ds * gh2[p]);
+                }
+            }
+        }
+        if (live) {
+            T *ddp = ddense + (size_t)bg * 25 * hi + pix, *wdp = window + (size_t)bg * 25 * hi + pix;
+#pragma unroll
+            for (int k = 0; k < 25; ++k) { ddp[(size_t)k * hi] = from_acc<T>(d[k]); wdp[(size_t)k * hi] = from_acc<T>(w[k]); }
+        }
+        const unsigned int any = __ballot_sync(0xffffffffu, outliers != 0);
+        if (any != 0) {
+            const int mine = __popc(outliers);
+            int incl = mine;
+#pragma unroll
+            for (int sft = 1; sft < 32; sft <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, sft);
+                if (lane >= sft) incl += up;
+            }
+            const int warp_total = __shfl_sync(0xffffffffu, incl, 31);
+            unsigned int base = 0;
+            if (lane == 0) base = atomicAdd(tap_count, (unsigned int)warp_total);
+            base = __shfl_sync(0xffffffffu, base, 0);
+            unsigned int pos = base + (unsigned int)(incl - mine);
+#pragma unroll
+            for (int p = 0; p < PMAX; ++p)
+                if (outliers & (1u << p)) {
+                    OutlierGrad t;
+                    t.k = (unsigned int)(bg * P + p); t.pix = (unsigned int)pix; t.a = at[p]; t.ds = da[p];
+                    taps[pos++] = t;
+                }
+        }
+    }
+}
+
+// Gradients of the listed outlier points: eight threads per point share its sampling set-up and take every eighth
+// channel; dQ, dKey and dV are added to what the SAPA-B kernels wrote (atomics), the point's offset gradient is written.
+template <typename T>
+__global__ void deform_outlier_bwd_kernel(const OutlierGrad *__restrict__ taps, const unsigned int *__restrict__ tap_count,
+                                          const T *__restrict__ grad_out, const T *__restrict__ query, const T *__restrict__ key,
+                                          const T *__restrict__ value, const T *__restrict__ offset, T *__restrict__ grad_query,
+                                          T *__restrict__ grad_key, T *__restrict__ grad_value, T *__restrict__ grad_offset,
+                                          int Cq, int C, int H, int W, int P, int G) {
+    const int sW = 2 * W, gq = Cq / G, gc = C / G;
+    const size_t hi = (size_t)(2 * H) * sW, lo = (size_t)H * W;
+    const unsigned int n = *tap_count;
+    const int lane = threadIdx.x & 31, sub = lane & 7;
+    const unsigned int group_mask = 0xffu << (lane & ~7);
+    for (unsigned int e = (blockIdx.x * blockDim.x + threadIdx.x) >> 3; e < n; e += (gridDim.x * blockDim.x) >> 3) {
+        const OutlierGrad t = taps[e];
+        const size_t pix = t.pix;
+        const int px = (int)(pix % sW) >> 1, py = (int)(pix / sW) >> 1;
+        const float w = float(px) + to_acc(__ldg(offset + (size_t)t.k * 2 * hi + pix));
+        const float h = float(py) + to_acc(__ldg(offset + (size_t)t.k * 2 * hi + hi + pix));
+        Bilinear<float> bl;
+        bl.setup(h, w, H, W);
+        const float hh = 1.f - bl.lh, hw = 1.f - bl.lw;
+        const size_t bg = t.k / (unsigned int)P;
+        float g_w = 0.f, g_h = 0.f;
+        for (int c = sub; c < gc; c += 8) {            // aggregation: dV scatter and its offset gradient
+            float v00, v01, v10, v11;
+            bl.corners(value + (bg * gc + c) * lo, v00, v01, v10, v11);
+            const float tw = to_acc(grad_out[(bg * gc + c) * hi + pix]) * t.a;
+            T *gp = grad_value + (bg * gc + c) * lo;
+            if (bl.i00 >= 0) atomicAdd(gp + bl.i00, from_acc<T>(bl.w00 * tw));
+            if (bl.i01 >= 0) atomicAdd(gp + bl.i01, from_acc<T>(bl.w01 * tw));
+            if (bl.i10 >= 0) atomicAdd(gp + bl.i10, from_acc<T>(bl.w10 * tw));
+            if (bl.i11 >= 0) atomicAdd(gp + bl.i11, from_acc<T>(bl.w11 * tw));
+            g_w += (-hh * v00 + hh * v01 - bl.lh * v10 + bl.lh * v11) * tw;
+            g_h += (-hw * v00 - bl.lw * v01 + hw * v10 + bl.lw * v11) * tw;
+        }
+        for (int c = sub; c < gq; c += 8) {            // similarity: dQ, dKey scatter and its offset gradient
+            float v00, v01, v10, v11;
+            bl.corners(key + (bg * gq + c) * lo, v00, v01, v10, v11);
+            atomicAdd(grad_query + (bg * gq + c) * hi + pix, from_acc<T>(t.ds * (bl.w00 * v00 + bl.w01 * v01 + bl.w10 * v10 + bl.w11 * v11)));
+            const float tw = t.ds * to_acc(query[(bg * gq + c) * hi + pix]);
+            T *gp = grad_key + (bg * gq + c) * lo;
+            if (bl.i00 >= 0) atomicAdd(gp + bl.i00, from_acc<T>(bl.w00 * tw));
+            if (bl.i01 >= 0) atomicAdd(gp + bl.i01, from_acc<T>(bl.w01 * tw));
+            if (bl.i10 >= 0) atomicAdd(gp + bl.i10, from_acc<T>(bl.w10 * tw));
+            if (bl.i11 >= 0) atomicAdd(gp + bl.i11, from_acc<T>(bl.w11 * tw));
+            g_w += (-hh * v00 + hh * v01 - bl.lh * v10 + bl.lh * v11) * tw;
+            g_h += (-hw * v00 - bl.lw * v01 + hw * v10 + bl.lw * v11) * tw;
+        }
+#pragma unroll
+        for (int sh = 1; sh < 8; sh <<= 1) {
+            g_w += __shfl_xor_sync(group_mask, g_w, sh);
+            g_h += __shfl_xor_sync(group_mask, g_h, sh);
+        }
+        if (sub == 0) {
+            grad_offset[(size_t)t.k * 2 * hi + pix] = from_acc<T>(g_w);
+            grad_offset[(size_t)t.k * 2 * hi + hi + pix] = from_acc<T>(g_h);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------- backward, fused
 // Gradients of out = deform_av(softmax_p(deform_qk(q, k, off)), v, off) in ONE kernel.  One thread per (image, group,
 // high-res pixel) walks the P points three times, with the per-point values parked in shared memory:
@@ -711,6 +934,7 @@ int sapa_deform_fused_backward(const void *grad_out, const void *query, const vo
 namespace sapa {
 int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st);
 int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st);
+int run_gath(const void *hi, const void *wt, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st);
 }
 
 extern "C" {
@@ -767,6 +991,67 @@ int sapa_deform_fused_forward_dense(const void *query, const void *key, const vo
                                                           static_cast<const float *>(offset), static_cast<float *>(out),
                                                           C, H, W, P, G);
     return check_launch("deform_outlier_kernel");
+}
+
+size_t sapa_deform_fused_backward_workspace(int B, int H, int W, int P, int s, int G, int dtype) {
+    if (B <= 0 || H <= 0 || W <= 0 || P <= 0 || G <= 0 || s != 2 || dtype != SAPA_F32) return 0;
+    const size_t hi = (size_t)s * H * s * W;
+    if ((size_t)B * G * P >= 0xffffffffull || hi >= 0xffffffffull) return 0;
+    // D, dWd, dD, Wd, the outlier list (worst case: every point) and its counter
+    return (size_t)B * G * 100 * hi * dtype_size(dtype) + (size_t)B * G * P * hi * sizeof(OutlierGrad) + 16;
+}
+
+int sapa_deform_fused_backward_dense(const void *grad_out, const void *query, const void *key, const void *value,
+                                     const void *offset, const void *attn, void *grad_query, void *grad_key, void *grad_value,
+                                     void *grad_offset, void *workspace, size_t workspace_bytes, int B, int Cq, int C, int H,
+                                     int W, int P, int s, int G, int dtype, void *stream) {
+    const char *fn = "sapa_deform_fused_backward_dense";
+    trace_reset();
+    if (int e = check_deform(fn, B, Cq, C, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value);
+    SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, grad_query); SAPA_CHECK_PTR(fn, grad_key);
+    SAPA_CHECK_PTR(fn, grad_value); SAPA_CHECK_PTR(fn, grad_offset);
+    const size_t need = sapa_deform_fused_backward_workspace(B, H, W, P, s, G, dtype);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_fused_backward)", fn, MAXP);
+    SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
+                 "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
+    const size_t hi = (size_t)s * H * s * W, plane = (size_t)B * G * 25 * hi;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float *dense = static_cast<float *>(workspace), *dwin = dense + plane, *ddense = dwin + plane, *window = ddense + plane;
+    OutlierGrad *taps = reinterpret_cast<OutlierGrad *>(window + plane);
+    unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * P * hi);
+    if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
+        set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
+        return SAPA_ERR_LAUNCH;
+    }
+    const float *go = static_cast<const float *>(grad_out), *q = static_cast<const float *>(query), *k = static_cast<const float *>(key);
+    const float *v = static_cast<const float *>(value), *o = static_cast<const float *>(offset), *a = static_cast<const float *>(attn);
+    // 1. D = sim(Q, Key) and dWd = sim(dOut, Value), the B x G groups as images
+    if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
+    if (int e = run_sim(grad_out, value, dwin, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
+    // 2. per pixel: softmax backward over the points, dD, Wd, offset gradients, list of the points outside the window
+    {
+        const long long total = (long long)B * G * hi;
+        const int grid = grid_1d(total, WIN_THREADS);
+        float *goff = static_cast<float *>(grad_offset);
+        if (P == 9)
+            deform_window_bwd_kernel<float, 9><<<grid, WIN_THREADS, 0, st>>>(go, v, o, a, dense, dwin, ddense, window, goff, taps, tap_count,
+                                                                           B, C, H, W, P, G);
+        else
+            deform_window_bwd_kernel<float, 0><<<grid, WIN_THREADS, 0, st>>>(go, v, o, a, dense, dwin, ddense, window, goff, taps, tap_count,
+                                                                           B, C, H, W, P, G);
+        if (int e = check_launch("deform_window_bwd_kernel")) return e;
+    }
+    // 3. dQ = agg(dD, Key), dKey = gath(Q, dD), dV = gath(dOut, Wd): SAPA-B kernels per group, all outputs overwritten
+    if (int e = run_agg(ddense, key, grad_query, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
+    if (int e = run_gath(query, ddense, grad_key, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
+    if (int e = run_gath(grad_out, window, grad_value, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
+    // 4. the listed points
+    deform_outlier_bwd_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, go, q, k, v, o, static_cast<float *>(grad_query),
+                                                              static_cast<float *>(grad_key), static_cast<float *>(grad_value),
+                                                              static_cast<float *>(grad_offset), Cq, C, H, W, P, G);
+    return check_launch("deform_outlier_bwd_kernel");
 }
 
 }  // extern "C"

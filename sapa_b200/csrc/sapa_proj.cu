@@ -22,8 +22,8 @@
 //     K-major rows (row = pixel, 128 bytes = the stage's 32 channels, 128-byte swizzle): both sides are free of bank
 //     conflicts and the ring slot is released at once.  (The landed boxes can also be fed as an MN-major tf32 operand:
 //     that needs the 128-byte swizzle of 32-byte chunks - CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, descriptor layout type 1,
-//     4-row atoms; with the ordinary swizzle the product is wrong.  It was built first, is as accurate and measured the
-//     same speed.)  W' arrives already split.
+//     4-row atoms; with the ordinary swizzle the product is wrong.  That form is as accurate and no faster.)  W' arrives
+//     already split.
 //   * warp 5 (one lane): issues tcgen05.mma (M = 128, N = d, K = 32 bytes) into one of two TMEM accumulators, frees a
 //     stage with tcgen05.commit, signals the epilogue with another commit.  Its own instruction latency is on the
 //     critical path (one thread, 12 MMAs per float32 stage): ring positions and descriptors advance by additions only.
@@ -48,7 +48,7 @@ constexpr int EPI_WARPS = 4, TMA_WARP = 4, MMA_WARP = 5, W_WARP = 6, SPLIT_WARP0
 constexpr int THREADS = (SPLIT_WARP0 + SPLIT_WARPS) * 32;
 constexpr int Y_STAGE = 16384;           // bytes of activations per stage: 128 px x (128 B / esize) channels
 constexpr int MAX_SLOTS = 8;              // slots per ring
-constexpr int OP_SLOTS_F32 = 2, OP_SLOTS_16 = 4;     // operand ring depth (deeper rings measured no faster)
+constexpr int OP_SLOTS_F32 = 2, OP_SLOTS_16 = 4;     // operand ring depth (the kernel is not sensitive to it)
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int STAT_THREADS = 256, MAX_SPLIT = 64, MAX_GROUPS = 256;
 

@@ -184,6 +184,18 @@ class DeformSapaFusedFunction(Function):
         query, key, value, offset, attn = ctx.saved_tensors
         num_point, scale_factor, groups = ctx.cfg
         grad_output = grad_output.contiguous()
+        n, cq, h, w = key.shape
+        nbytes = 0
+        if query.dtype == torch.float32 and num_point <= 16:
+            nbytes = int(_lib.lib().sapa_deform_fused_backward_workspace(n, h, w, num_point, scale_factor, groups, _lib.SAPA_F32))
+        if nbytes:          # s = 2, float32: the dense-window path on the SAPA-B kernels
+            grad_query, grad_key, grad_value = torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
+            grad_offset = torch.empty_like(offset)
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
+            _lib.call("sapa_deform_fused_backward_dense", query.device, grad_output, query, key, value, offset, attn, grad_query,
+                      grad_key, grad_value, grad_offset, workspace, nbytes, n, cq, value.size(1), h, w, num_point, scale_factor,
+                      groups, _lib.SAPA_F32)
+            return grad_query, grad_key, grad_value, grad_offset, None, None, None
         if deform_fused_supported(num_point, query.dtype) or (num_point <= 16 and query.dtype == torch.float64):
             acc = _acc_dtype(query)
             grad_query = torch.empty(query.shape, dtype=acc, device=query.device)
