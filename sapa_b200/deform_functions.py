@@ -186,16 +186,19 @@ class DeformSapaFusedFunction(Function):
         grad_output = grad_output.contiguous()
         n, cq, h, w = key.shape
         nbytes = 0
-        if query.dtype == torch.float32 and num_point <= 16:
+        if query.dtype in (torch.float32, torch.float16, torch.bfloat16) and num_point <= 16:
             nbytes = int(_lib.lib().sapa_deform_fused_backward_workspace(n, h, w, num_point, scale_factor, groups, _lib.SAPA_F32))
-        if nbytes:          # s = 2, float32: the dense-window path on the SAPA-B kernels
-            grad_query, grad_key, grad_value = torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
-            grad_offset = torch.empty_like(offset)
+        if nbytes:          # s = 2: the dense-window path on the SAPA-B kernels (float32; 16-bit tensors are widened for it)
+            dt = query.dtype
+            f = (lambda t: t) if dt == torch.float32 else (lambda t: t.float())
+            q32, k32, v32, o32 = f(query), f(key), f(value), f(offset)
+            grad_query, grad_key, grad_value = torch.empty_like(q32), torch.empty_like(k32), torch.empty_like(v32)
+            grad_offset = torch.empty_like(o32)
             workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
-            _lib.call("sapa_deform_fused_backward_dense", query.device, grad_output, query, key, value, offset, attn, grad_query,
+            _lib.call("sapa_deform_fused_backward_dense", query.device, f(grad_output), q32, k32, v32, o32, f(attn), grad_query,
                       grad_key, grad_value, grad_offset, workspace, nbytes, n, cq, value.size(1), h, w, num_point, scale_factor,
                       groups, _lib.SAPA_F32)
-            return grad_query, grad_key, grad_value, grad_offset, None, None, None
+            return grad_query.to(dt), grad_key.to(dt), grad_value.to(dt), grad_offset.to(dt), None, None, None
         if deform_fused_supported(num_point, query.dtype) or (num_point <= 16 and query.dtype == torch.float64):
             acc = _acc_dtype(query)
             grad_query = torch.empty(query.shape, dtype=acc, device=query.device)
