@@ -165,3 +165,40 @@ def test_row_slab_backward_of_two_slabs_sums_to_the_unsharded_gradients(dtype, t
         sum_v[:, :, half * hl:half * hl + hl + 2 * r] += mv.float()
     for got, want in ((sum_k[:, :, r:r + H], gk), (sum_v[:, :, r:r + H], gv)):
         assert float((got - want.float()).abs().max()) <= tol * float(want.float().abs().max())
+
+
+DEFORM_SHAPES = [
+    # B, Cq, C, H, W, P, G, sigma
+    (1, 8, 8, 5, 8, 1, 1, 0.5),          # one point, one group
+    (2, 16, 24, 7, 12, 4, 2, 0.8),       # rows of 16 bytes (tensor-map kernels), four points
+    (1, 12, 20, 6, 9, 9, 4, 0.5),        # odd width: the tiled / generic SAPA-B kernels under the dense path
+    (2, 32, 32, 8, 16, 16, 4, 2.5),      # the largest point count, most points outside the window
+    (1, 16, 16, 4, 4, 9, 2, 6.0),        # offsets that leave the image
+]
+
+
+@pytest.mark.parametrize("shape", DEFORM_SHAPES, ids=lambda s: "B%d_q%d_c%d_%dx%d_P%d_G%d_s%g" % s)
+def test_dense_window_deform_matches_the_separate_ops(shape):
+    """SAPA-D fused forward and backward (dense 5x5 window path for s = 2) against the chain of separate ops, which the
+    golden tests pin to the reference: outputs and all four gradients, ragged shapes, every point count, offsets from
+    well inside the window to far outside the image."""
+    import sapa_b200
+    from sapa_b200 import _lib
+    B, Cq, C, H, W, P, G, sigma = shape
+    dev, s = torch.device("cuda:0"), 2
+    g = torch.Generator().manual_seed(31)
+    q, k, v, off, go = (torch.randn(*sh, generator=g).to(dev) for sh in
+                        ((B, Cq, s * H, s * W), (B, Cq, H, W), (B, C, H, W), (B, G * P * 2, s * H, s * W), (B, C, s * H, s * W)))
+    off = off * sigma
+    a = [t.clone().requires_grad_() for t in (q, k, v, off)]
+    out = sapa_b200.deform_sapa_fused(*a, P, s, G)
+    assert "deform_window_kernel" in _lib.last_kernels()
+    grads = torch.autograd.grad(out, a, go)
+    assert "deform_window_bwd_kernel" in _lib.last_kernels()
+    b = [t.clone().requires_grad_() for t in (q, k, v, off)]
+    ref = sapa_b200.deform_av(torch.softmax(sapa_b200.deform_qk(b[0], b[1], b[3], P, s, G), dim=2), b[2], b[3], P, s, G)
+    ref_grads = torch.autograd.grad(ref, b, go)
+    for got, want in [(out.detach(), ref.detach())] + list(zip(grads, ref_grads)):
+        scale = float(want.abs().max())
+        assert float((got - want).abs().max()) <= 1e-5 * max(scale, 1e-30)
+    assert _lib.wait_timeout_flags(dev) == 0

@@ -151,3 +151,24 @@ def test_graphed_pyramid_replays_bit_equal(sp):
         assert torch.equal(got, want)
     from sapa_b200 import _lib
     assert _lib.wait_timeout_flags(dev) == 0
+
+
+def test_projection_random_shapes(sp):
+    """Seeded sweep over channel counts, pixel counts, output widths and batch sizes (float32, 1e-5)."""
+    from sapa_b200.projection import project, project_supported
+    rng = np.random.RandomState(5)
+    done = 0
+    for _ in range(40):
+        B = int(rng.randint(1, 5))
+        C = 32 * int(rng.randint(1, 11))
+        H, W = int(rng.randint(1, 40)), 4 * int(rng.randint(1, 12))
+        d = 16 * int(rng.randint(1, 9))
+        groups = 32 if rng.rand() < 0.7 else 0
+        x, norm, conv, ref = _case(B, C, H, W, d, groups, torch.float32, bias=bool(rng.rand() < 0.5), seed=int(rng.randint(1 << 30)))
+        if not project_supported(x, norm, conv):
+            continue
+        out = project(x, norm, conv)
+        err = float((out.double() - ref).abs().max() / ref.abs().max())
+        assert err < 1e-5, (B, C, H, W, d, groups, err)
+        done += 1
+    assert done >= 30
