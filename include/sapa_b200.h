@@ -215,6 +215,17 @@ int sapa_deform_fused_forward_dense(const void *query, const void *key, const vo
                                     void *out, void *attn, void *workspace, size_t workspace_bytes,
                                     int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
 
+/* sapa_deform_qk_forward and sapa_deform_av_forward by way of the dense 5 x 5 window (s = 2, float32): the two halves of
+ * sapa_deform_fused_forward_dense with the reference's op boundaries - raw logits out (deform_qk_cuda_kernel.cu:139-197)
+ * and attention in (deform_av_cuda_kernel.cu:139-195).  Same results as the gather kernels; `workspace`:
+ * sapa_deform_fused_forward_workspace() bytes, 16-byte aligned. */
+int sapa_deform_qk_forward_dense(const void *query, const void *key, const void *offset, void *out, void *workspace,
+                                 size_t workspace_bytes, int B, int Cq, int H, int W, int P, int s, int G, int dtype,
+                                 void *stream);
+int sapa_deform_av_forward_dense(const void *attn, const void *value, const void *offset, void *out, void *workspace,
+                                 size_t workspace_bytes, int B, int C, int H, int W, int P, int s, int G, int dtype,
+                                 void *stream);
+
 /* The same gradients as sapa_deform_fused_backward by way of the SAPA-B kernels, for s = 2 and float32 (the backward
  * counterpart of sapa_deform_fused_forward_dense): two similarity launches (Q x Key and dOut x Value per group), one
  * per-pixel kernel (softmax backward over the points, logit-gradient and weight windows, offset gradients), one

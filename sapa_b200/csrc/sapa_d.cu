@@ -305,7 +305,11 @@ struct WindowTap {
 // NP = number of points known at compile time (0: read P at run time, up to MAXP).  The P points are walked ONCE with a
 // running maximum (the window weights collected so far are rescaled when the maximum grows), so the bilinear set-up of
 // a point is computed once.
-template <typename T, int NP>
+// MODE: WIN_FUSED = logits -> softmax -> window weights (the fused op); WIN_LOGITS = raw logits only, written where the
+// fused op writes the attention (deform_qk); WIN_WEIGHTS = window weights from a given attention map (deform_av).
+constexpr int WIN_FUSED = 0, WIN_LOGITS = 1, WIN_WEIGHTS = 2;
+
+template <typename T, int NP, int MODE>
 __global__ void __launch_bounds__(WIN_THREADS, 4)
 deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ offset,
                      const T *__restrict__ dense /* [B*G, 25, sH, sW] */, T *__restrict__ attn /* [B, G, P, sH, sW] or null */,
@@ -328,7 +332,7 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
         const T *dp = dense + (size_t)bg * 25 * hi + pix;
 #pragma unroll
         for (int k = 0; k < 25; ++k) {
-            d[k] = live ? to_acc(__ldcs(dp + (size_t)k * hi)) : 0.f;
+            d[k] = (MODE != WIN_WEIGHTS && live) ? to_acc(__ldcs(dp + (size_t)k * hi)) : 0.f;
             wd[k] = 0.f;
         }
         const T *offp = offset + (size_t)bg * P * 2 * hi + pix;
@@ -350,6 +354,21 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
                 t.axis(vy, t.r0, t.lh);
                 t.axis(vx, t.c0, t.lw);
                 float acc = 0.f;
+                if (MODE == WIN_WEIGHTS) {     // the attention is given: it takes the place of exp(logit - max) / sum
+                    const float a = to_acc(__ldg(attn + ((size_t)bg * P + p) * hi + pix));
+                    logit[p] = a;
+                    if (t.dense) {
+#pragma unroll
+                        for (int r = 0; r < 5; ++r) {
+                            const float ay = a * vy[r];
+#pragma unroll
+                            for (int c = 0; c < 5; ++c) wd[r * 5 + c] += ay * vx[c];
+                        }
+                    } else if (t.inside) {
+                        outliers |= 1u << p;
+                    }
+                    continue;
+                }
                 if (t.dense) {
 #pragma unroll
                     for (int r = 0; r < 5; ++r) {
@@ -367,6 +386,10 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
                     for (int c = 0; c < gq; ++c) acc += bl.sample(kp + (size_t)c * lo) * to_acc(qp[(size_t)c * hi]);
                 }
                 logit[p] = acc;
+                if (MODE == WIN_LOGITS) {
+                    attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(acc);
+                    continue;
+                }
                 if (acc > m) {                // new running maximum: bring what was collected so far to the new scale
                     const float f = __expf(m - acc);      // 0 on the first point (m = -inf)
                     z *= f;
@@ -386,16 +409,19 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
                 }
             }
         }
-        const float inv = 1.f / z;
+        if (MODE == WIN_LOGITS) continue;                   // no lane-crossing operation below was entered by any lane yet
+        const float inv = MODE == WIN_WEIGHTS ? 1.f : 1.f / z;
         if (live) {
             T *wp = window + (size_t)bg * 25 * hi + pix;
 #pragma unroll
             for (int k = 0; k < 25; ++k) wp[(size_t)k * hi] = from_acc<T>(wd[k] * inv);
         }
+        if (MODE == WIN_FUSED) {
 #pragma unroll
-        for (int p = 0; p < PMAX; ++p) {
-            logit[p] = __expf(logit[p] - m) * inv;        // the attention weight of the point
-            if (live && p < P && attn != nullptr) attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(logit[p]);
+            for (int p = 0; p < PMAX; ++p) {
+                logit[p] = __expf(logit[p] - m) * inv;        // the attention weight of the point
+                if (live && p < P && attn != nullptr) attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(logit[p]);
+            }
         }
         // append this warp's outlier points to the list: one counter update per warp
         const unsigned int any = __ballot_sync(0xffffffffu, outliers != 0);
@@ -977,10 +1003,10 @@ int sapa_deform_fused_forward_dense(const void *query, const void *key, const vo
         const float *q = static_cast<const float *>(query), *k = static_cast<const float *>(key), *o = static_cast<const float *>(offset);
         const int grid = grid_1d(total, WIN_THREADS);
         if (P == 9)          // the 3 x 3 points of the reference modules' default
-            deform_window_kernel<float, 9><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, static_cast<float *>(attn), window, taps, tap_count,
+            deform_window_kernel<float, 9, WIN_FUSED><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, static_cast<float *>(attn), window, taps, tap_count,
                                                                        B, Cq, H, W, P, G);
         else
-            deform_window_kernel<float, 0><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, static_cast<float *>(attn), window, taps, tap_count,
+            deform_window_kernel<float, 0, WIN_FUSED><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, static_cast<float *>(attn), window, taps, tap_count,
                                                                        B, Cq, H, W, P, G);
         if (int e = check_launch("deform_window_kernel")) return e;
     }
@@ -990,6 +1016,62 @@ int sapa_deform_fused_forward_dense(const void *query, const void *key, const vo
     deform_outlier_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, static_cast<const float *>(value),
                                                           static_cast<const float *>(offset), static_cast<float *>(out),
                                                           C, H, W, P, G);
+    return check_launch("deform_outlier_kernel");
+}
+
+// deform_qk and deform_av through the dense window (s = 2, float32): the halves of the fused forward, with the reference's
+// op boundaries (raw logits out / attention in).  Workspace as for sapa_deform_fused_forward_dense.
+int sapa_deform_qk_forward_dense(const void *query, const void *key, const void *offset, void *out, void *workspace,
+                                 size_t workspace_bytes, int B, int Cq, int H, int W, int P, int s, int G, int dtype, void *stream) {
+    const char *fn = "sapa_deform_qk_forward_dense";
+    trace_reset();
+    if (int e = check_deform(fn, B, Cq, Cq, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, out);
+    const size_t need = sapa_deform_fused_forward_workspace(B, H, W, P, s, G, dtype);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_qk_forward)", fn, MAXP);
+    SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
+                 "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
+    const size_t hi = (size_t)s * H * s * W;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float *dense = static_cast<float *>(workspace);
+    if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
+    const long long total = (long long)B * G * hi;
+    const float *q = static_cast<const float *>(query), *k = static_cast<const float *>(key), *o = static_cast<const float *>(offset);
+    deform_window_kernel<float, 0, WIN_LOGITS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+        q, k, o, dense, static_cast<float *>(out), nullptr, nullptr, nullptr, B, Cq, H, W, P, G);
+    return check_launch("deform_window_kernel<logits>");
+}
+
+int sapa_deform_av_forward_dense(const void *attn, const void *value, const void *offset, void *out, void *workspace,
+                                 size_t workspace_bytes, int B, int C, int H, int W, int P, int s, int G, int dtype, void *stream) {
+    const char *fn = "sapa_deform_av_forward_dense";
+    trace_reset();
+    if (int e = check_deform(fn, B, C, C, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, out);
+    const size_t need = sapa_deform_fused_forward_workspace(B, H, W, P, s, G, dtype);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_av_forward)", fn, MAXP);
+    SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
+                 "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
+    const size_t hi = (size_t)s * H * s * W;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float *window = static_cast<float *>(workspace) + (size_t)B * G * 25 * hi;
+    OutlierTap *taps = reinterpret_cast<OutlierTap *>(window + (size_t)B * G * 25 * hi);
+    unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * P * hi);
+    if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
+        set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
+        return SAPA_ERR_LAUNCH;
+    }
+    const long long total = (long long)B * G * hi;
+    const float *o = static_cast<const float *>(offset);
+    // the attention is only read in this mode
+    deform_window_kernel<float, 0, WIN_WEIGHTS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+        nullptr, nullptr, o, nullptr, const_cast<float *>(static_cast<const float *>(attn)), window, taps, tap_count, B, C, H, W, P, G);
+    if (int e = check_launch("deform_window_kernel<weights>")) return e;
+    if (int e = run_agg(window, value, out, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
+    deform_outlier_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, static_cast<const float *>(value), o,
+                                                          static_cast<float *>(out), C, H, W, P, G);
     return check_launch("deform_outlier_kernel");
 }
 

@@ -24,6 +24,13 @@ def _check_offset(offset, ref_lo, num_point, scale_factor, groups):
     assert num_point >= 1
 
 
+def _dense_workspace_bytes(t, n, h, w, num_point, scale_factor, groups) -> int:
+    """Workspace of the dense-window kernels for this problem, 0 when they do not apply (needs s = 2 and float32)."""
+    if t.dtype != torch.float32 or num_point > 16 or t.data_ptr() % 16 != 0:
+        return 0
+    return int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, _lib.SAPA_F32))
+
+
 class DeformQKFunction(Function):
     """out[b,g,p,qh,qw] = <query_g[b,:,qh,qw], bilinear(key_g[b], (qh/s, qw/s) + offset[b,g,p])>."""
 
@@ -42,8 +49,14 @@ class DeformQKFunction(Function):
         ctx.cfg = (num_point, scale_factor, groups)
         n, c, h, w = query.shape
         out = torch.empty((n, groups, num_point, h, w), dtype=query.dtype, device=query.device)
-        _lib.call("sapa_deform_qk_forward", query.device, query, key, offset, out, n, c, key.size(2), key.size(3),
-                  num_point, scale_factor, groups, _lib.dtype_code(query))
+        nbytes = _dense_workspace_bytes(query, n, key.size(2), key.size(3), num_point, scale_factor, groups)
+        if nbytes:          # s = 2, float32: dense 5x5 similarity of the SAPA-B kernel + bilinear combination per point
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
+            _lib.call("sapa_deform_qk_forward_dense", query.device, query, key, offset, out, workspace, nbytes, n, c, key.size(2),
+                      key.size(3), num_point, scale_factor, groups, _lib.dtype_code(query))
+        else:
+            _lib.call("sapa_deform_qk_forward", query.device, query, key, offset, out, n, c, key.size(2), key.size(3),
+                      num_point, scale_factor, groups, _lib.dtype_code(query))
         if query.requires_grad or key.requires_grad or offset.requires_grad:
             ctx.save_for_backward(query, key, offset)
         return out
@@ -91,8 +104,14 @@ class DeformAVFunction(Function):
         ctx.cfg = (num_point, scale_factor, groups)
         n, c, h, w = value.shape
         out = torch.empty((n, c, scale_factor * h, scale_factor * w), dtype=value.dtype, device=value.device)
-        _lib.call("sapa_deform_av_forward", value.device, attn, value, offset, out, n, c, h, w, num_point, scale_factor,
-                  groups, _lib.dtype_code(value))
+        nbytes = _dense_workspace_bytes(value, n, h, w, num_point, scale_factor, groups)
+        if nbytes:          # s = 2, float32: window weights per pixel + the SAPA-B aggregation kernel
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=value.device)
+            _lib.call("sapa_deform_av_forward_dense", value.device, attn, value, offset, out, workspace, nbytes, n, c, h, w,
+                      num_point, scale_factor, groups, _lib.dtype_code(value))
+        else:
+            _lib.call("sapa_deform_av_forward", value.device, attn, value, offset, out, n, c, h, w, num_point, scale_factor,
+                      groups, _lib.dtype_code(value))
         if attn.requires_grad or value.requires_grad or offset.requires_grad:
             ctx.save_for_backward(attn, value, offset)
         return out
