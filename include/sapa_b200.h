@@ -226,6 +226,19 @@ int sapa_deform_av_forward_dense(const void *attn, const void *value, const void
                                  size_t workspace_bytes, int B, int C, int H, int W, int P, int s, int G, int dtype,
                                  void *stream);
 
+/* sapa_deform_av_backward and sapa_deform_qk_backward by way of the dense 5 x 5 window (s = 2, float32): the two halves
+ * of sapa_deform_fused_backward_dense without the softmax between them (deform_av_cuda_kernel.cu:230-292,
+ * deform_qk_cuda_kernel.cu:233-296).  All gradients are float32 tensors of the shapes of their inputs and are
+ * overwritten; `workspace`: sapa_deform_fused_backward_workspace() bytes, 16-byte aligned. */
+int sapa_deform_av_backward_dense(const void *grad_out, const void *attn, const void *value, const void *offset,
+                                  void *grad_attn, void *grad_value, void *grad_offset, void *workspace,
+                                  size_t workspace_bytes, int B, int C, int H, int W, int P, int s, int G, int dtype,
+                                  void *stream);
+int sapa_deform_qk_backward_dense(const void *grad_out, const void *query, const void *key, const void *offset,
+                                  void *grad_query, void *grad_key, void *grad_offset, void *workspace,
+                                  size_t workspace_bytes, int B, int Cq, int H, int W, int P, int s, int G, int dtype,
+                                  void *stream);
+
 /* The same gradients as sapa_deform_fused_backward by way of the SAPA-B kernels, for s = 2 and float32 (the backward
  * counterpart of sapa_deform_fused_forward_dense): two similarity launches (Q x Key and dOut x Value per group), one
  * per-pixel kernel (softmax backward over the points, logit-gradient and weight windows, offset gradients), one

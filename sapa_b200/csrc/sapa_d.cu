@@ -496,12 +496,18 @@ __device__ __forceinline__ void axis_derivative(float (&v)[5], int i0) {
     for (int r = 0; r < 5; ++r) v[r] = (r == i0 + 1) ? 1.f : (r == i0) ? -1.f : 0.f;
 }
 
-template <typename T, int NP>
+// MODE: BWD_FUSED = the whole chain; BWD_AV = backward of deform_av alone (`attn` given, dA written to `ddense`'s place
+// is not needed: it goes to `grad_attn`, no logit gradients); BWD_QK = backward of deform_qk alone (`attn` carries the
+// logit gradients dS, no aggregation part).
+constexpr int BWD_FUSED = 0, BWD_AV = 1, BWD_QK = 2;
+
+template <typename T, int NP, int MODE>
 __global__ void __launch_bounds__(WIN_THREADS, 3)
 deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ value, const T *__restrict__ offset,
                          const T *__restrict__ attn, const T *__restrict__ dense /* D [B*G, 25, hi] */,
                          const T *__restrict__ dwin /* dWd [B*G, 25, hi] */, T *__restrict__ ddense /* dD, out */,
-                         T *__restrict__ window /* Wd, out */, T *__restrict__ grad_offset, OutlierGrad *__restrict__ taps,
+                         T *__restrict__ window /* Wd, out */, T *__restrict__ grad_offset, T *__restrict__ grad_attn /* BWD_AV only */,
+                         OutlierGrad *__restrict__ taps,
                          unsigned int *__restrict__ tap_count, int B, int C, int H, int W, int P_runtime, int G) {
     constexpr int PMAX = NP > 0 ? NP : MAXP;
     const int P = NP > 0 ? NP : P_runtime;
@@ -519,8 +525,8 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
         const T *dp = dense + (size_t)bg * 25 * hi + pix, *wp = dwin + (size_t)bg * 25 * hi + pix;
 #pragma unroll
         for (int k = 0; k < 25; ++k) {
-            d[k] = live ? to_acc(__ldcs(dp + (size_t)k * hi)) : 0.f;
-            w[k] = live ? to_acc(__ldcs(wp + (size_t)k * hi)) : 0.f;
+            d[k] = (MODE != BWD_AV && live) ? to_acc(__ldcs(dp + (size_t)k * hi)) : 0.f;
+            w[k] = (MODE != BWD_QK && live) ? to_acc(__ldcs(wp + (size_t)k * hi)) : 0.f;
         }
         const T *offp = offset + (size_t)bg * P * 2 * hi + pix, *ap = attn + (size_t)bg * P * hi + pix;
 #pragma unroll
@@ -568,6 +574,7 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
                     da[p] = acc_a; gh1[p] = acc_h1; gh2[p] = acc_h2; gw1[p] = acc_w1; gw2[p] = acc_w2;
                 } else if (t.inside) {        // outlier: dA by direct gather
                     outliers |= 1u << p;
+                    if (MODE == BWD_QK) continue;
                     Bilinear<float> bl;
                     bl.setup(oh[p], ow[p], H, W);
                     const T *gp = grad_out + (size_t)bg * gc * hi + pix, *vp = value + (size_t)bg * gc * lo;
@@ -585,7 +592,10 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
 #pragma unroll
         for (int p = 0; p < PMAX; ++p) {
             if (live && p < P) {
-                const float a = at[p], ds = a * (da[p] - dot);
+                // BWD_QK: `attn` holds the logit gradients themselves; BWD_AV: no logit gradient, dA goes out as it is
+                const float a = MODE == BWD_QK ? 0.f : at[p];
+                const float ds = MODE == BWD_QK ? at[p] : MODE == BWD_AV ? 0.f : a * (da[p] - dot);
+                if (MODE == BWD_AV) grad_attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(da[p]);
                 da[p] = ds;
                 WindowTap t;
                 t.setup(oh[p], ow[p], H, W, py, px);
@@ -609,7 +619,10 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
         if (live) {
             T *ddp = ddense + (size_t)bg * 25 * hi + pix, *wdp = window + (size_t)bg * 25 * hi + pix;
 #pragma unroll
-            for (int k = 0; k < 25; ++k) { ddp[(size_t)k * hi] = from_acc<T>(d[k]); wdp[(size_t)k * hi] = from_acc<T>(w[k]); }
+            for (int k = 0; k < 25; ++k) {
+                if (MODE != BWD_AV) ddp[(size_t)k * hi] = from_acc<T>(d[k]);
+                if (MODE != BWD_QK) wdp[(size_t)k * hi] = from_acc<T>(w[k]);
+            }
         }
         const unsigned int any = __ballot_sync(0xffffffffu, outliers != 0);
         if (any != 0) {
@@ -629,7 +642,7 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
             for (int p = 0; p < PMAX; ++p)
                 if (outliers & (1u << p)) {
                     OutlierGrad t;
-                    t.k = (unsigned int)(bg * P + p); t.pix = (unsigned int)pix; t.a = at[p]; t.ds = da[p];
+                    t.k = (unsigned int)(bg * P + p); t.pix = (unsigned int)pix; t.a = MODE == BWD_QK ? 0.f : at[p]; t.ds = da[p];
                     taps[pos++] = t;
                 }
         }
@@ -660,7 +673,7 @@ __global__ void deform_outlier_bwd_kernel(const OutlierGrad *__restrict__ taps, 
         const float hh = 1.f - bl.lh, hw = 1.f - bl.lw;
         const size_t bg = t.k / (unsigned int)P;
         float g_w = 0.f, g_h = 0.f;
-        for (int c = sub; c < gc; c += 8) {            // aggregation: dV scatter and its offset gradient
+        for (int c = sub; c < gc && grad_value != nullptr; c += 8) {      // aggregation: dV scatter and its offset gradient
             float v00, v01, v10, v11;
             bl.corners(value + (bg * gc + c) * lo, v00, v01, v10, v11);
             const float tw = to_acc(grad_out[(bg * gc + c) * hi + pix]) * t.a;
@@ -672,7 +685,7 @@ __global__ void deform_outlier_bwd_kernel(const OutlierGrad *__restrict__ taps, 
             g_w += (-hh * v00 + hh * v01 - bl.lh * v10 + bl.lh * v11) * tw;
             g_h += (-hw * v00 - bl.lw * v01 + hw * v10 + bl.lw * v11) * tw;
         }
-        for (int c = sub; c < gq; c += 8) {            // similarity: dQ, dKey scatter and its offset gradient
+        for (int c = sub; c < gq && grad_query != nullptr; c += 8) {      // similarity: dQ, dKey scatter and its offset gradient
             float v00, v01, v10, v11;
             bl.corners(key + (bg * gq + c) * lo, v00, v01, v10, v11);
             atomicAdd(grad_query + (bg * gq + c) * hi + pix, from_acc<T>(t.ds * (bl.w00 * v00 + bl.w01 * v01 + bl.w10 * v10 + bl.w11 * v11)));
@@ -1118,10 +1131,10 @@ int sapa_deform_fused_backward_dense(const void *grad_out, const void *query, co
         const int grid = grid_1d(total, WIN_THREADS);
         float *goff = static_cast<float *>(grad_offset);
         if (P == 9)
-            deform_window_bwd_kernel<float, 9><<<grid, WIN_THREADS, 0, st>>>(go, v, o, a, dense, dwin, ddense, window, goff, taps, tap_count,
+            deform_window_bwd_kernel<float, 9, BWD_FUSED><<<grid, WIN_THREADS, 0, st>>>(go, v, o, a, dense, dwin, ddense, window, goff, nullptr, taps, tap_count,
                                                                            B, C, H, W, P, G);
         else
-            deform_window_bwd_kernel<float, 0><<<grid, WIN_THREADS, 0, st>>>(go, v, o, a, dense, dwin, ddense, window, goff, taps, tap_count,
+            deform_window_bwd_kernel<float, 0, BWD_FUSED><<<grid, WIN_THREADS, 0, st>>>(go, v, o, a, dense, dwin, ddense, window, goff, nullptr, taps, tap_count,
                                                                            B, C, H, W, P, G);
         if (int e = check_launch("deform_window_bwd_kernel")) return e;
     }
@@ -1133,6 +1146,84 @@ int sapa_deform_fused_backward_dense(const void *grad_out, const void *query, co
     deform_outlier_bwd_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, go, q, k, v, o, static_cast<float *>(grad_query),
                                                               static_cast<float *>(grad_key), static_cast<float *>(grad_value),
                                                               static_cast<float *>(grad_offset), Cq, C, H, W, P, G);
+    return check_launch("deform_outlier_bwd_kernel");
+}
+
+// Backward of deform_av and of deform_qk alone through the dense window (s = 2, float32): the two halves of
+// sapa_deform_fused_backward_dense without the softmax between them.  Workspace as for that entry point.
+int sapa_deform_av_backward_dense(const void *grad_out, const void *attn, const void *value, const void *offset, void *grad_attn,
+                                  void *grad_value, void *grad_offset, void *workspace, size_t workspace_bytes, int B, int C,
+                                  int H, int W, int P, int s, int G, int dtype, void *stream) {
+    const char *fn = "sapa_deform_av_backward_dense";
+    trace_reset();
+    if (int e = check_deform(fn, B, C, C, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset);
+    SAPA_CHECK_PTR(fn, grad_attn); SAPA_CHECK_PTR(fn, grad_value); SAPA_CHECK_PTR(fn, grad_offset);
+    const size_t need = sapa_deform_fused_backward_workspace(B, H, W, P, s, G, dtype);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_av_backward)", fn, MAXP);
+    SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
+                 "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
+    const size_t hi = (size_t)s * H * s * W, plane = (size_t)B * G * 25 * hi;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float *dwin = static_cast<float *>(workspace) + plane, *window = dwin + 2 * plane;
+    OutlierGrad *taps = reinterpret_cast<OutlierGrad *>(window + plane);
+    unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * P * hi);
+    if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
+        set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
+        return SAPA_ERR_LAUNCH;
+    }
+    const float *go = static_cast<const float *>(grad_out), *v = static_cast<const float *>(value);
+    const float *o = static_cast<const float *>(offset), *a = static_cast<const float *>(attn);
+    if (int e = run_sim(grad_out, value, dwin, B * G, C / G, H, W, 5, 2, dtype, st)) return e;        // dWd
+    const long long total = (long long)B * G * hi;
+    deform_window_bwd_kernel<float, 0, BWD_AV><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+        go, v, o, a, nullptr, dwin, nullptr, window, static_cast<float *>(grad_offset), static_cast<float *>(grad_attn), taps,
+        tap_count, B, C, H, W, P, G);
+    if (int e = check_launch("deform_window_bwd_kernel<av>")) return e;
+    if (int e = run_gath(grad_out, window, grad_value, B * G, C / G, H, W, 5, 2, dtype, st)) return e;  // dV
+    deform_outlier_bwd_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, go, nullptr, nullptr, v, o, nullptr, nullptr,
+                                                              static_cast<float *>(grad_value), static_cast<float *>(grad_offset),
+                                                              C, C, H, W, P, G);
+    return check_launch("deform_outlier_bwd_kernel");
+}
+
+int sapa_deform_qk_backward_dense(const void *grad_out, const void *query, const void *key, const void *offset, void *grad_query,
+                                  void *grad_key, void *grad_offset, void *workspace, size_t workspace_bytes, int B, int Cq,
+                                  int H, int W, int P, int s, int G, int dtype, void *stream) {
+    const char *fn = "sapa_deform_qk_backward_dense";
+    trace_reset();
+    if (int e = check_deform(fn, B, Cq, Cq, H, W, P, s, G, dtype)) return e;
+    SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, offset);
+    SAPA_CHECK_PTR(fn, grad_query); SAPA_CHECK_PTR(fn, grad_key); SAPA_CHECK_PTR(fn, grad_offset);
+    const size_t need = sapa_deform_fused_backward_workspace(B, H, W, P, s, G, dtype);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_qk_backward)", fn, MAXP);
+    SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
+                 "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
+    const size_t hi = (size_t)s * H * s * W, plane = (size_t)B * G * 25 * hi;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float *dense = static_cast<float *>(workspace), *ddense = dense + 2 * plane;
+    OutlierGrad *taps = reinterpret_cast<OutlierGrad *>(dense + 4 * plane);
+    unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * P * hi);
+    if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
+        set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
+        return SAPA_ERR_LAUNCH;
+    }
+    const float *ds = static_cast<const float *>(grad_out), *q = static_cast<const float *>(query), *k = static_cast<const float *>(key);
+    const float *o = static_cast<const float *>(offset);
+    if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;             // D, for the offset gradients
+    const long long total = (long long)B * G * hi;
+    // the logit gradients enter where the fused chain reads the attention
+    deform_window_bwd_kernel<float, 0, BWD_QK><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+        nullptr, nullptr, o, ds, dense, nullptr, ddense, nullptr, static_cast<float *>(grad_offset), nullptr, taps, tap_count,
+        B, Cq, H, W, P, G);
+    if (int e = check_launch("deform_window_bwd_kernel<qk>")) return e;
+    if (int e = run_agg(ddense, key, grad_query, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;       // dQ
+    if (int e = run_gath(query, ddense, grad_key, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;      // dKey
+    deform_outlier_bwd_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, nullptr, q, k, nullptr, o,
+                                                              static_cast<float *>(grad_query), static_cast<float *>(grad_key), nullptr,
+                                                              static_cast<float *>(grad_offset), Cq, Cq, H, W, P, G);
     return check_launch("deform_outlier_bwd_kernel");
 }
 

@@ -31,6 +31,13 @@ def _dense_workspace_bytes(t, n, h, w, num_point, scale_factor, groups) -> int:
     return int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, _lib.SAPA_F32))
 
 
+def _dense_backward_bytes(t, grad_output, n, h, w, num_point, scale_factor, groups) -> int:
+    """Workspace of the dense-window backward kernels, 0 when they do not apply (needs s = 2 and float32)."""
+    if t.dtype != torch.float32 or num_point > 16 or t.data_ptr() % 16 != 0 or grad_output.data_ptr() % 16 != 0:
+        return 0
+    return int(_lib.lib().sapa_deform_fused_backward_workspace(n, h, w, num_point, scale_factor, groups, _lib.SAPA_F32))
+
+
 class DeformQKFunction(Function):
     """out[b,g,p,qh,qw] = <query_g[b,:,qh,qw], bilinear(key_g[b], (qh/s, qw/s) + offset[b,g,p])>."""
 
@@ -76,6 +83,12 @@ def deform_qk_backward_raw(grad_output, query, key, offset, num_point, scale_fac
     grad_key = torch.empty(key.shape, dtype=acc, device=key.device)
     grad_offset = torch.empty_like(offset)
     n, c, h, w = key.shape
+    nbytes = _dense_backward_bytes(query, grad_output, n, h, w, num_point, scale_factor, groups)
+    if nbytes:              # s = 2, float32: SAPA-B kernels around one per-pixel kernel
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
+        _lib.call("sapa_deform_qk_backward_dense", query.device, grad_output, query, key, offset, grad_query, grad_key,
+                  grad_offset, workspace, nbytes, n, c, h, w, num_point, scale_factor, groups, _lib.SAPA_F32)
+        return grad_query, grad_key, grad_offset
     _lib.call("sapa_deform_qk_backward", query.device, grad_output, query, key, offset, grad_query, grad_key,
               grad_offset, n, c, h, w, num_point, scale_factor, groups, _lib.dtype_code(query))
     return grad_query.to(query.dtype), grad_key.to(key.dtype), grad_offset
@@ -130,6 +143,12 @@ def deform_av_backward_raw(grad_output, attn, value, offset, num_point, scale_fa
     grad_value = torch.empty(value.shape, dtype=_acc_dtype(value), device=value.device)
     grad_offset = torch.empty_like(offset)
     n, c, h, w = value.shape
+    nbytes = _dense_backward_bytes(value, grad_output, n, h, w, num_point, scale_factor, groups)
+    if nbytes:
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=value.device)
+        _lib.call("sapa_deform_av_backward_dense", value.device, grad_output, attn, value, offset, grad_attn, grad_value,
+                  grad_offset, workspace, nbytes, n, c, h, w, num_point, scale_factor, groups, _lib.SAPA_F32)
+        return grad_attn, grad_value, grad_offset
     _lib.call("sapa_deform_av_backward", value.device, grad_output, attn, value, offset, grad_attn, grad_value,
               grad_offset, n, c, h, w, num_point, scale_factor, groups, _lib.dtype_code(value))
     return grad_attn, grad_value.to(value.dtype), grad_offset
