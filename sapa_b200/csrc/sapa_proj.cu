@@ -26,7 +26,9 @@
 //     already split.
 //   * warp 5 (one lane): issues tcgen05.mma (M = 128, N = d, K = 32 bytes) into one of two TMEM accumulators, frees a
 //     stage with tcgen05.commit, signals the epilogue with another commit.  Its own instruction latency is on the
-//     critical path (one thread, 12 MMAs per float32 stage): ring positions and descriptors advance by additions only.
+//     critical path (one thread): ring positions and descriptors advance by additions only, and for float32 with
+//     d <= 128 the terms x_hi * W'_hi and x_hi * W'_lo are ONE instruction of N = 2d (the two W' blocks are adjacent
+//     rows of the operand; the epilogue adds the two halves of the accumulator): 8 instead of 12 MMAs per stage.
 //   * warps 0-3: epilogue.  tcgen05.ld (lane = pixel, column = output channel), add bias', store: for a fixed output
 //     channel the 32 lanes of a warp write 32 consecutive pixels.  Runs under the MMAs of the next tile.
 // Tiles walk the images from the last to the first: the statistics pass has just read them in ascending order, so the
@@ -60,6 +62,7 @@ struct Args {
     const float *bias;              // folded bias [images or 1][d]
     void *out;                      // [B][d][HW]
     int B, C, HW, d, w_per_image, tiles_per_image, total_tiles, kblocks, nx, no, tmem_cols;
+    int wide;                       // float32: hi*hi and hi*lo in ONE instruction of N = 2d (W' hi and lo blocks are adjacent rows)
 };
 
 // ---------------------------------------------------------------------------------- tcgen05 wrappers
@@ -179,6 +182,7 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
     asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
 
     const int tpi = a.tiles_per_image, kblocks = a.kblocks;
+    const unsigned acc_cols = (unsigned)(a.wide ? 2 * d : d);       // accumulator columns per tile
     bool ok = true;
 
     if (warp == TMA_WARP) {            // activations: global -> ring
@@ -215,6 +219,7 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
         if (lane == 0) {
             const unsigned idesc = (1u << 4) | (UmmaFormat<T>::code << 7) | (UmmaFormat<T>::code << 10) | (F32 ? 0u : (1u << 15)) |
                                    ((unsigned)(d >> 3) << 17) | ((unsigned)(TILE_PX >> 4) << 24);
+            const unsigned idesc_wide = (idesc & ~(0x3fu << 17)) | ((unsigned)(2 * d >> 3) << 17);      // the same with N = 2d
             // low descriptor words per ring slot are base + slot * pitch; a K step adds a constant (all in 16-byte units)
             const unsigned a_base = F32 ? desc_lo(opring, 16) : desc_lo(xring, A_BOX);
             const unsigned a_pitch = (F32 ? op_bytes : (unsigned)Y_STAGE) >> 4, a_kstep = (F32 ? 32u : A_KSTEP) >> 4;
@@ -224,7 +229,7 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
                 const unsigned buf = ti & 1u, tph = (ti >> 1) & 1u;
                 if (!mbar_wait_bounded(tempty0 + 8 * buf, tph ^ 1u)) { ok = false; break; }
                 tc_fence_after();
-                const unsigned d_tmem = tmem_base + buf * (unsigned)d;
+                const unsigned d_tmem = tmem_base + buf * acc_cols;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait_bounded((F32 ? ready0 + 8 * o : xfull0 + 8 * r), F32 ? oph : rph) ||
                         !mbar_wait_bounded(wfull0 + 8 * o, oph)) { ok = false; break; }
@@ -233,10 +238,17 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
 #pragma unroll
                     for (int ks = 0; ks < KSTEPS; ++ks) {
                         const unsigned first = (ks != 0 || kb != 0) ? 1u : 0u;
-                        tc_mma<F32>(d_tmem, a0 + ks * a_kstep, b0 + ks * 2u, DESC_HI, idesc, first);
-                        if (F32) {
-                            tc_mma<F32>(d_tmem, a0 + (Y_STAGE >> 4) + ks * a_kstep, b0 + ks * 2u, DESC_HI, idesc, 1u);          // lo * hi
-                            tc_mma<F32>(d_tmem, a0 + ks * a_kstep, b0 + (w_bytes >> 4) + ks * 2u, DESC_HI, idesc, 1u);          // hi * lo
+                        if (F32 && a.wide) {
+                            // x_hi * [W'_hi ; W'_lo] as one instruction of N = 2d (columns [0, d) and [d, 2d) of the
+                            // accumulator, added by the epilogue), then x_lo * W'_hi into the first half
+                            tc_mma<F32>(d_tmem, a0 + ks * a_kstep, b0 + ks * 2u, DESC_HI, idesc_wide, first);
+                            tc_mma<F32>(d_tmem, a0 + (Y_STAGE >> 4) + ks * a_kstep, b0 + ks * 2u, DESC_HI, idesc, 1u);
+                        } else {
+                            tc_mma<F32>(d_tmem, a0 + ks * a_kstep, b0 + ks * 2u, DESC_HI, idesc, first);
+                            if (F32) {
+                                tc_mma<F32>(d_tmem, a0 + (Y_STAGE >> 4) + ks * a_kstep, b0 + ks * 2u, DESC_HI, idesc, 1u);      // lo * hi
+                                tc_mma<F32>(d_tmem, a0 + ks * a_kstep, b0 + (w_bytes >> 4) + ks * 2u, DESC_HI, idesc, 1u);      // hi * lo
+                            }
                         }
                     }
                     if (!F32) tc_commit(xempty0 + 8 * r);   // the activation slot is free once these MMAs have read it
@@ -258,18 +270,22 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
                     const unsigned src = xring + r * (unsigned)Y_STAGE, dst = opring + o * op_bytes;
                     // item = (pixel group j, channel c = lane, 16-byte chunk q = 4 pixels): two warps per pixel group
                     const int sw = st >> 5, c = st & 31, j = sw >> 1;
+                    unsigned v[4][4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {            // all four loads in flight before the first store
+                        const int q = (sw & 1) * 4 + i;
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v[i][0]), "=r"(v[i][1]), "=r"(v[i][2]), "=r"(v[i][3])
+                                     : "r"(src + (unsigned)j * A_BOX + (unsigned)c * 128u + (unsigned)((q ^ (c & 7)) << 4)) : "memory");
+                    }
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int q = (sw & 1) * 4 + i;
-                        unsigned v[4];
-                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
-                                     : "r"(src + (unsigned)j * A_BOX + (unsigned)c * 128u + (unsigned)((q ^ (c & 7)) << 4)) : "memory");
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int p = 32 * j + 4 * q + e;            // pixel = operand row
                             const unsigned at = dst + (unsigned)p * 128u + (unsigned)((((c >> 2) ^ (p & 7)) << 4) | ((c & 3) << 2));
-                            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(at), "r"(v[e] & TF32_MASK) : "memory");
-                            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(at + Y_STAGE), "r"(tf32_lo(v[e])) : "memory");
+                            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(at), "r"(v[i][e] & TF32_MASK) : "memory");
+                            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(at + Y_STAGE), "r"(tf32_lo(v[i][e])) : "memory");
                         }
                     }
                     mbar_arrive(xempty0 + 8 * r);                                    // the ring slot can be refilled
@@ -286,13 +302,20 @@ __global__ void __launch_bounds__(THREADS, 1) sapa_proj_umma_kernel(const __grid
             const int bi = tile / tpi, b = a.B - 1 - bi, px = (tile - bi * tpi) * TILE_PX + warp * 32 + lane, wb = a.w_per_image ? b : 0;
             if (!mbar_wait_bounded(tfull0 + 8 * buf, tph)) { ok = false; break; }
             tc_fence_after();
-            const unsigned taddr = tmem_base + ((unsigned)(warp * 32) << 16) + buf * (unsigned)d;
+            const unsigned taddr = tmem_base + ((unsigned)(warp * 32) << 16) + buf * acc_cols;
             const float *bias = a.bias + (size_t)wb * d;
             T *op = out + (size_t)b * d * a.HW + px;
             for (int c0 = 0; c0 < d; c0 += 16) {
                 unsigned r[16];
                 tc_ld16(taddr + (unsigned)c0, r);
                 tc_wait_ld();
+                if (a.wide) {                           // second half of the accumulator: the x_hi * W'_lo term
+                    unsigned r2[16];
+                    tc_ld16(taddr + (unsigned)(d + c0), r2);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+                }
                 if (c0 + 16 >= d) {                     // last read of this accumulator: hand it back to the MMA warp
                     tc_fence_before();
                     mbar_arrive(tempty0 + 8 * buf);
@@ -429,7 +452,7 @@ __global__ void __launch_bounds__(STAT_THREADS) gn_fold_kernel(const double2 *__
 
 // ---------------------------------------------------------------------------------- host side
 struct Plan {
-    int esize, nsplit, nimg, nx, no, tmem_cols;
+    int esize, nsplit, nimg, nx, no, tmem_cols, wide;
     size_t smem;
     size_t partial_ofs, whi_ofs, wlo_ofs, bias_ofs, total;
 };
@@ -450,8 +473,9 @@ static bool make_plan(Plan &p, int B, int C, int HW, int d, int groups, int dtyp
     if (fixed + p.no * op + 2 * (size_t)Y_STAGE > SMEM_LIMIT) return false;
     p.nx = (int)std::min<size_t>(MAX_SLOTS, (SMEM_LIMIT - fixed - p.no * op) / Y_STAGE);
     p.smem = fixed + p.no * op + (size_t)p.nx * Y_STAGE;
+    p.wide = p.esize == 4 && 4 * d <= 512 ? 1 : 0;     // two accumulators of 2d columns must fit into TMEM
     p.tmem_cols = 32;
-    while (p.tmem_cols < 2 * d) p.tmem_cols *= 2;
+    while (p.tmem_cols < 2 * (p.wide ? 2 * d : d)) p.tmem_cols *= 2;
     p.nimg = groups > 0 ? B : 1;
     p.nsplit = groups > 0 ? std::max(1, std::min(MAX_SPLIT, (148 * 8 + B * groups - 1) / (B * groups))) : 1;
     size_t at = 0;
@@ -495,7 +519,7 @@ static int run_project(const Plan &p, const void *x, const void *gamma, const vo
     a.tiles_per_image = (HW + TILE_PX - 1) / TILE_PX;
     a.total_tiles = a.tiles_per_image * B;
     a.kblocks = (C + KCH - 1) / KCH;
-    a.nx = p.nx; a.no = p.no; a.tmem_cols = p.tmem_cols;
+    a.nx = p.nx; a.no = p.no; a.tmem_cols = p.tmem_cols; a.wide = p.wide;
     const size_t smem = p.smem;
     static int sms = 0;
     if (sms == 0) {
