@@ -33,8 +33,8 @@ constexpr int ROWS = 4, COLS = 8;          // low-res output tile of a CTA
 constexpr int HR = 2 * (ROWS + 4);         // high-res rows per box
 constexpr int BPX = 32;                    // high-res pixels per box row: 2*x0-8 .. 2*x0+23 (used: 4 .. 27)
 constexpr int NSTAGE = 3;                  // ring slots of 32 KB
-constexpr int NW = 2 * ROWS;               // 8 warps
-constexpr int NT = NW * 32;
+constexpr int NW = 2 * ROWS;               // 8 consumer warps
+constexpr int NT = (NW + 1) * 32;          // + one producer warp
 constexpr int CTAS_PER_SM = 2;
 
 __device__ int g_wait_timeout = 0;
@@ -152,6 +152,13 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
         }
     };
 
+    // The producer is a warp of its own (one lane works): inside a consumer warp it took a quarter of that warp's time
+    // and the other warps waited a third of theirs for stages it had not issued yet.
+    if (warp == NW) {
+        if (lane == 0) produce(0x7fffffff);
+        return;
+    }
+
     // ---- per-lane fragment offsets.  Pixel group kg covers box pixels 4 + 8*kg .. 11 + 8*kg.
     //   float32 A fragment: a0 = X[ch g][px t], a1 = X[ch g+8][px t], a2 = X[ch g][px t+4], a3 = X[ch g+8][px t+4]
     //   16-bit  A fragment: a0 = X[ch g][px 2t, 2t+1], a1 = X[ch g+8][same]
@@ -176,10 +183,6 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
     T *o_ptr = nullptr;
     bool store_ok = false;
     for (;; ++gs) {
-        if (warp == 0) {
-            if (lane == 0) produce(gs);
-            __syncwarp();
-        }
         if (!mbar_wait_bounded(full_addr + 8 * slot, phase)) {
             atomicExch(&g_wait_timeout, 1);
             return;
