@@ -17,7 +17,7 @@
 //     loads bank-conflict-free;
 //   * warp = (output row, upper / lower high-res row of the parents): the two warps of a row add their partial
 //     sums through shared memory (an mbarrier handshake per pair and stage), nothing is CTA-wide in the steady state;
-//   * ring protocol: full / empty mbarriers, lane 0 of warp 0 refills a slot as soon as all 8 warps released it;
+//   * ring protocol: full / empty mbarriers, one lane of a ninth, producer-only warp refills a slot as soon as all 8 warps released it;
 //     every wait is bounded and raises g_wait_timeout instead of spinning for ever.
 #include "tma_util.cuh"
 
@@ -111,7 +111,7 @@ sapa_gath_mma_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
     }
     __syncthreads();
 
-    // ---- producer state (lane 0 of warp 0): the stages of successive tiles form one stream through the ring
+    // ---- producer state (lane 0 of the producer warp): the stages of successive tiles form one stream through the ring
     int p_issued = 0, p_slot = 0, p_phase = 0, p_it = 0, p_ti = 0, p_n = 0, p_x0 = 0, p_y0 = 0;
     bool p_done = false;
     auto produce = [&](int need) {

@@ -417,7 +417,7 @@ sapa_tma_fused_f32_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
 //     packed register;
 //   * all fragments come from ldmatrix: K^T and Q with .trans, V without;
 //   * no CTA-wide barrier in the steady state: ring slots are handed back on "empty" mbarriers (one arrival per
-//     warp) and refilled by lane 0 of warp 0 whenever it finds one free; outputs go from registers to global memory.
+//     warp) and refilled by one lane of a ninth, producer-only warp; outputs go from registers to global memory.
 namespace h16 {
 constexpr int COLS = 8;                         // low-res columns of a CTA tile
 constexpr int NSTAGE = 4;                       // ring slots of 20 KB
@@ -505,7 +505,7 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
     }
     __syncthreads();
 
-    // ---- producer state (lane 0 of warp 0).  The stages of successive tiles form one continuous stream through
+    // ---- producer state (lane 0 of the producer warp).  The stages of successive tiles form one continuous stream through
     // the ring; the first tile of a CTA is blockIdx.x, further tiles come from a global counter.
     int p_issued = 0, p_slot = 0, p_phase = 0, p_it = 0, p_ti = 0, p_n = 0, p_x0 = 0, p_y0 = 0;
     bool p_done = false;
