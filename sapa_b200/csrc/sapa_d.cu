@@ -309,6 +309,7 @@ struct WindowTap {
 // fused op writes the attention (deform_qk); WIN_WEIGHTS = window weights from a given attention map (deform_av).
 constexpr int WIN_FUSED = 0, WIN_LOGITS = 1, WIN_WEIGHTS = 2;
 
+// (four blocks per SM: 128 registers; more blocks spill, fewer leave the SM short of warps - both measured slower)
 template <typename T, int NP, int MODE>
 __global__ void __launch_bounds__(WIN_THREADS, 4)
 deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ offset,
