@@ -603,6 +603,17 @@ def main():
                                           "achieved_gbs": bytes_b / (ms_b * 1e-3) / 1e9, "roofline_frac": bytes_b / (ms_b * 1e-3) / 1e9 / peak_gbs,
                                           "mpix_per_s": pix_per_step_rank / (ms_b * 1e-3) / 1e6}
         del out_b, gq, gk, gv, ws
+        # the same forward on channels-last tensors (one warp per pixel, no tiles): same algorithmic bytes
+        ql, kl, vl = (x.permute(0, 2, 3, 1).contiguous() for x in (t["q"], t["k"], t["v"]))
+        with torch.no_grad():
+            ms_n = time_path(lambda: sapa_b200.sapa_fused_nhwc(ql, kl, vl, K, s), 10)
+        abytes = algorithmic_bytes(wl, esize)
+        paths["sapa_b_fused_forward_channels_last"] = {"ms": ms_n, "launches": 1, "algorithmic_bytes": abytes,
+                                                       "achieved_gbs": abytes / (ms_n * 1e-3) / 1e9,
+                                                       "roofline_frac": abytes / (ms_n * 1e-3) / 1e9 / peak_gbs,
+                                                       "mpix_per_s": pix_per_step_rank / (ms_n * 1e-3) / 1e6,
+                                                       "kernels": sapa_b200._lib.last_kernels()}
+        del ql, kl, vl
         # SAPA-D, config 3: 4 groups, 9 points, offsets ~ N(0, 0.5^2), q/k channels = d in total
         G_, P_ = 4, 9
         off = (torch.randn(B_, G_ * P_ * 2, s * H_, s * W_, device=device) * 0.5).to(dtype)

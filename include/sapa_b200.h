@@ -264,6 +264,14 @@ int sapa_fused_backward_slab(const void *grad_out, const void *query, const void
                              int B, int d, int C, int H, int W, int halo_top, int halo_bottom, int K, int s, int dtype,
                              void *stream);
 
+/* sapa_fused_forward for channels-last tensors: query [B, sH, sW, d], key [B, H, W, d], value [B, H, W, C] ->
+ * out [B, sH, sW, C]; `attn` (optional) receives the attention as [B, sH, sW, K*K].  Same arithmetic and border rule as
+ * the channels-first entry point (sapa_base.py:38-40).  Needs K <= 5, d and C multiples of 16 bytes worth of elements and
+ * 16-byte aligned tensors (SAPA_ERR_UNSUPPORTED / SAPA_ERR_ALIGNMENT otherwise); float32, float16, bfloat16; forward only.
+ * No counterpart in the reference, whose tensors are channels-first throughout. */
+int sapa_fused_forward_nhwc(const void *query, const void *key, const void *value, void *out, void *attn,
+                            int B, int d, int C, int H, int W, int K, int s, int dtype, void *stream);
+
 /* GroupNorm followed by the 1 x 1 projection that produces the query or the key (reference: sapa_base.py:27-34,
  * sapa_deform.py:35-42 - `self.q(self.norm_y(y))`, `self.k(self.norm_x(x))`), forward only:
  *   out[b, j, p] = bias[j] + sum_c weight[j, c] * (gamma[c] * (x[b, c, p] - mean[b, g(c)]) * rstd[b, g(c)] + beta[c])

@@ -11,12 +11,12 @@ import os as _os
 
 from .deform_functions import (DeformAVFunction, DeformQKFunction, DeformSapaFusedFunction, deform_av, deform_qk,
                                deform_sapa_fused)
-from .functions import AVFunction, QKFunction, SapaFusedFunction, av, qk, sapa_fused
+from .functions import AVFunction, QKFunction, SapaFusedFunction, av, qk, sapa_fused, sapa_fused_nhwc
 from .graphs import GraphedForward
 from .modules import SAPA, SAPADeform
 from .projection import project
 
-__all__ = ["qk", "av", "sapa_fused", "deform_qk", "deform_av", "deform_sapa_fused", "SAPA", "SAPADeform",
+__all__ = ["qk", "av", "sapa_fused", "sapa_fused_nhwc", "deform_qk", "deform_av", "deform_sapa_fused", "SAPA", "SAPADeform",
            "QKFunction", "AVFunction", "SapaFusedFunction", "DeformQKFunction", "DeformAVFunction",
            "DeformSapaFusedFunction", "GraphedForward", "project", "compat_path"]
 

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libsapa_b200.so")
-SOURCES = ["api.cu", "sapa_b.cu", "sapa_mma.cu", "sapa_tma.cu", "sapa_gath_mma.cu", "sapa_d.cu", "sapa_proj.cu"]
+SOURCES = ["api.cu", "sapa_b.cu", "sapa_mma.cu", "sapa_tma.cu", "sapa_gath_mma.cu", "sapa_d.cu", "sapa_proj.cu", "sapa_nhwc.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "tma_util.cuh"), os.path.join(INCLUDE, "sapa_b200.h")]
 
 NVCC_FLAGS = [

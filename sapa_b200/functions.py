@@ -159,3 +159,23 @@ class SapaFusedFunction(Function):
 def sapa_fused(query, key, value, kernel_size=5, scale_factor=2):
     """Fused SAPA-B attention; differentiable with respect to query, key and value."""
     return SapaFusedFunction.apply(query, key, value, kernel_size, scale_factor)
+
+
+def sapa_fused_nhwc(query, key, value, kernel_size=5, scale_factor=2, return_attn=False):
+    """Fused SAPA-B forward on channels-last tensors: ``query`` [B, sH, sW, d], ``key`` [B, H, W, d], ``value``
+    [B, H, W, C] -> [B, sH, sW, C] (plus the attention [B, sH, sW, K*K] when ``return_attn``).  Forward only: for
+    gradients use the channels-first ops.  The reference has no channels-last path."""
+    if not value.is_cuda:
+        raise NotImplementedError
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value)):
+        raise NotImplementedError("sapa_fused_nhwc is forward only; use sapa_fused (channels-first) for training")
+    _lib.check_tensors(("value", value), ("query", query), ("key", key))
+    n, hq, wq, d = query.shape
+    h, w, c = value.shape[1:]
+    assert key.shape == (n, h, w, d) and hq == h * scale_factor and wq == w * scale_factor
+    query, key, value = _lib.aligned(query), _lib.aligned(key), _lib.aligned(value)
+    out = torch.empty((n, hq, wq, c), dtype=value.dtype, device=value.device)
+    attn = torch.empty((n, hq, wq, kernel_size ** 2), dtype=value.dtype, device=value.device) if return_attn else None
+    _lib.call("sapa_fused_forward_nhwc", value.device, query, key, value, out, attn, n, d, c, h, w, kernel_size, scale_factor,
+              _lib.dtype_code(value))
+    return (out, attn) if return_attn else out

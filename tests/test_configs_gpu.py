@@ -202,3 +202,30 @@ def test_dense_window_deform_matches_the_separate_ops(shape):
         scale = float(want.abs().max())
         assert float((got - want).abs().max()) <= 1e-5 * max(scale, 1e-30)
     assert _lib.wait_timeout_flags(dev) == 0
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2), (torch.float16, 2e-3)])
+@pytest.mark.parametrize("shape", [(2, 16, 24, 9, 13, 5, 2), (1, 8, 8, 1, 1, 5, 2), (2, 32, 64, 7, 6, 3, 2), (1, 8, 16, 5, 4, 5, 4),
+                                   (1, 16, 16, 6, 6, 1, 1), (3, 64, 256, 16, 16, 5, 2)],
+                         ids=lambda s: "B%d_d%d_C%d_%dx%d_K%d_s%d" % s)
+def test_channels_last_forward_matches_channels_first(shape, dtype, tol, oracle):
+    """sapa_fused_forward_nhwc against the CPU oracle (through the permuted tensors) and against the channels-first fused
+    op: outputs and attention, odd sizes, window sizes 1 / 3 / 5, scale factors 1 / 2 / 4."""
+    import sapa_b200
+    from sapa_b200 import _lib
+    B, d, C, H, W, K, s = shape
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(41)
+    q, k, v = (torch.randn(*sh, generator=g).to(dtype) for sh in ((B, d, s * H, s * W), (B, d, H, W), (B, C, H, W)))
+    ql, kl, vl = (t.permute(0, 2, 3, 1).contiguous().to(dev) for t in (q, k, v))
+    out, attn = sapa_b200.sapa_fused_nhwc(ql, kl, vl, K, s, return_attn=True)
+    assert _lib.last_kernels() == ["sapa_nhwc_fwd_kernel"]
+    want = oracle.sapa_forward(q.double().numpy(), k.double().numpy(), v.double().numpy(), K, s)
+    got = out.permute(0, 3, 1, 2).double().cpu().numpy()
+    assert float(np.abs(got - want).max() / np.abs(want).max()) < tol
+    if sapa_b200.functions.fused_supported(K, s, dtype):
+        from sapa_b200.functions import fused_forward_raw
+        ref_out, ref_attn = fused_forward_raw(q.to(dev), k.to(dev), v.to(dev), K, s, True)
+        assert float((attn.permute(0, 3, 1, 2).float() - ref_attn.float()).abs().max()) < (1e-5 if dtype == torch.float32 else 1e-2)
+    with pytest.raises(NotImplementedError):
+        sapa_b200.sapa_fused_nhwc(ql.requires_grad_(), kl, vl, K, s)
