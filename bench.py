@@ -336,6 +336,71 @@ def measure_config5(name, world, rank, device, dist, steps=10, warm=3):
             "workload": f"{name}: B={w['B']}, C={w['C']}, d={w['d']}, {w['H']}x{w['W']} -> {s * w['H']}x{s * w['W']}"}
 
 
+def measure_deform_rows(world, rank, device, dist, steps=5, warm=3):
+    """SAPA-D fused forward, float32, on ONE 512^2 -> 1024^2 image (C=256, d=64, 4 groups x 9 points, offsets ~
+    N(0, 0.5^2)) split into row slabs over the ranks of this run (`sharding.sapa_deform_row_sharded`: the halo depth is
+    measured from the offsets at every step - a device reduction, a MAX all-reduce and a host read - then the halo rows of
+    key / value travel to the neighbours and the padded slab runs as an image of its own).  At N = 1 the whole image runs
+    through `deform_sapa_fused`.  Strong scaling; device time by CUDA events, max over ranks."""
+    import sapa_b200
+    from sapa_b200 import sharding
+    B, C, d, H, W, G, P, s = 1, 256, 64, 512, 512, 4, 9, 2
+    sl = sharding.row_slice(H, world, rank)
+    Hl = sl.stop - sl.start
+    gen = torch.Generator(device=device).manual_seed(70 + rank)
+    q = torch.randn(B, d, s * Hl, s * W, generator=gen, device=device)
+    k = torch.randn(B, d, Hl, W, generator=gen, device=device)
+    v = torch.randn(B, C, Hl, W, generator=gen, device=device)
+    off = 0.5 * torch.randn(B, 2 * G * P, s * Hl, s * W, generator=gen, device=device)
+    halo = sharding.deform_halo_rows(off, local_rows=Hl) if world > 1 else None
+
+    def step():
+        with torch.no_grad():
+            if world > 1:
+                return sharding.sapa_deform_row_sharded(q, k, v, off, P, s, G)      # measures the halo depth itself
+            return sapa_b200.deform_sapa_fused(q, k, v, off, P, s, G)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        t = e0.elapsed_time(e1) / steps
+        if world > 1:
+            tt = torch.tensor([t], device=device, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = float(tt.item())
+        return t
+
+    ms_measured = timed(step)
+    ms = ms_measured
+    if world > 1:
+        # resident padded key / value and a halo depth known beforehand (offsets bounded by the caller): nothing but the
+        # halo rows moves and no host read happens inside the step
+        del k, v
+        slab = sharding.DeformRowSlab(B, d, C, Hl, W, max(halo, 2), device, P, G)
+        gen2 = torch.Generator(device=device).manual_seed(70 + rank)
+        slab.key.copy_(torch.randn(B, d, Hl, W, generator=gen2, device=device))
+        slab.value.copy_(torch.randn(B, C, Hl, W, generator=gen2, device=device))
+        out = torch.empty(B, C, s * Hl, s * W, device=device)
+        ms = timed(lambda: slab.forward(q, off, halo=halo, out=out))
+    pix = B * s * H * s * W
+    return {"mpix_per_s": pix / (ms * 1e-3) / 1e6, "ms_per_step": ms, "steps": steps, "dtype": "f32", "n_gpus": world,
+            "sharding": "rows", "scaling": "strong", "halo_rows": halo,
+            "ms_per_step_halo_measured_every_step": ms_measured,
+            "workload": f"SAPA-D fused forward: B={B}, C={C}, d={d}, groups={G}, points={P}, {H}x{W} -> {s * H}x{s * W}"}
+
+
 # ------------------------------------------------------------------ GPU arm
 
 def main():
@@ -708,6 +773,7 @@ def main():
     if not args.no_extra and args.workload == "cfg2":
         for name in ("cfg5a", "cfg5b"):
             config5[name] = measure_config5(name, world, rank, device, dist)
+        config5["sapa_d_rows"] = measure_deform_rows(world, rank, device, dist)
 
     # ---- end to end: public op, pinned host buffers in and out, copies inside the timed region ----
     e2e_steps = max(3, min(args.steps, 30))

@@ -215,6 +215,17 @@ int sapa_deform_fused_forward_dense(const void *query, const void *key, const vo
                                     void *out, void *attn, void *workspace, size_t workspace_bytes,
                                     int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
 
+/* sapa_deform_fused_forward_dense for one row slab of a larger image (row-slab sharding of SAPA-D across GPUs): `key` and
+ * `value` hold halo_top + H + halo_bottom low-res rows per plane - the slab's own H rows with the neighbouring slabs'
+ * rows above and below (zeros where the image ends) - while `query`, `offset`, `out` and `attn` hold only the slab's own
+ * s*H high-res rows.  Exact when no sampling point of the slab reaches further than the halo (the caller derives the
+ * halo depth from max |offset_y|; rows beyond it read as outside the image).  Workspace as for H rows.
+ * No counterpart in the reference. */
+int sapa_deform_fused_forward_slab(const void *query, const void *key, const void *value, const void *offset,
+                                   void *out, void *attn, void *workspace, size_t workspace_bytes,
+                                   int B, int Cq, int C, int H, int W, int halo_top, int halo_bottom,
+                                   int P, int s, int G, int dtype, void *stream);
+
 /* sapa_deform_qk_forward and sapa_deform_av_forward by way of the dense 5 x 5 window (s = 2, float32): the two halves of
  * sapa_deform_fused_forward_dense with the reference's op boundaries - raw logits out (deform_qk_cuda_kernel.cu:139-197)
  * and attention in (deform_av_cuda_kernel.cu:139-195).  Same results as the gather kernels; `workspace`:

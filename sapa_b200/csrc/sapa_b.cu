@@ -604,18 +604,24 @@ static int check_common(const char *fn, int B, int C, int H, int W, int K, int s
 
 
 // sim / agg / gath dispatchers (tiled when possible, else generic); sim and agg also serve the dense path of SAPA-D
-int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
-                   cudaStream_t st) {
+// Slab form: `lo` holds `rows` = top + H + bottom low-res rows per plane, of which the H rows from `top` on are the
+// ones the high-res rows of `hi` / `out` belong to (rows = H, top = 0: a whole image).
+int run_sim_slab(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int rows, int top, int K, int s,
+                 int dtype, cudaStream_t st) {
     const bool al = all_aligned16(hi, lo, out);     // misaligned views take the scalar generic kernels
     if (al && K == 5 && s == 2 && fused_tma_supported(W, dtype)) {     // logit half of the TMA kernel
-        const int e = launch_fused_tma(2, hi, lo, nullptr, nullptr, out, nullptr, B, Cc, 0, H, W, H, 0, 0, H, dtype, st);
+        const int e = launch_fused_tma(2, hi, lo, nullptr, nullptr, out, nullptr, B, Cc, 0, H, W, rows, top, 0, H, dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
     if (al && tiled_supported(K, s, dtype)) {
         TileArgs a{};
         a.hi = hi; a.lo1 = lo; a.out_slots = out;
-        a.B = B; a.C1 = Cc; a.C2 = 0; a.H = H; a.W = W; a.rows = H; a.ytop0 = 0;
+        a.B = B; a.C1 = Cc; a.C2 = 0; a.H = H; a.W = W; a.rows = rows; a.ytop0 = top;
         return SAPA_DISPATCH_FAST(dtype, [&] { return launch_tile_ks<scalar_t, MODE_SIM>(a, K, st); });
+    }
+    if (rows != H || top != 0) {
+        set_error("run_sim_slab: a padded slab needs 16-byte aligned tensors and a tiled (K, s)");
+        return SAPA_ERR_UNSUPPORTED;
     }
     return SAPA_DISPATCH_ALL(dtype, [&] {
         const long long total = (long long)B * K * K * s * H * s * W;
@@ -625,18 +631,27 @@ int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int
     });
 }
 
-int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,
-                   cudaStream_t st) {
+int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st) {
+    return run_sim_slab(hi, lo, out, B, Cc, H, W, H, 0, K, s, dtype, st);
+}
+
+int run_agg_slab(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int rows, int top, int K, int s,
+                 int dtype, cudaStream_t st) {
     const bool al = all_aligned16(wt, lo, out);
     if (al && K == 5 && s == 2 && fused_tma_supported(W, dtype)) {     // aggregation half of the TMA kernel
-        const int e = launch_fused_tma(3, nullptr, nullptr, lo, out, const_cast<void *>(wt), nullptr, B, 0, Cc, H, W, H, 0, 0, H, dtype, st);
+        const int e = launch_fused_tma(3, nullptr, nullptr, lo, out, const_cast<void *>(wt), nullptr, B, 0, Cc, H, W, rows, top, 0, H,
+                                       dtype, st);
         if (e != SAPA_ERR_UNSUPPORTED) return e;
     }
     if (al && tiled_supported(K, s, dtype)) {
         TileArgs a{};
         a.slots_in = wt; a.lo2 = lo; a.out_hi = out;
-        a.B = B; a.C1 = 0; a.C2 = Cc; a.H = H; a.W = W; a.rows = H; a.ytop0 = 0;
+        a.B = B; a.C1 = 0; a.C2 = Cc; a.H = H; a.W = W; a.rows = rows; a.ytop0 = top;
         return SAPA_DISPATCH_FAST(dtype, [&] { return launch_tile_ks<scalar_t, MODE_AGG>(a, K, st); });
+    }
+    if (rows != H || top != 0) {
+        set_error("run_agg_slab: a padded slab needs 16-byte aligned tensors and a tiled (K, s)");
+        return SAPA_ERR_UNSUPPORTED;
     }
     return SAPA_DISPATCH_ALL(dtype, [&] {
         const long long total = (long long)B * Cc * s * H * s * W;
@@ -644,6 +659,10 @@ int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int
             static_cast<const scalar_t *>(wt), static_cast<const scalar_t *>(lo), static_cast<scalar_t *>(out), B, Cc, H, W, K, s);
         return check_launch("agg_generic_kernel");
     });
+}
+
+int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st) {
+    return run_agg_slab(wt, lo, out, B, Cc, H, W, H, 0, K, s, dtype, st);
 }
 
 int run_gath(const void *hi, const void *wt, void *out, int B, int Cc, int H, int W, int K, int s, int dtype,

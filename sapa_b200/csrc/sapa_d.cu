@@ -315,11 +315,12 @@ __global__ void __launch_bounds__(WIN_THREADS, 4)
 deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ offset,
                      const T *__restrict__ dense /* [B*G, 25, sH, sW] */, T *__restrict__ attn /* [B, G, P, sH, sW] or null */,
                      T *__restrict__ window /* [B*G, 25, sH, sW] */, OutlierTap *__restrict__ taps,
-                     unsigned int *__restrict__ tap_count, int B, int Cq, int H, int W, int P_runtime, int G) {
+                     unsigned int *__restrict__ tap_count, int B, int Cq, int H, int W, int P_runtime, int G,
+                     int rows /* low-res rows held by key */, int ytop /* the row of key that is parent row 0 */) {
     constexpr int PMAX = NP > 0 ? NP : MAXP;
     const int P = NP > 0 ? NP : P_runtime;
     const int sH = 2 * H, sW = 2 * W, gq = Cq / G;
-    const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
+    const size_t hi = (size_t)sH * sW, lo = (size_t)rows * W;
     const int lane = threadIdx.x & 31;
     const long long total = (long long)B * G * hi;
     for (long long i0 = (long long)blockIdx.x * WIN_THREADS; i0 < total; i0 += (long long)gridDim.x * WIN_THREADS) {
@@ -328,7 +329,7 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
         const size_t pix = live ? (size_t)(i % hi) : 0;
         const long long bg = live ? i / (long long)hi : 0;
         const int g = (int)(bg % G), b = (int)(bg / G);
-        const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = qh >> 1, px = qw >> 1;
+        const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = (qh >> 1) + ytop, px = qw >> 1;   // rows in the frame of key
         float d[25], wd[25], oh[PMAX], ow[PMAX], logit[PMAX];
         const T *dp = dense + (size_t)bg * 25 * hi + pix;
 #pragma unroll
@@ -350,7 +351,7 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
             logit[p] = 0.f;
             if (live && p < P) {
                 WindowTap t;
-                t.setup(oh[p], ow[p], H, W, py, px);
+                t.setup(oh[p], ow[p], rows, W, py, px);
                 float vy[5], vx[5];
                 t.axis(vy, t.r0, t.lh);
                 t.axis(vx, t.c0, t.lw);
@@ -381,7 +382,7 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
                 } else if (t.inside) {        // outlier: gather the key directly
                     outliers |= 1u << p;
                     Bilinear<float> bl;
-                    bl.setup(oh[p], ow[p], H, W);
+                    bl.setup(oh[p], ow[p], rows, W);
                     const T *qp = query + ((size_t)b * Cq + (size_t)g * gq) * hi + pix;
                     const T *kp = key + ((size_t)b * Cq + (size_t)g * gq) * lo;
                     for (int c = 0; c < gq; ++c) acc += bl.sample(kp + (size_t)c * lo) * to_acc(qp[(size_t)c * hi]);
@@ -455,19 +456,19 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
 template <typename T>
 __global__ void deform_outlier_kernel(const OutlierTap *__restrict__ taps, const unsigned int *__restrict__ tap_count,
                                       const T *__restrict__ value, const T *__restrict__ offset, T *__restrict__ out,
-                                      int C, int H, int W, int P, int G) {
+                                      int C, int H, int W, int P, int G, int rows, int ytop) {
     const int sW = 2 * W, gc = C / G;
-    const size_t hi = (size_t)(2 * H) * sW, lo = (size_t)H * W;
+    const size_t hi = (size_t)(2 * H) * sW, lo = (size_t)rows * W;
     const unsigned int n = *tap_count;
     const int sub = threadIdx.x & 7;
     for (unsigned int e = (blockIdx.x * blockDim.x + threadIdx.x) >> 3; e < n; e += (gridDim.x * blockDim.x) >> 3) {
         const OutlierTap t = taps[e];
         const size_t pix = t.pix;
-        const int px = (int)(pix % sW) >> 1, py = (int)(pix / sW) >> 1;
+        const int px = (int)(pix % sW) >> 1, py = ((int)(pix / sW) >> 1) + ytop;
         const float w = float(px) + to_acc(__ldg(offset + (size_t)t.k * 2 * hi + pix));
         const float h = float(py) + to_acc(__ldg(offset + (size_t)t.k * 2 * hi + hi + pix));
         Bilinear<float> bl;
-        bl.setup(h, w, H, W);
+        bl.setup(h, w, rows, W);
         const size_t bg = t.k / (unsigned int)P;
         const T *vp = value + bg * gc * lo;
         T *op = out + bg * gc * hi + pix;
@@ -975,6 +976,10 @@ namespace sapa {
 int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st);
 int run_agg(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st);
 int run_gath(const void *hi, const void *wt, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st);
+int run_sim_slab(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int rows, int top, int K, int s, int dtype,
+                 cudaStream_t st);
+int run_agg_slab(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int rows, int top, int K, int s, int dtype,
+                 cudaStream_t st);
 }
 
 extern "C" {
@@ -987,12 +992,15 @@ size_t sapa_deform_fused_forward_workspace(int B, int H, int W, int P, int s, in
     return (size_t)B * G * 50 * hi * dtype_size(dtype) + (size_t)B * G * P * hi * sizeof(OutlierTap) + 16;
 }
 
-int sapa_deform_fused_forward_dense(const void *query, const void *key, const void *value, const void *offset, void *out,
-                                    void *attn, void *workspace, size_t workspace_bytes, int B, int Cq, int C, int H, int W,
-                                    int P, int s, int G, int dtype, void *stream) {
-    const char *fn = "sapa_deform_fused_forward_dense";
+int sapa_deform_fused_forward_slab(const void *query, const void *key, const void *value, const void *offset, void *out,
+                                   void *attn, void *workspace, size_t workspace_bytes, int B, int Cq, int C, int H, int W,
+                                   int halo_top, int halo_bottom, int P, int s, int G, int dtype, void *stream) {
+    const char *fn = "sapa_deform_fused_forward_slab";
     trace_reset();
     if (int e = check_deform(fn, B, Cq, C, H, W, P, s, G, dtype)) return e;
+    SAPA_REQUIRE(halo_top >= 0 && halo_bottom >= 0 && ((long long)halo_top + H + halo_bottom) * W < (1LL << 31), SAPA_ERR_ARGUMENT,
+                 "%s: bad halo (%d, %d)", fn, halo_top, halo_bottom);
+    const int rows = halo_top + H + halo_bottom;
     SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset);
     SAPA_CHECK_PTR(fn, out);
     const size_t need = sapa_deform_fused_forward_workspace(B, H, W, P, s, G, dtype);
@@ -1010,7 +1018,7 @@ int sapa_deform_fused_forward_dense(const void *query, const void *key, const vo
         return SAPA_ERR_LAUNCH;
     }
     // 1. dense 25-slot similarity of every group: the B x G groups are images of Cq / G channels
-    if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
+    if (int e = run_sim_slab(query, key, dense, B * G, Cq / G, H, W, rows, halo_top, 5, 2, dtype, st)) return e;
     // 2. attention over the points, dense window weights, list of the points that leave the window
     {
         const long long total = (long long)B * G * hi;
@@ -1018,19 +1026,26 @@ int sapa_deform_fused_forward_dense(const void *query, const void *key, const vo
         const int grid = grid_1d(total, WIN_THREADS);
         if (P == 9)          // the 3 x 3 points of the reference modules' default
             deform_window_kernel<float, 9, WIN_FUSED><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, static_cast<float *>(attn), window, taps, tap_count,
-                                                                       B, Cq, H, W, P, G);
+                                                                       B, Cq, H, W, P, G, rows, halo_top);
         else
             deform_window_kernel<float, 0, WIN_FUSED><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, static_cast<float *>(attn), window, taps, tap_count,
-                                                                       B, Cq, H, W, P, G);
+                                                                       B, Cq, H, W, P, G, rows, halo_top);
         if (int e = check_launch("deform_window_kernel")) return e;
     }
     // 3. aggregation of every group's channels over the window
-    if (int e = run_agg(window, value, out, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
+    if (int e = run_agg_slab(window, value, out, B * G, C / G, H, W, rows, halo_top, 5, 2, dtype, st)) return e;
     // 4. the listed points (the count is only known on the device: a fixed grid strides over the list)
     deform_outlier_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, static_cast<const float *>(value),
                                                           static_cast<const float *>(offset), static_cast<float *>(out),
-                                                          C, H, W, P, G);
+                                                          C, H, W, P, G, rows, halo_top);
     return check_launch("deform_outlier_kernel");
+}
+
+int sapa_deform_fused_forward_dense(const void *query, const void *key, const void *value, const void *offset, void *out,
+                                    void *attn, void *workspace, size_t workspace_bytes, int B, int Cq, int C, int H, int W,
+                                    int P, int s, int G, int dtype, void *stream) {
+    return sapa_deform_fused_forward_slab(query, key, value, offset, out, attn, workspace, workspace_bytes, B, Cq, C, H, W, 0, 0,
+                                          P, s, G, dtype, stream);
 }
 
 // deform_qk and deform_av through the dense window (s = 2, float32): the halves of the fused forward, with the reference's
@@ -1053,7 +1068,7 @@ int sapa_deform_qk_forward_dense(const void *query, const void *key, const void 
     const long long total = (long long)B * G * hi;
     const float *q = static_cast<const float *>(query), *k = static_cast<const float *>(key), *o = static_cast<const float *>(offset);
     deform_window_kernel<float, 0, WIN_LOGITS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-        q, k, o, dense, static_cast<float *>(out), nullptr, nullptr, nullptr, B, Cq, H, W, P, G);
+        q, k, o, dense, static_cast<float *>(out), nullptr, nullptr, nullptr, B, Cq, H, W, P, G, H, 0);
     return check_launch("deform_window_kernel<logits>");
 }
 
@@ -1081,11 +1096,11 @@ int sapa_deform_av_forward_dense(const void *attn, const void *value, const void
     const float *o = static_cast<const float *>(offset);
     // the attention is only read in this mode
     deform_window_kernel<float, 0, WIN_WEIGHTS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-        nullptr, nullptr, o, nullptr, const_cast<float *>(static_cast<const float *>(attn)), window, taps, tap_count, B, C, H, W, P, G);
+        nullptr, nullptr, o, nullptr, const_cast<float *>(static_cast<const float *>(attn)), window, taps, tap_count, B, C, H, W, P, G, H, 0);
     if (int e = check_launch("deform_window_kernel<weights>")) return e;
     if (int e = run_agg(window, value, out, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
     deform_outlier_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, static_cast<const float *>(value), o,
-                                                          static_cast<float *>(out), C, H, W, P, G);
+                                                          static_cast<float *>(out), C, H, W, P, G, H, 0);
     return check_launch("deform_outlier_kernel");
 }
 

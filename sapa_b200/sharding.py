@@ -134,13 +134,19 @@ def exchange_row_halo(tensors, halo: int, group=None):
         return list(tensors)
     Hl = tensors[0].size(2)
     check_row_split(Hl, halo, group)
-    padded = []
-    for t in tensors:
-        p = t.new_zeros((t.size(0), t.size(1), Hl + 2 * halo, t.size(3)))
-        p[:, :, halo:halo + Hl, :] = t
-        padded.append(p)
+    padded = [_pad_rows(t, halo) for t in tensors]
     _exchange_into(padded, halo, group)
     return padded
+
+
+def _pad_rows(t: torch.Tensor, halo: int) -> torch.Tensor:
+    """[B,C,Hl,W] -> [B,C,halo+Hl+halo,W] with zero halo rows (only the halo rows are cleared: one pass over the slab)."""
+    Hl = t.size(2)
+    p = t.new_empty((t.size(0), t.size(1), Hl + 2 * halo, t.size(3)))
+    p[:, :, :halo, :] = 0
+    p[:, :, halo + Hl:, :] = 0
+    p[:, :, halo:halo + Hl, :] = t
+    return p
 
 
 class RowSlab:
@@ -276,3 +282,175 @@ def sapa_fused_row_sharded(query, key, value, kernel_size=5, scale_factor=2, gro
     run the backward pass: it exchanges halo-row gradients with the neighbours).
     """
     return _RowShardedFused.apply(query, key, value, kernel_size, scale_factor, group)
+
+
+# ---------------------------------------------------------------------------------------------- SAPA-D row slabs
+
+class _HaloPad(torch.autograd.Function):
+    """[B,C_i,Hl,W] slabs -> [B,C_i,halo+Hl+halo,W] with the neighbours' rows in the halos (zeros at the image border).
+    Backward: the halo rows of the gradients go back to the neighbours and are added to their edge rows."""
+
+    @staticmethod
+    def forward(ctx, halo, group, *tensors):
+        ctx.halo, ctx.group = halo, group
+        padded = [_pad_rows(t, halo) for t in tensors]         # the caller has checked the shares of all ranks
+        _exchange_into(padded, halo, group)
+        return tuple(padded)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        halo = ctx.halo
+        padded = [g.contiguous().clone() for g in grads]
+        if dist.is_initialized():
+            _reduce_halo_grads(padded, halo, ctx.group)
+        Hl = padded[0].size(2) - 2 * halo
+        return (None, None) + tuple(p[:, :, halo:halo + Hl, :].contiguous() for p in padded)
+
+
+def deform_halo_rows(offset: torch.Tensor, group=None, local_rows=None) -> int:
+    """Halo depth (low-res rows) that makes row-slab sharding of SAPA-D exact for these offsets.
+
+    A sampling point of a pixel with parent row y lies at row y + oy and reads rows floor(y + oy) and floor(y + oy) + 1
+    (deform_qk_cuda_kernel.cu:159-170 of the reference: bilinear corners of ``h = qh / s + offset_y``), so with
+    m = max |oy| over every rank no tap leaves ``floor(m) + 1`` rows beyond a slab.  The y offsets are the odd
+    channels of ``offset`` (x first, then y, per sampling point).  One device reduction, one MAX all-reduce and one
+    host read: the depth must be the same on every rank.  With ``local_rows`` (this rank's share of rows) the same
+    all-reduce also carries the smallest share, and a depth beyond it raises ``ValueError`` on every rank together
+    (a halo comes from the direct neighbour only).
+    """
+    if offset.numel():
+        lo, hi = torch.aminmax(offset.detach()[:, 1::2])            # one pass, no temporary
+        m = torch.maximum(-lo, hi).to(torch.float32).reshape(1)
+    else:
+        m = offset.new_zeros(1, dtype=torch.float32)
+    rows = m.new_full((1,), -float(local_rows) if local_rows is not None else -float("inf"))
+    both = torch.cat([m, rows])                                     # MAX of (-rows) = -(smallest share)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world > 1:
+        dist.all_reduce(both, op=dist.ReduceOp.MAX, group=group)
+    m, min_rows = float(both[0].item()), -float(both[1].item())
+    if not m < float("inf"):
+        raise ValueError("SAPA-D row-slab sharding: the offsets hold a non-finite value")
+    depth = int(m) + 1
+    if world > 1 and depth > min_rows:
+        raise ValueError(f"SAPA-D row-slab sharding: the offsets reach {depth} rows beyond a slab but the smallest slab has "
+                         f"{int(min_rows)} rows; shard by batch or gather the image instead")
+    return depth
+
+
+def _deform_slab_forward(query, key, value, offset, num_point, s, groups, halo, group):
+    """Inference path of :func:`sapa_deform_row_sharded`: only key and value get halo rows, the kernels take the slab
+    form (``sapa_deform_fused_forward_slab``), so query, offsets and output stay as they are and no row is computed
+    twice.  Returns None when the dense-window kernels do not cover the configuration (the caller pads instead)."""
+    from . import _lib
+    from .deform_functions import _dense_workspace_bytes
+    B, d, Hl, W = key.shape
+    C = value.size(1)
+    if not query.is_cuda:
+        return None
+    nbytes = _dense_workspace_bytes(query, B, Hl, W, num_point, s, groups)
+    if not nbytes or (W * query.element_size()) % 16 != 0:
+        return None
+    key_p, value_p = _pad_rows(key, halo), _pad_rows(value, halo)
+    _exchange_into([key_p, value_p], halo, group)
+    query, offset = query.contiguous(), offset.contiguous()
+    _lib.check_tensors(("query", query), ("key", key_p), ("value", value_p), ("offset", offset))
+    out = torch.empty((B, C, s * Hl, s * W), dtype=value.dtype, device=value.device)
+    workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
+    _lib.call("sapa_deform_fused_forward_slab", query.device, query, key_p, value_p, offset, out, None, workspace, nbytes,
+              B, d, C, Hl, W, halo, halo, num_point, s, groups, _lib.dtype_code(query))
+    return out
+
+
+def sapa_deform_row_sharded(query, key, value, offset, num_point=9, scale_factor=2, groups=4, group=None, halo=None,
+                            op=None):
+    """Fused SAPA-D on this rank's row slab of one larger image; equals the same rows of the unsharded op.
+
+    ``query`` [B,d,s*Hl,s*W], ``key`` [B,d,Hl,W], ``value`` [B,C,Hl,W], ``offset`` [B,2*groups*num_point,s*Hl,s*W]
+    hold the rank's rows.  The offsets are unbounded, so the halo depth is data-dependent: ``halo=None`` measures it
+    (:func:`deform_halo_rows`, one host read per call); a caller that bounds its offsets passes the bound's depth
+    instead.  Every rank must own at least ``halo`` rows (``ValueError`` on all ranks together otherwise: fall back to
+    batch sharding or gather the image).  The slab, padded with the neighbours' rows - zeros at the image's own top
+    and bottom, which sample exactly like the reference's dropped corners and its outside-the-image guard - goes to
+    the kernels in one of two ways.  No gradient needed (float32, s = 2): the slab form of the dense-window kernels,
+    where only key and value carry halo rows.  Otherwise the padded slab is run as an image of its own with zero
+    query / offset rows over the halo, and the halo rows are cut from the result (2*halo / (Hl + 2*halo) of the work is
+    thrown away, the price of reusing the single-GPU autograd function unchanged); the backward pass returns the
+    halo-row gradients of key and value to the neighbours (every rank must run it).
+
+    ``op`` replaces the per-slab operator (default :func:`sapa_b200.deform_sapa_fused`); the CPU tests pass a
+    PyTorch transcription.
+    """
+    from .deform_functions import deform_sapa_fused
+    if op is None:
+        op = deform_sapa_fused
+    s = scale_factor
+    Hl = key.size(2)
+    if halo is None:
+        halo = deform_halo_rows(offset, group, local_rows=Hl)       # checks the shares of all ranks in the same all-reduce
+    else:
+        check_row_split(Hl, halo, group)
+    if halo == 0 or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return op(query, key, value, offset, num_point, s, groups)
+    if op is deform_sapa_fused and not (torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value, offset))):
+        fast = _deform_slab_forward(query, key, value, offset, num_point, s, groups, halo, group)
+        if fast is not None:
+            return fast
+    key_p, value_p = _HaloPad.apply(halo, group, key, value)
+    pad = (0, 0, s * halo, s * halo)
+    query_p = torch.nn.functional.pad(query, pad)
+    offset_p = torch.nn.functional.pad(offset, pad)
+    out = op(query_p.contiguous(), key_p, value_p, offset_p.contiguous(), num_point, s, groups)
+    return out[:, :, s * halo:s * (halo + Hl), :]
+
+
+class DeformRowSlab:
+    """A rank's row slab of ONE image for repeated SAPA-D forward passes (inference): key and value live in buffers
+    padded with ``max_halo`` rows above and below, so that a step moves nothing but the halo rows.
+
+    ``slab.key`` [B,d,Hl,W] and ``slab.value`` [B,C,Hl,W] are views of the rank's own rows: the producer writes them
+    in place.  :meth:`forward` exchanges ``halo`` rows with the neighbours (``halo=None``: measured from the offsets,
+    one host read; a caller whose offsets are bounded - a clamp or a tanh in front of the op - passes the bound's depth
+    and the step stays asynchronous), and runs the slab form of the dense-window kernels on the rank's own query /
+    offset rows.  Every rank must own at least ``max_halo`` rows (checked once, here, on all ranks together); a step
+    whose depth exceeds ``max_halo`` raises ``ValueError`` on every rank (the depth is the same everywhere).
+    float32, scale factor 2 (the dense-window kernels).  The reference has no multi-device code.
+    """
+
+    def __init__(self, batch, channels_qk, channels_v, local_rows, width, max_halo, device, num_point=9, groups=4,
+                 group=None):
+        if max_halo < 2:
+            raise ValueError("max_halo must be at least 2 (the 5 x 5 window of the dense similarity)")
+        check_row_split(local_rows, max_halo, group)
+        self.group, self.cap, self.rows, self.width = group, int(max_halo), int(local_rows), int(width)
+        self.num_point, self.groups = num_point, groups
+        rows = local_rows + 2 * self.cap
+        self.key_padded = torch.zeros((batch, channels_qk, rows, width), dtype=torch.float32, device=device)
+        self.value_padded = torch.zeros((batch, channels_v, rows, width), dtype=torch.float32, device=device)
+        self.key = self.key_padded[:, :, self.cap:self.cap + local_rows, :]
+        self.value = self.value_padded[:, :, self.cap:self.cap + local_rows, :]
+        self._workspace = None
+
+    def forward(self, query, offset, halo=None, out=None):
+        from . import _lib
+        B, d = self.key_padded.shape[:2]
+        C, Hl, W, P, G, s = self.value_padded.size(1), self.rows, self.width, self.num_point, self.groups, 2
+        if halo is None:
+            halo = deform_halo_rows(offset, self.group)
+        if halo > self.cap:
+            raise ValueError(f"the offsets reach {halo} rows beyond the slab, the buffers hold {self.cap}")
+        depth = max(int(halo), 2)            # the dense similarity always reads the two window rows above and below
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            lo, hi = self.cap - depth, self.cap + Hl + depth
+            _exchange_into([self.key_padded[:, :, lo:hi, :], self.value_padded[:, :, lo:hi, :]], depth, self.group)
+        _lib.check_tensors(("query", query), ("key", self.key_padded), ("value", self.value_padded), ("offset", offset))
+        nbytes = int(_lib.lib().sapa_deform_fused_forward_workspace(B, Hl, W, P, s, G, _lib.SAPA_F32))
+        if nbytes == 0:
+            raise RuntimeError("DeformRowSlab needs float32, at most 16 points and rows of 16 bytes")
+        if self._workspace is None or self._workspace.numel() < nbytes:
+            self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
+        if out is None:
+            out = torch.empty((B, C, s * Hl, s * W), dtype=torch.float32, device=query.device)
+        _lib.call("sapa_deform_fused_forward_slab", query.device, query, self.key_padded, self.value_padded, offset, out, None,
+                  self._workspace, nbytes, B, d, C, Hl, W, self.cap, self.cap, P, s, G, _lib.SAPA_F32)
+        return out

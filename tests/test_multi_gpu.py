@@ -74,3 +74,67 @@ def test_row_sharded_equals_unsharded_rows_on_two_gpus(dtype_name):
         ret = mgr.dict()
         mp.spawn(_worker, args=(2, port, dtype_name, ret), nprocs=2, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def _worker_deform(rank, world, port, ret):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import sapa_b200
+        from sapa_b200 import sharding
+        B, d, C, H, W, G, P, s = 2, 32, 64, 48, 32, 4, 9, 2
+        g = torch.Generator().manual_seed(29)
+        q, k, v, off, go = (torch.randn(*sh, generator=g).to(dev) for sh in (
+            (B, d, s * H, s * W), (B, d, H, W), (B, C, H, W), (B, 2 * G * P, s * H, s * W), (B, C, s * H, s * W)))
+        off = 0.5 * off
+        full_in = [t.clone().requires_grad_() for t in (q, k, v, off)]
+        full = sapa_b200.deform_sapa_fused(*full_in, P, s, G)
+        grads = torch.autograd.grad(full, full_in, go)
+        rows = sharding.row_slice(H, world, rank)
+        hi = slice(s * rows.start, s * rows.stop)
+        mine_in = [q[:, :, hi], k[:, :, rows], v[:, :, rows], off[:, :, hi]]
+        mine_in = [t.contiguous().requires_grad_() for t in mine_in]
+        depth = sharding.deform_halo_rows(mine_in[3])
+        mine = sharding.sapa_deform_row_sharded(*mine_in, P, s, G)
+        mine_grads = torch.autograd.grad(mine, mine_in, go[:, :, hi].contiguous())
+        torch.cuda.synchronize()
+
+        def close(a, b, tol=2e-5):
+            return float((a - b).abs().max()) <= tol * float(b.abs().max())
+        ok = depth == int(off[:, 1::2].abs().max()) + 1 and close(mine, full[:, :, hi])
+        with torch.no_grad():       # inference: the slab form of the kernels, no padded query / offsets
+            fast = sharding.sapa_deform_row_sharded(*[t.detach() for t in mine_in], P, s, G)
+        ok = ok and "deform_window_kernel" in sapa_b200._lib.last_kernels() and close(fast, full[:, :, hi])
+        # resident slab: halo rows exchanged in place; first with the measured depth, then with a larger given bound
+        slab = sharding.DeformRowSlab(B, d, C, rows.stop - rows.start, W, depth + 2, dev, P, G)
+        slab.key.copy_(k[:, :, rows]); slab.value.copy_(v[:, :, rows])
+        qd, od = mine_in[0].detach(), mine_in[3].detach()
+        ok = ok and close(slab.forward(qd, od), full[:, :, hi]) and close(slab.forward(qd, od, halo=depth + 1), full[:, :, hi])
+        try:
+            slab.forward(qd, od, halo=depth + 3)
+            ok = False
+        except ValueError:
+            pass
+        for got, want, sl in zip(mine_grads, grads, (hi, rows, rows, hi)):
+            ok = ok and close(got, want[:, :, sl])
+        ret[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_deform_row_sharded_equals_unsharded_rows_on_two_gpus():
+    """SAPA-D on two row slabs with the measured halo depth: output rows and the gradients of query, key, value and
+    offsets equal the rows of the unsharded op (float32; sums over atomics, so to rounding)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_deform, args=(2, port, ret), nprocs=2, join=True)
+        assert dict(ret) == {0: True, 1: True}

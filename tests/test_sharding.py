@@ -153,3 +153,80 @@ def test_halo_gradient_reduction_gloo(world, halo):
         ret = mgr.dict()
         mp.spawn(_worker_reduce, args=(world, port, halo, ret), nprocs=world, join=True)
         assert dict(ret) == {r: True for r in range(world)}
+
+
+def _deform_case(world, hl, sigma):
+    """One image split into ``world`` slabs of ``hl`` low-res rows: float64 so that the comparison can be tight."""
+    g = torch.Generator().manual_seed(23)
+    B, d, C, W, G, P, s = 1, 8, 8, 6, 2, 4, 2
+    H = world * hl
+    q = torch.randn(B, d, s * H, s * W, generator=g, dtype=torch.float64)
+    k = torch.randn(B, d, H, W, generator=g, dtype=torch.float64)
+    v = torch.randn(B, C, H, W, generator=g, dtype=torch.float64)
+    off = sigma * torch.randn(B, 2 * G * P, s * H, s * W, generator=g, dtype=torch.float64)
+    go = torch.randn(B, C, s * H, s * W, generator=g, dtype=torch.float64)
+    return q, k, v, off, go, (P, s, G)
+
+
+def _worker_deform(rank, world, port, sigma, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import unfold_port
+        hl = 5
+        q, k, v, off, go, (P, s, G) = _deform_case(world, hl, sigma)
+        full = [t.clone().requires_grad_(True) for t in (q, k, v, off)]
+        want = unfold_port.deform_sapa(*full, P, s, G)
+        want.backward(go)
+        lo, hi = slice(rank * hl, (rank + 1) * hl), slice(s * rank * hl, s * (rank + 1) * hl)
+        mine = [q[:, :, hi].clone(), k[:, :, lo].clone(), v[:, :, lo].clone(), off[:, :, hi].clone()]
+        mine = [t.requires_grad_(True) for t in mine]
+        depth = sharding.deform_halo_rows(mine[3])
+        got = sharding.sapa_deform_row_sharded(*mine, P, s, G, op=unfold_port.deform_sapa)
+        got.backward(go[:, :, hi])
+        ok = depth == int(off[:, 1::2].abs().max()) + 1 and depth <= hl
+        ok = ok and bool(torch.allclose(got, want[:, :, hi], atol=1e-12))
+        for t, f, rows in zip(mine, full, (hi, lo, lo, hi)):
+            ok = ok and bool(torch.allclose(t.grad, f.grad[:, :, rows], atol=1e-12))
+        ret[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,sigma", [(2, 0.5), (3, 1.0)])
+def test_deform_row_sharding_equals_the_unsharded_rows_gloo(world, sigma):
+    """SAPA-D on row slabs with a measured halo depth: output rows and all four gradients equal the unsharded op's
+    (PyTorch transcription as the per-slab operator; the CUDA kernels take its place on GPUs)."""
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_deform, args=(world, port, sigma, ret), nprocs=world, join=True)
+        assert dict(ret) == {r: True for r in range(world)}
+
+
+def _worker_deform_refuse(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import unfold_port
+        q, k, v, off, _, (P, s, G) = _deform_case(world, 2, 0.1)
+        off[0, 1, 0, 0] = 7.5            # one far point on rank 0: depth 8 > 2 rows per rank, seen by every rank
+        lo, hi = slice(rank * 2, (rank + 1) * 2), slice(s * rank * 2, s * (rank + 1) * 2)
+        try:
+            sharding.sapa_deform_row_sharded(q[:, :, hi], k[:, :, lo], v[:, :, lo], off[:, :, hi], P, s, G,
+                                             op=unfold_port.deform_sapa)
+            ret[rank] = "no error"
+        except ValueError:
+            ret[rank] = "raised"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_deform_row_sharding_refuses_a_halo_deeper_than_a_slab_on_every_rank():
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_deform_refuse, args=(2, port, ret), nprocs=2, join=True)
+        assert dict(ret) == {0: "raised", 1: "raised"}
