@@ -199,13 +199,14 @@ int sapa_deform_fused_forward(const void *query, const void *key, const void *va
                               void *out, void *attn,
                               int B, int Cq, int C, int H, int W, int P, int s, int G, int dtype, void *stream);
 
-/* The same result as sapa_deform_fused_forward by way of the SAPA-B kernels, for s = 2 and float32: with offsets inside
+/* The same result as sapa_deform_fused_forward by way of the SAPA-B kernels, for s = 2 and float32 (float16 / bfloat16
+ * too when W is a multiple of 8: 16-bit operands, float32 similarity in the workspace): with offsets inside
  * [-2, 2) low-res pixels every sampling point falls into the 5 x 5 window of the pixel's parent, so the logits are
  * bilinear combinations of the dense 25-slot similarity of each group (one call of the sim kernel with the B x G
  * groups as images) and the aggregation is the 5 x 5 aggregation with per-group window weights (one call of the agg
  * kernel); a small kernel in between forms the softmax over the points and the window weights and lists the points
- * that leave the window, and a last one adds the listed points to the output with atomics (any offset is handled,
- * large ones just cost more).  Several times faster than sapa_deform_fused_forward at B=8, C=256, 64x64 -> 128x128.
+ * that leave the window, and a last one adds the listed points to the output, one read-modify-write per output element
+ * and no atomics, so the result is deterministic (any offset is handled, large ones just cost more).  Several times faster than sapa_deform_fused_forward at B=8, C=256, 64x64 -> 128x128.
  * `workspace` holds the dense similarity, the window weights and the list: sapa_deform_fused_forward_workspace()
  * bytes, 16-byte aligned, owned by the caller.  `attn` (optional) receives the attention over the points.  Other
  * configurations return SAPA_ERR_UNSUPPORTED (the workspace query returns 0 for them).

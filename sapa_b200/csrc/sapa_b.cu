@@ -541,6 +541,9 @@ int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void
                      int H, int W, int rows, int ytop0, int y_begin, int y_end, int dtype, cudaStream_t st);
 int launch_fused_mma(const void *q, const void *k, const void *v, void *out, void *attn, int B, int d, int C, int H, int W,
                      int rows, int ytop0, int dtype, cudaStream_t st);
+int launch_fused_tma_slots(int mode, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d,
+                           int C, int H, int W, int rows, int ytop0, int y_begin, int y_end, int dtype, bool slots_f32,
+                           cudaStream_t st);
 
 int tma_wait_timeout_flag();
 int proj_wait_timeout_flag();
@@ -629,6 +632,17 @@ int run_sim_slab(const void *hi, const void *lo, void *out, int B, int Cc, int H
             static_cast<const scalar_t *>(hi), static_cast<const scalar_t *>(lo), static_cast<scalar_t *>(out), B, Cc, H, W, K, s);
         return check_launch("sim_generic_kernel");
     });
+}
+
+// 16-bit tensors with a float32 slot tensor (K = 5, s = 2, TMA kernel only): sim writes float32 logits.  The dense-window
+// path of SAPA-D keeps its 25-slot similarity at full precision this way.
+int run_sim_mixed(const void *hi, const void *lo, float *out, int B, int Cc, int H, int W, int rows, int top, int dtype,
+                  cudaStream_t st) {
+    if (!(all_aligned16(hi, lo, out) && (dtype == SAPA_F16 || dtype == SAPA_BF16) && fused_tma_supported(W, dtype))) {
+        set_error("run_sim_mixed: needs 16-bit tensors, 16-byte aligned, rows of 16 bytes");
+        return SAPA_ERR_UNSUPPORTED;
+    }
+    return launch_fused_tma_slots(2, hi, lo, nullptr, nullptr, out, nullptr, B, Cc, 0, H, W, rows, top, 0, H, dtype, true, st);
 }
 
 int run_sim(const void *hi, const void *lo, void *out, int B, int Cc, int H, int W, int K, int s, int dtype, cudaStream_t st) {

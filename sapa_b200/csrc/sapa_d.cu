@@ -276,11 +276,12 @@ __global__ void deform_bwd_kernel(const T *__restrict__ top, const T *__restrict
 // the logits and to the output, as in the reference.
 constexpr int WIN_THREADS = 128;
 
+// One entry per (image, group, pixel) that has at least one point outside its window: the points as a bit mask and
+// the attention weights of all points of the pixel.
 struct OutlierTap {
-    unsigned int k;      // (image * G + group) * P + point
-    unsigned int pix;    // high-res pixel
-    float a;             // attention weight of the point
-    unsigned int pad;
+    unsigned int idx;    // (image * G + group) * sH * sW + high-res pixel
+    unsigned int mask;   // bit p: point p left the window
+    float a[MAXP];       // attention weight of every point (only the masked ones are read)
 };
 
 // Position of a sampling point relative to the window of its pixel: r0 / c0 = window row / column of the upper-left
@@ -313,7 +314,7 @@ constexpr int WIN_FUSED = 0, WIN_LOGITS = 1, WIN_WEIGHTS = 2;
 template <typename T, int NP, int MODE>
 __global__ void __launch_bounds__(WIN_THREADS, 4)
 deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ offset,
-                     const T *__restrict__ dense /* [B*G, 25, sH, sW] */, T *__restrict__ attn /* [B, G, P, sH, sW] or null */,
+                     const float *__restrict__ dense /* [B*G, 25, sH, sW] */, T *__restrict__ attn /* [B, G, P, sH, sW] or null */,
                      T *__restrict__ window /* [B*G, 25, sH, sW] */, OutlierTap *__restrict__ taps,
                      unsigned int *__restrict__ tap_count, int B, int Cq, int H, int W, int P_runtime, int G,
                      int rows /* low-res rows held by key */, int ytop /* the row of key that is parent row 0 */) {
@@ -331,10 +332,10 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
         const int g = (int)(bg % G), b = (int)(bg / G);
         const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = (qh >> 1) + ytop, px = qw >> 1;   // rows in the frame of key
         float d[25], wd[25], oh[PMAX], ow[PMAX], logit[PMAX];
-        const T *dp = dense + (size_t)bg * 25 * hi + pix;
+        const float *dp = dense + (size_t)bg * 25 * hi + pix;
 #pragma unroll
         for (int k = 0; k < 25; ++k) {
-            d[k] = (MODE != WIN_WEIGHTS && live) ? to_acc(__ldcs(dp + (size_t)k * hi)) : 0.f;
+            d[k] = (MODE != WIN_WEIGHTS && live) ? __ldcs(dp + (size_t)k * hi) : 0.f;
             wd[k] = 0.f;
         }
         const T *offp = offset + (size_t)bg * P * 2 * hi + pix;
@@ -425,54 +426,68 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
                 if (live && p < P && attn != nullptr) attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(logit[p]);
             }
         }
-        // append this warp's outlier points to the list: one counter update per warp
+        // append the pixels of this warp that have outlier points to the list: one counter update per warp
         const unsigned int any = __ballot_sync(0xffffffffu, outliers != 0);
         if (any != 0) {
-            const int mine = __popc(outliers);
-            int incl = mine;
-#pragma unroll
-            for (int sft = 1; sft < 32; sft <<= 1) {
-                const int up = __shfl_up_sync(0xffffffffu, incl, sft);
-                if (lane >= sft) incl += up;
-            }
-            const int warp_total = __shfl_sync(0xffffffffu, incl, 31);
             unsigned int base = 0;
-            if (lane == 0) base = atomicAdd(tap_count, (unsigned int)warp_total);
+            if (lane == 0) base = atomicAdd(tap_count, (unsigned int)__popc(any));
             base = __shfl_sync(0xffffffffu, base, 0);
-            unsigned int at = base + (unsigned int)(incl - mine);
+            if (outliers != 0) {
+                OutlierTap *t = taps + base + __popc(any & ((1u << lane) - 1u));
+                t->idx = (unsigned int)i;
+                t->mask = outliers;
 #pragma unroll
-            for (int p = 0; p < PMAX; ++p)
-                if (outliers & (1u << p)) {
-                    OutlierTap t;
-                    t.k = (unsigned int)(bg * P + p); t.pix = (unsigned int)pix; t.a = logit[p]; t.pad = 0;
-                    taps[at++] = t;
-                }
+                for (int p = 0; p < PMAX; ++p) t->a[p] = logit[p];
+            }
         }
     }
 }
 
-// Adds a_p * bilinear(value_c) of the listed outlier points to the output: eight threads per point share its sampling
-// set-up and take every eighth channel of the group.
+// Adds a_p * bilinear(value_c) of the listed outlier points to the output.  Eight threads per listed pixel: each takes
+// every eighth channel of the group, four channels at a time in registers, walks the pixel's outlier points for them
+// and then updates the output elements once, read-modify-write without atomics (a listed pixel of a group belongs to
+// exactly one thread group, and the aggregation kernel that wrote the output has finished): the forward pass is
+// deterministic and a 16-bit output is rounded once more, not once per point.
 template <typename T>
 __global__ void deform_outlier_kernel(const OutlierTap *__restrict__ taps, const unsigned int *__restrict__ tap_count,
                                       const T *__restrict__ value, const T *__restrict__ offset, T *__restrict__ out,
                                       int C, int H, int W, int P, int G, int rows, int ytop) {
+    constexpr int CH = 4;
     const int sW = 2 * W, gc = C / G;
     const size_t hi = (size_t)(2 * H) * sW, lo = (size_t)rows * W;
     const unsigned int n = *tap_count;
     const int sub = threadIdx.x & 7;
     for (unsigned int e = (blockIdx.x * blockDim.x + threadIdx.x) >> 3; e < n; e += (gridDim.x * blockDim.x) >> 3) {
-        const OutlierTap t = taps[e];
-        const size_t pix = t.pix;
+        const OutlierTap *t = taps + e;
+        const unsigned int idx = __ldg(&t->idx), mask = __ldg(&t->mask);
+        const size_t bg = idx / hi, pix = idx % hi;
         const int px = (int)(pix % sW) >> 1, py = ((int)(pix / sW) >> 1) + ytop;
-        const float w = float(px) + to_acc(__ldg(offset + (size_t)t.k * 2 * hi + pix));
-        const float h = float(py) + to_acc(__ldg(offset + (size_t)t.k * 2 * hi + hi + pix));
-        Bilinear<float> bl;
-        bl.setup(h, w, rows, W);
-        const size_t bg = t.k / (unsigned int)P;
+        const T *offp = offset + bg * P * 2 * hi + pix;
         const T *vp = value + bg * gc * lo;
         T *op = out + bg * gc * hi + pix;
-        for (int c = sub; c < gc; c += 8) atomicAdd(op + (size_t)c * hi, from_acc<T>(t.a * bl.sample(vp + (size_t)c * lo)));
+        for (int c0 = sub; c0 < gc; c0 += 8 * CH) {
+            float acc[CH];
+#pragma unroll
+            for (int j = 0; j < CH; ++j) acc[j] = 0.f;
+            for (unsigned int m = mask; m != 0; m &= m - 1) {
+                const int p = __ffs(m) - 1;
+                const float w = float(px) + to_acc(__ldg(offp + (size_t)(2 * p) * hi));
+                const float h = float(py) + to_acc(__ldg(offp + (size_t)(2 * p + 1) * hi));
+                const float a = __ldg(&t->a[p]);
+                Bilinear<float> bl;
+                bl.setup(h, w, rows, W);
+#pragma unroll
+                for (int j = 0; j < CH; ++j) {
+                    const int c = c0 + 8 * j;
+                    if (c < gc) acc[j] += a * bl.sample(vp + (size_t)c * lo);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+                const int c = c0 + 8 * j;
+                if (c < gc) op[(size_t)c * hi] = from_acc<T>(to_acc(op[(size_t)c * hi]) + acc[j]);
+            }
+        }
     }
 }
 
@@ -980,16 +995,21 @@ int run_sim_slab(const void *hi, const void *lo, void *out, int B, int Cc, int H
                  cudaStream_t st);
 int run_agg_slab(const void *wt, const void *lo, void *out, int B, int Cc, int H, int W, int rows, int top, int K, int s, int dtype,
                  cudaStream_t st);
+int run_sim_mixed(const void *hi, const void *lo, float *out, int B, int Cc, int H, int W, int rows, int top, int dtype, cudaStream_t st);
+bool fused_tma_supported(int W, int dtype);
 }
 
 extern "C" {
 
 size_t sapa_deform_fused_forward_workspace(int B, int H, int W, int P, int s, int G, int dtype) {
-    if (B <= 0 || H <= 0 || W <= 0 || P <= 0 || G <= 0 || s != 2 || dtype != SAPA_F32) return 0;
+    if (B <= 0 || H <= 0 || W <= 0 || P <= 0 || G <= 0 || s != 2) return 0;
+    // 16-bit tensors: the mixed modes of the TMA kernels (16-bit operands, float32 windows) need rows of 16 bytes
+    if (dtype != SAPA_F32 && !((dtype == SAPA_F16 || dtype == SAPA_BF16) && W % 8 == 0 && fused_tma_supported(W, dtype))) return 0;
     const size_t hi = (size_t)s * H * s * W;
-    if ((size_t)B * G * P >= 0xffffffffull || hi >= 0xffffffffull) return 0;       // the outlier list indexes with 32 bits
-    // dense similarity + window weights, the outlier list (worst case: every point) and its counter
-    return (size_t)B * G * 50 * hi * dtype_size(dtype) + (size_t)B * G * P * hi * sizeof(OutlierTap) + 16;
+    if ((size_t)B * G * hi >= 0xffffffffull) return 0;       // the outlier list indexes (image, group, pixel) with 32 bits
+    // dense similarity + window weights (float32 whatever the tensors' type), the outlier list (worst case: every
+    // point) and its counter
+    return (size_t)B * G * 50 * hi * sizeof(float) + (size_t)B * G * hi * sizeof(OutlierTap) + 16;
 }
 
 int sapa_deform_fused_forward_slab(const void *query, const void *key, const void *value, const void *offset, void *out,
@@ -1004,41 +1024,57 @@ int sapa_deform_fused_forward_slab(const void *query, const void *key, const voi
     SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset);
     SAPA_CHECK_PTR(fn, out);
     const size_t need = sapa_deform_fused_forward_workspace(B, H, W, P, s, G, dtype);
-    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
-                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_fused_forward)", fn, MAXP);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && need != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32, or float16 / bfloat16 with rows of 16 bytes "
+                 "(use sapa_deform_fused_forward)", fn, MAXP);
     SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
                  "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
     const size_t hi = (size_t)s * H * s * W;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    float *dense = static_cast<float *>(workspace), *window = dense + (size_t)B * G * 25 * hi;
-    OutlierTap *taps = reinterpret_cast<OutlierTap *>(window + (size_t)B * G * 25 * hi);
-    unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * P * hi);
+    // the window weights have the tensors' type (the aggregation kernel rounds them to it anyway), the similarity is
+    // always float32; both regions are sized for float32
+    float *dense = static_cast<float *>(workspace);
+    void *window = dense + (size_t)B * G * 25 * hi;
+    OutlierTap *taps = reinterpret_cast<OutlierTap *>(dense + (size_t)B * G * 50 * hi);
+    unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * hi);
     if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
         set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
         return SAPA_ERR_LAUNCH;
     }
-    // 1. dense 25-slot similarity of every group: the B x G groups are images of Cq / G channels
-    if (int e = run_sim_slab(query, key, dense, B * G, Cq / G, H, W, rows, halo_top, 5, 2, dtype, st)) return e;
+    // 1. dense 25-slot similarity of every group: the B x G groups are images of Cq / G channels.  16-bit tensors: the
+    //    logits leave the tensor-core kernel as float32 (a 16-bit logit would cost the softmax two digits)
+    if (dtype == SAPA_F32) {
+        if (int e = run_sim_slab(query, key, dense, B * G, Cq / G, H, W, rows, halo_top, 5, 2, dtype, st)) return e;
+    } else {
+        if (int e = run_sim_mixed(query, key, dense, B * G, Cq / G, H, W, rows, halo_top, dtype, st)) return e;
+    }
     // 2. attention over the points, dense window weights, list of the points that leave the window
     {
         const long long total = (long long)B * G * hi;
-        const float *q = static_cast<const float *>(query), *k = static_cast<const float *>(key), *o = static_cast<const float *>(offset);
         const int grid = grid_1d(total, WIN_THREADS);
-        if (P == 9)          // the 3 x 3 points of the reference modules' default
-            deform_window_kernel<float, 9, WIN_FUSED><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, static_cast<float *>(attn), window, taps, tap_count,
-                                                                       B, Cq, H, W, P, G, rows, halo_top);
-        else
-            deform_window_kernel<float, 0, WIN_FUSED><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, static_cast<float *>(attn), window, taps, tap_count,
-                                                                       B, Cq, H, W, P, G, rows, halo_top);
-        if (int e = check_launch("deform_window_kernel")) return e;
+        const int e = SAPA_DISPATCH_FAST(dtype, [&] {
+            const scalar_t *q = static_cast<const scalar_t *>(query), *k = static_cast<const scalar_t *>(key);
+            const scalar_t *o = static_cast<const scalar_t *>(offset);
+            scalar_t *at = static_cast<scalar_t *>(attn), *wn = static_cast<scalar_t *>(window);
+            if (P == 9)          // the 3 x 3 points of the reference modules' default
+                deform_window_kernel<scalar_t, 9, WIN_FUSED><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, at, wn, taps, tap_count, B, Cq,
+                                                                                  H, W, P, G, rows, halo_top);
+            else
+                deform_window_kernel<scalar_t, 0, WIN_FUSED><<<grid, WIN_THREADS, 0, st>>>(q, k, o, dense, at, wn, taps, tap_count, B, Cq,
+                                                                                  H, W, P, G, rows, halo_top);
+            return check_launch("deform_window_kernel");
+        });
+        if (e) return e;
     }
     // 3. aggregation of every group's channels over the window
     if (int e = run_agg_slab(window, value, out, B * G, C / G, H, W, rows, halo_top, 5, 2, dtype, st)) return e;
     // 4. the listed points (the count is only known on the device: a fixed grid strides over the list)
-    deform_outlier_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, static_cast<const float *>(value),
-                                                          static_cast<const float *>(offset), static_cast<float *>(out),
-                                                          C, H, W, P, G, rows, halo_top);
-    return check_launch("deform_outlier_kernel");
+    return SAPA_DISPATCH_FAST(dtype, [&] {
+        deform_outlier_kernel<scalar_t><<<148 * 8, 256, 0, st>>>(taps, tap_count, static_cast<const scalar_t *>(value),
+                                                                 static_cast<const scalar_t *>(offset), static_cast<scalar_t *>(out),
+                                                                 C, H, W, P, G, rows, halo_top);
+        return check_launch("deform_outlier_kernel");
+    });
 }
 
 int sapa_deform_fused_forward_dense(const void *query, const void *key, const void *value, const void *offset, void *out,
@@ -1087,7 +1123,7 @@ int sapa_deform_av_forward_dense(const void *attn, const void *value, const void
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     float *window = static_cast<float *>(workspace) + (size_t)B * G * 25 * hi;
     OutlierTap *taps = reinterpret_cast<OutlierTap *>(window + (size_t)B * G * 25 * hi);
-    unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * P * hi);
+    unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * hi);
     if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
         set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
         return SAPA_ERR_LAUNCH;

@@ -64,6 +64,7 @@ struct Args {
     int y_begin, y_end;    // low-res output rows produced by this launch (a band of [0, H); the whole image except in row-slab calls)
     int tiles_x, tiles_y;  // tiles_y covers the band only
     int sched_slot;        // index into g_next_tile / g_ctas_done
+    int slots_f32;         // 16-bit kernel, MODE_SIM: the logits are written as float32
 };
 
 // byte offset of element `col` of a 64-byte row under the 64-byte swizzle: the 16-byte chunk index is XORed with
@@ -744,7 +745,21 @@ sapa_tma_fused_16_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
                         pb[p][dy][1] = pack_pair(T(), s[p][dy][2], s[p][dy][3]);
                     }
             }
-            if (it == nk - 1 && (MODE == MODE_FWD || MODE == MODE_SIM)) {
+            if (it == nk - 1 && MODE == MODE_SIM && a.slots_f32 != 0) {
+                if (row_ok) {         // raw logits as float32 pairs (the dense similarity of the 16-bit SAPA-D path)
+                    float2 *af = reinterpret_cast<float2 *>(static_cast<float *>(a.attn) + (size_t)n * 25 * hi_plane +
+                                                            (size_t)(2 * y + r) * sW + 2 * x0 + 2 * t);
+#pragma unroll
+                    for (int p = 0; p < 2; ++p)
+                        if (p == 0 ? col_ok0 : col_ok1) {
+#pragma unroll
+                            for (int dy = 0; dy < 5; ++dy) {
+                                if (ok_lo[p]) af[(size_t)(dy * 5 + dx_lo[p]) * plane_w + 4 * p] = make_float2(s[p][dy][0], s[p][dy][1]);
+                                if (ok_hi[p]) af[(size_t)(dy * 5 + dx_lo[p] + 8) * plane_w + 4 * p] = make_float2(s[p][dy][2], s[p][dy][3]);
+                            }
+                        }
+                }
+            } else if (it == nk - 1 && (MODE == MODE_FWD || MODE == MODE_SIM)) {
                 if (a.attn != nullptr && row_ok) {
                     // the two pixels of a pair are neighbours in memory: one 32-bit store per (window slot, pair)
                     unsigned *an = reinterpret_cast<unsigned *>(static_cast<T *>(a.attn) + (size_t)n * 25 * hi_plane +
@@ -857,6 +872,10 @@ bool fused_tma_supported(int W, int dtype) {
     return false;
 }
 
+int launch_fused_tma_slots(int mode, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d,
+                           int C, int H, int W, int rows, int ytop0, int y_begin, int y_end, int dtype, bool slots_f32,
+                           cudaStream_t st);
+
 // Returns SAPA_ERR_UNSUPPORTED when a tensor map cannot be built (the caller then uses another kernel).
 // mode 0 (forward): out = atn(softmax(sim(q, k)), v), attn = optional output.
 // mode 1 (backward stage 1): q = grad_out [B,d,2H,2W], k = value [B,d,H,W] (d = value channels), v = key [B,C,H,W]
@@ -864,7 +883,19 @@ bool fused_tma_supported(int W, int dtype) {
 // mode 2 (sim): attn (output) = sim(q, k); v, out unused, C ignored.   mode 3 (agg): out = atn(attn (input), v); q, k unused, d ignored.
 int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d, int C,
                      int H, int W, int rows, int ytop0, int y_begin, int y_end, int dtype, cudaStream_t st) {
+    return launch_fused_tma_slots(mode, q, k, v, out, attn, ws, B, d, C, H, W, rows, ytop0, y_begin, y_end, dtype, false, st);
+}
+
+// slots_f32 (16-bit tensors, mode 2 only): `attn` is a float32 tensor - the logits are written at full precision while
+// query and key stay 16-bit.
+int launch_fused_tma_slots(int mode, const void *q, const void *k, const void *v, void *out, void *attn, void *ws, int B, int d,
+                           int C, int H, int W, int rows, int ytop0, int y_begin, int y_end, int dtype, bool slots_f32,
+                           cudaStream_t st) {
     using namespace tma;
+    if (slots_f32 && (dtype == SAPA_F32 || mode != MODE_SIM)) {
+        set_error("sapa_tma_fused: float32 slots are for the 16-bit logit mode");
+        return SAPA_ERR_UNSUPPORTED;
+    }
     if (mode == MODE_SIM) C = 0;
     if (mode == MODE_AGG) d = 0;
     const bool use_qk = mode != MODE_AGG, use_v = mode != MODE_SIM;
@@ -893,6 +924,7 @@ int launch_fused_tma(int mode, const void *q, const void *k, const void *v, void
     Args a{};
     a.out = out; a.attn = attn; a.ws = ws;
     a.B = B; a.d = d; a.C = C; a.H = H; a.W = W; a.rows = rows; a.ytop0 = ytop0;
+    a.slots_f32 = slots_f32 ? 1 : 0;
     static_assert(h16::COLS == COLS, "both kernels use the same tile");
     a.y_begin = y_begin; a.y_end = y_end;
     a.tiles_x = ceil_div(W, COLS);

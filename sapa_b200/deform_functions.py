@@ -187,11 +187,14 @@ class DeformSapaFusedFunction(Function):
             out = torch.empty((n, c, hq, wq), dtype=value.dtype, device=value.device)
             attn = torch.empty((n, groups, num_point, hq, wq), dtype=value.dtype, device=value.device) if need_grad else None
             code = _lib.dtype_code(value)
-            # s = 2: the dense-window path on the SAPA-B kernels.  It computes in float32; 16-bit tensors are widened for
-            # it and the results narrowed again (seven small casts against a 4x faster kernel chain).
+            # s = 2: the dense-window path on the SAPA-B kernels.  float32 runs it as is; 16-bit tensors with rows of 16
+            # bytes too (16-bit operands, float32 windows between the kernels); other 16-bit shapes are widened for it
+            # and the results narrowed again (seven small casts against a 4x faster kernel chain).
             f32 = _lib.SAPA_F32
-            nbytes = int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, f32))
-            if nbytes and value.dtype == torch.float32:
+            aligned = all(t.data_ptr() % 16 == 0 for t in (query, key, value, offset))
+            native = int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, code)) if aligned else 0
+            nbytes = native or int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, f32))
+            if native:
                 workspace = torch.empty(nbytes, dtype=torch.uint8, device=value.device)
                 _lib.call("sapa_deform_fused_forward_dense", value.device, query, key, value, offset, out, attn, workspace,
                           workspace.numel(), n, cq, c, h, w, num_point, scale_factor, groups, code)
