@@ -268,12 +268,12 @@ __global__ void deform_bwd_kernel(const T *__restrict__ top, const T *__restrict
 //   aggregation: out_c = sum_p a_p * bilinear(value_c) = sum_cells Wd[cell] * value_c[cell],  Wd[cell] = sum of a_p * w_corner
 //                over the corners that land on the cell (one call of the SAPA-B aggregation kernel).
 // deform_window_kernel sits between the two: one thread per (image, group, pixel) turns D and the offsets into the
-// attention over the P points and the dense window weights Wd, all in registers (the bilinear weights of a point are
-// written as a 5-vector per axis with two non-zero entries, so that no register array is indexed dynamically).  A point
-// with a corner outside the window (|offset| >= 2) is an "outlier": its logit is gathered directly here, it adds
-// nothing to Wd, and it is appended to a list from which deform_outlier_kernel adds its contribution to the output
-// afterwards (atomics; rare for learned offsets, but always correct).  Points outside the image contribute exactly 0 to
-// the logits and to the output, as in the reference.
+// attention over the P points and the dense window weights Wd (the thread's two windows sit in its column of a shared
+// array, where the four cells of a point can be addressed at run time).  A point with a corner outside the window
+// (|offset| >= 2) is an "outlier": its logit is gathered directly here, it adds nothing to Wd, and its pixel is
+// appended to a list from which deform_outlier_kernel adds the contribution to the output afterwards (rare for learned
+// offsets, but always correct).  Points outside the image contribute exactly 0 to the logits and to the output, as in
+// the reference.
 constexpr int WIN_THREADS = 128;
 
 // One entry per (image, group, pixel) that has at least one point outside its window: the points as a bit mask and
@@ -297,47 +297,49 @@ struct WindowTap {
         r0 = (int)fh - (py - 2); c0 = (int)fw - (px - 2);
         dense = inside && r0 >= 0 && r0 <= 3 && c0 >= 0 && c0 <= 3;
     }
-    __device__ __forceinline__ void axis(float (&v)[5], int i0, float l) const {
-#pragma unroll
-        for (int r = 0; r < 5; ++r) v[r] = (r == i0) ? 1.f - l : (r == i0 + 1) ? l : 0.f;
-    }
 };
 
-// NP = number of points known at compile time (0: read P at run time, up to MAXP).  The P points are walked ONCE with a
-// running maximum (the window weights collected so far are rescaled when the maximum grows), so the bilinear set-up of
-// a point is computed once.
+// NP = number of points known at compile time (0: read P at run time, up to MAXP).
 // MODE: WIN_FUSED = logits -> softmax -> window weights (the fused op); WIN_LOGITS = raw logits only, written where the
 // fused op writes the attention (deform_qk); WIN_WEIGHTS = window weights from a given attention map (deform_av).
 constexpr int WIN_FUSED = 0, WIN_LOGITS = 1, WIN_WEIGHTS = 2;
 
-// (four blocks per SM: 128 registers; more blocks spill, fewer leave the SM short of warps - both measured slower)
+// The two 25-slot windows of a thread (similarity in, window weights out) live in shared memory, column = thread, so
+// every access is conflict-free: a point touches four cells of each window, and shared memory can be indexed with the
+// cell computed at run time (a register array cannot: that form multiplies every point with all 25 cells and took
+// 82 us where this takes 56 us at B=8, 4 groups, 128 x 128 pixels).  Two passes over the points: logits and their
+// maximum, then exp and the window weights.  Six blocks per SM (80 registers; 4 and 8 measured slower).
 template <typename T, int NP, int MODE>
-__global__ void __launch_bounds__(WIN_THREADS, 4)
+__global__ void __launch_bounds__(WIN_THREADS, 6)
 deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ offset,
-                     const float *__restrict__ dense /* [B*G, 25, sH, sW] */, T *__restrict__ attn /* [B, G, P, sH, sW] or null */,
-                     T *__restrict__ window /* [B*G, 25, sH, sW] */, OutlierTap *__restrict__ taps,
-                     unsigned int *__restrict__ tap_count, int B, int Cq, int H, int W, int P_runtime, int G,
-                     int rows /* low-res rows held by key */, int ytop /* the row of key that is parent row 0 */) {
+                          const float *__restrict__ dense, T *__restrict__ attn, T *__restrict__ window,
+                          OutlierTap *__restrict__ taps, unsigned int *__restrict__ tap_count, int B, int Cq, int H, int W,
+                          int P_runtime, int G, int rows, int ytop) {
     constexpr int PMAX = NP > 0 ? NP : MAXP;
+    __shared__ float sd[MODE != WIN_WEIGHTS ? 25 : 1][WIN_THREADS];     // dense similarity of the thread's pixel
+    __shared__ float sw[MODE != WIN_LOGITS ? 25 : 1][WIN_THREADS];      // window weights being collected
     const int P = NP > 0 ? NP : P_runtime;
     const int sH = 2 * H, sW = 2 * W, gq = Cq / G;
     const size_t hi = (size_t)sH * sW, lo = (size_t)rows * W;
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, tid = threadIdx.x;
     const long long total = (long long)B * G * hi;
     for (long long i0 = (long long)blockIdx.x * WIN_THREADS; i0 < total; i0 += (long long)gridDim.x * WIN_THREADS) {
-        const long long i = i0 + threadIdx.x;
+        const long long i = i0 + tid;
         const bool live = i < total;
         const size_t pix = live ? (size_t)(i % hi) : 0;
         const long long bg = live ? i / (long long)hi : 0;
         const int g = (int)(bg % G), b = (int)(bg / G);
-        const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = (qh >> 1) + ytop, px = qw >> 1;   // rows in the frame of key
-        float d[25], wd[25], oh[PMAX], ow[PMAX], logit[PMAX];
-        const float *dp = dense + (size_t)bg * 25 * hi + pix;
+        const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = (qh >> 1) + ytop, px = qw >> 1;
+        if (MODE != WIN_WEIGHTS) {
+            const float *dp = dense + (size_t)bg * 25 * hi + pix;
 #pragma unroll
-        for (int k = 0; k < 25; ++k) {
-            d[k] = (MODE != WIN_WEIGHTS && live) ? __ldcs(dp + (size_t)k * hi) : 0.f;
-            wd[k] = 0.f;
+            for (int k = 0; k < 25; ++k) sd[k][tid] = live ? __ldcs(dp + (size_t)k * hi) : 0.f;
         }
+        if (MODE != WIN_LOGITS) {
+#pragma unroll
+            for (int k = 0; k < 25; ++k) sw[k][tid] = 0.f;
+        }
+        float oh[PMAX], ow[PMAX], logit[PMAX];
         const T *offp = offset + (size_t)bg * P * 2 * hi + pix;
 #pragma unroll
         for (int p = 0; p < PMAX; ++p) {
@@ -345,84 +347,67 @@ deform_window_kernel(const T *__restrict__ query, const T *__restrict__ key, con
             ow[p] = on ? float(px) + to_acc(__ldg(offp + (size_t)(2 * p) * hi)) : 0.f;
             oh[p] = on ? float(py) + to_acc(__ldg(offp + (size_t)(2 * p + 1) * hi)) : 0.f;
         }
-        float m = -INFINITY, z = 0.f;
         unsigned int outliers = 0;
+        float m = -INFINITY;
+        // ---- pass 1: logits (or the given attention) and which points leave the window
 #pragma unroll
         for (int p = 0; p < PMAX; ++p) {
             logit[p] = 0.f;
             if (live && p < P) {
                 WindowTap t;
                 t.setup(oh[p], ow[p], rows, W, py, px);
-                float vy[5], vx[5];
-                t.axis(vy, t.r0, t.lh);
-                t.axis(vx, t.c0, t.lw);
+                if (!t.dense && t.inside) outliers |= 1u << p;
                 float acc = 0.f;
-                if (MODE == WIN_WEIGHTS) {     // the attention is given: it takes the place of exp(logit - max) / sum
-                    const float a = to_acc(__ldg(attn + ((size_t)bg * P + p) * hi + pix));
-                    logit[p] = a;
-                    if (t.dense) {
-#pragma unroll
-                        for (int r = 0; r < 5; ++r) {
-                            const float ay = a * vy[r];
-#pragma unroll
-                            for (int c = 0; c < 5; ++c) wd[r * 5 + c] += ay * vx[c];
-                        }
-                    } else if (t.inside) {
-                        outliers |= 1u << p;
-                    }
-                    continue;
-                }
-                if (t.dense) {
-#pragma unroll
-                    for (int r = 0; r < 5; ++r) {
-                        float row = 0.f;
-#pragma unroll
-                        for (int c = 0; c < 5; ++c) row += vx[c] * d[r * 5 + c];
-                        acc += vy[r] * row;
-                    }
+                if (MODE == WIN_WEIGHTS) {
+                    acc = to_acc(__ldg(attn + ((size_t)bg * P + p) * hi + pix));
+                } else if (t.dense) {
+                    const int c = t.r0 * 5 + t.c0;
+                    const float top = (1.f - t.lw) * sd[c][tid] + t.lw * sd[c + 1][tid];
+                    const float bot = (1.f - t.lw) * sd[c + 5][tid] + t.lw * sd[c + 6][tid];
+                    acc = (1.f - t.lh) * top + t.lh * bot;
                 } else if (t.inside) {        // outlier: gather the key directly
-                    outliers |= 1u << p;
                     Bilinear<float> bl;
                     bl.setup(oh[p], ow[p], rows, W);
                     const T *qp = query + ((size_t)b * Cq + (size_t)g * gq) * hi + pix;
                     const T *kp = key + ((size_t)b * Cq + (size_t)g * gq) * lo;
-                    for (int c = 0; c < gq; ++c) acc += bl.sample(kp + (size_t)c * lo) * to_acc(qp[(size_t)c * hi]);
+                    for (int ch = 0; ch < gq; ++ch) acc += bl.sample(kp + (size_t)ch * lo) * to_acc(qp[(size_t)ch * hi]);
                 }
                 logit[p] = acc;
-                if (MODE == WIN_LOGITS) {
-                    attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(acc);
-                    continue;
-                }
-                if (acc > m) {                // new running maximum: bring what was collected so far to the new scale
-                    const float f = __expf(m - acc);      // 0 on the first point (m = -inf)
-                    z *= f;
-#pragma unroll
-                    for (int k = 0; k < 25; ++k) wd[k] *= f;
-                    m = acc;
-                }
-                const float e = __expf(acc - m);
-                z += e;
-                if (t.dense) {
-#pragma unroll
-                    for (int r = 0; r < 5; ++r) {
-                        const float ey = e * vy[r];
-#pragma unroll
-                        for (int c = 0; c < 5; ++c) wd[r * 5 + c] += ey * vx[c];
-                    }
-                }
+                m = fmaxf(m, acc);
+                if (MODE == WIN_LOGITS) attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(acc);
             }
         }
         if (MODE == WIN_LOGITS) continue;                   // no lane-crossing operation below was entered by any lane yet
+        // ---- pass 2: exp and the window weights (the bilinear set-up is recomputed: cheaper than keeping it)
+        float z = 0.f;
+#pragma unroll
+        for (int p = 0; p < PMAX; ++p) {
+            if (live && p < P) {
+                const float e = MODE == WIN_WEIGHTS ? logit[p] : __expf(logit[p] - m);
+                logit[p] = e;
+                z += e;
+                WindowTap t;
+                t.setup(oh[p], ow[p], rows, W, py, px);
+                if (t.dense) {
+                    const int c = t.r0 * 5 + t.c0;
+                    const float et = e * (1.f - t.lh), eb = e * t.lh;
+                    sw[c][tid] += et * (1.f - t.lw);
+                    sw[c + 1][tid] += et * t.lw;
+                    sw[c + 5][tid] += eb * (1.f - t.lw);
+                    sw[c + 6][tid] += eb * t.lw;
+                }
+            }
+        }
         const float inv = MODE == WIN_WEIGHTS ? 1.f : 1.f / z;
         if (live) {
             T *wp = window + (size_t)bg * 25 * hi + pix;
 #pragma unroll
-            for (int k = 0; k < 25; ++k) wp[(size_t)k * hi] = from_acc<T>(wd[k] * inv);
+            for (int k = 0; k < 25; ++k) wp[(size_t)k * hi] = from_acc<T>(sw[k][tid] * inv);
         }
         if (MODE == WIN_FUSED) {
 #pragma unroll
             for (int p = 0; p < PMAX; ++p) {
-                logit[p] = __expf(logit[p] - m) * inv;        // the attention weight of the point
+                logit[p] *= inv;                             // the attention weight of the point
                 if (live && p < P && attn != nullptr) attn[((size_t)bg * P + p) * hi + pix] = from_acc<T>(logit[p]);
             }
         }
@@ -498,7 +483,7 @@ __global__ void deform_outlier_kernel(const OutlierTap *__restrict__ taps, const
 //   dD[cell]    = sum_p dS_p * B_p[cell],  Wd[cell] = sum_p A_p * B_p[cell]
 //   dQ = agg(dD, key),  dKey = gath(Q, dD),  dV = gath(dOut, Wd)  per group                         (SAPA-B kernels, no atomics)
 //   d offset_p  = A_p * (dB_p . dWd) + dS_p * (dB_p . D),   dB_p/dh = dvy (x) vx,  dB_p/dw = vy (x) dvx
-// deform_window_bwd_kernel does the per-pixel part (one thread per (image, group, pixel), everything in registers).
+// deform_window_bwd_kernel does the per-pixel part (one thread per (image, group, pixel); the windows in shared memory).
 // Points that leave the window are listed with their A_p and dS_p; deform_outlier_bwd_kernel adds their gradients
 // afterwards (atomics on dQ, dKey, dV; it owns their offset gradients).
 struct OutlierGrad {
@@ -508,10 +493,6 @@ struct OutlierGrad {
     float ds;            // gradient of its logit
 };
 
-__device__ __forceinline__ void axis_derivative(float (&v)[5], int i0) {
-#pragma unroll
-    for (int r = 0; r < 5; ++r) v[r] = (r == i0 + 1) ? 1.f : (r == i0) ? -1.f : 0.f;
-}
 
 // MODE: BWD_FUSED = the whole chain; BWD_AV = backward of deform_av alone (`attn` given, dA written to `ddense`'s place
 // is not needed: it goes to `grad_attn`, no logit gradients); BWD_QK = backward of deform_qk alone (`attn` carries the
@@ -519,7 +500,7 @@ __device__ __forceinline__ void axis_derivative(float (&v)[5], int i0) {
 constexpr int BWD_FUSED = 0, BWD_AV = 1, BWD_QK = 2;
 
 template <typename T, int NP, int MODE>
-__global__ void __launch_bounds__(WIN_THREADS, 3)
+__global__ void __launch_bounds__(WIN_THREADS, 4)
 deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ value, const T *__restrict__ offset,
                          const T *__restrict__ attn, const T *__restrict__ dense /* D [B*G, 25, hi] */,
                          const T *__restrict__ dwin /* dWd [B*G, 25, hi] */, T *__restrict__ ddense /* dD, out */,
@@ -530,7 +511,11 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
     const int P = NP > 0 ? NP : P_runtime;
     const int sH = 2 * H, sW = 2 * W, gc = C / G;
     const size_t hi = (size_t)sH * sW, lo = (size_t)H * W;
-    const int lane = threadIdx.x & 31;
+    // The two 25-slot windows of a thread (D and dWd going in, dD and Wd coming out) live in shared memory, column =
+    // thread (conflict-free): a point touches four cells of each, and shared memory can be indexed with the cell found
+    // at run time, where registers force a product with all 25 cells.
+    __shared__ float sd[25][WIN_THREADS], sw[25][WIN_THREADS];
+    const int lane = threadIdx.x & 31, tid = threadIdx.x;
     const long long total = (long long)B * G * hi;
     for (long long i0 = (long long)blockIdx.x * WIN_THREADS; i0 < total; i0 += (long long)gridDim.x * WIN_THREADS) {
         const long long i = i0 + threadIdx.x;
@@ -538,12 +523,12 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
         const size_t pix = live ? (size_t)(i % hi) : 0;
         const long long bg = live ? i / (long long)hi : 0;
         const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = qh >> 1, px = qw >> 1;
-        float d[25], w[25], oh[PMAX], ow[PMAX], at[PMAX];
+        float oh[PMAX], ow[PMAX], at[PMAX];
         const T *dp = dense + (size_t)bg * 25 * hi + pix, *wp = dwin + (size_t)bg * 25 * hi + pix;
 #pragma unroll
         for (int k = 0; k < 25; ++k) {
-            d[k] = (MODE != BWD_AV && live) ? to_acc(__ldcs(dp + (size_t)k * hi)) : 0.f;
-            w[k] = (MODE != BWD_QK && live) ? to_acc(__ldcs(wp + (size_t)k * hi)) : 0.f;
+            sd[k][tid] = (MODE != BWD_AV && live) ? to_acc(__ldcs(dp + (size_t)k * hi)) : 0.f;
+            sw[k][tid] = (MODE != BWD_QK && live) ? to_acc(__ldcs(wp + (size_t)k * hi)) : 0.f;
         }
         const T *offp = offset + (size_t)bg * P * 2 * hi + pix, *ap = attn + (size_t)bg * P * hi + pix;
 #pragma unroll
@@ -564,31 +549,21 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
                 WindowTap t;
                 t.setup(oh[p], ow[p], H, W, py, px);
                 if (t.dense) {
-                    float vy[5], vx[5], dvy[5], dvx[5];
-                    t.axis(vy, t.r0, t.lh);
-                    t.axis(vx, t.c0, t.lw);
-                    axis_derivative(dvy, t.r0);
-                    axis_derivative(dvx, t.c0);
-                    float acc_a = 0.f, acc_h1 = 0.f, acc_h2 = 0.f;
-                    float zw[5] = {0.f, 0.f, 0.f, 0.f, 0.f}, zd[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int r = 0; r < 5; ++r) {
-                        float uw = 0.f, ud = 0.f;
-#pragma unroll
-                        for (int c = 0; c < 5; ++c) {
-                            uw += vx[c] * w[r * 5 + c];
-                            ud += vx[c] * d[r * 5 + c];
-                            zw[c] += vy[r] * w[r * 5 + c];
-                            zd[c] += vy[r] * d[r * 5 + c];
-                        }
-                        acc_a += vy[r] * uw;
-                        acc_h1 += dvy[r] * uw;
-                        acc_h2 += dvy[r] * ud;
+                    // bilinear forms over the four cells: value (1-lh, lh) x (1-lw, lw); d/dh (-1, 1) x (1-lw, lw); d/dw (1-lh, lh) x (-1, 1)
+                    const int c = t.r0 * 5 + t.c0;
+                    const float hw = 1.f - t.lw, hh = 1.f - t.lh;
+                    if (MODE != BWD_QK) {
+                        const float w00 = sw[c][tid], w01 = sw[c + 1][tid], w10 = sw[c + 5][tid], w11 = sw[c + 6][tid];
+                        const float top = hw * w00 + t.lw * w01, bot = hw * w10 + t.lw * w11;
+                        da[p] = hh * top + t.lh * bot;
+                        gh1[p] = bot - top;
+                        gw1[p] = (hh * w01 + t.lh * w11) - (hh * w00 + t.lh * w10);
                     }
-                    float acc_w1 = 0.f, acc_w2 = 0.f;
-#pragma unroll
-                    for (int c = 0; c < 5; ++c) { acc_w1 += dvx[c] * zw[c]; acc_w2 += dvx[c] * zd[c]; }
-                    da[p] = acc_a; gh1[p] = acc_h1; gh2[p] = acc_h2; gw1[p] = acc_w1; gw2[p] = acc_w2;
+                    if (MODE != BWD_AV) {
+                        const float d00 = sd[c][tid], d01 = sd[c + 1][tid], d10 = sd[c + 5][tid], d11 = sd[c + 6][tid];
+                        gh2[p] = (hw * d10 + t.lw * d11) - (hw * d00 + t.lw * d01);
+                        gw2[p] = (hh * d01 + t.lh * d11) - (hh * d00 + t.lh * d10);
+                    }
                 } else if (t.inside) {        // outlier: dA by direct gather
                     outliers |= 1u << p;
                     if (MODE == BWD_QK) continue;
@@ -602,9 +577,9 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
                 dot += at[p] * da[p];
             }
         }
-        // ---- pass 2: logit gradients, dD, Wd (d[] and w[] become the accumulators), offset gradients
+        // ---- pass 2: logit gradients, dD, Wd (the two shared windows become the accumulators), offset gradients
 #pragma unroll
-        for (int k = 0; k < 25; ++k) { d[k] = 0.f; w[k] = 0.f; }
+        for (int k = 0; k < 25; ++k) { sd[k][tid] = 0.f; sw[k][tid] = 0.f; }
         T *gop = grad_offset + (size_t)bg * P * 2 * hi + pix;
 #pragma unroll
         for (int p = 0; p < PMAX; ++p) {
@@ -617,14 +592,13 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
                 WindowTap t;
                 t.setup(oh[p], ow[p], H, W, py, px);
                 if (t.dense) {
-                    float vy[5], vx[5];
-                    t.axis(vy, t.r0, t.lh);
-                    t.axis(vx, t.c0, t.lw);
-#pragma unroll
-                    for (int r = 0; r < 5; ++r) {
-                        const float sy = ds * vy[r], ay = a * vy[r];
-#pragma unroll
-                        for (int c = 0; c < 5; ++c) { d[r * 5 + c] += sy * vx[c]; w[r * 5 + c] += ay * vx[c]; }
+                    const int c = t.r0 * 5 + t.c0;
+                    const float b00 = (1.f - t.lh) * (1.f - t.lw), b01 = (1.f - t.lh) * t.lw, b10 = t.lh * (1.f - t.lw), b11 = t.lh * t.lw;
+                    if (MODE != BWD_AV) {
+                        sd[c][tid] += ds * b00; sd[c + 1][tid] += ds * b01; sd[c + 5][tid] += ds * b10; sd[c + 6][tid] += ds * b11;
+                    }
+                    if (MODE != BWD_QK) {
+                        sw[c][tid] += a * b00; sw[c + 1][tid] += a * b01; sw[c + 5][tid] += a * b10; sw[c + 6][tid] += a * b11;
                     }
                 }
                 if (!(outliers & (1u << p))) {      // the list kernel writes the offset gradients of the outliers
@@ -637,8 +611,8 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
             T *ddp = ddense + (size_t)bg * 25 * hi + pix, *wdp = window + (size_t)bg * 25 * hi + pix;
 #pragma unroll
             for (int k = 0; k < 25; ++k) {
-                if (MODE != BWD_AV) ddp[(size_t)k * hi] = from_acc<T>(d[k]);
-                if (MODE != BWD_QK) wdp[(size_t)k * hi] = from_acc<T>(w[k]);
+                if (MODE != BWD_AV) ddp[(size_t)k * hi] = from_acc<T>(sd[k][tid]);
+                if (MODE != BWD_QK) wdp[(size_t)k * hi] = from_acc<T>(sw[k][tid]);
             }
         }
         const unsigned int any = __ballot_sync(0xffffffffu, outliers != 0);
