@@ -255,10 +255,15 @@ int sapa_deform_qk_backward_dense(const void *grad_out, const void *query, const
  * counterpart of sapa_deform_fused_forward_dense): two similarity launches (Q x Key and dOut x Value per group), one
  * per-pixel kernel (softmax backward over the points, logit-gradient and weight windows, offset gradients), one
  * aggregation launch (dQ) and two gather launches (dKey, dV) - deterministic for every point inside the 5 x 5 window;
- * the points outside it are listed and added by a last kernel with atomics.  All four gradients are float32 tensors of
- * the shapes of their inputs and are overwritten.  `workspace`: sapa_deform_fused_backward_workspace() bytes, 16-byte
+ * the points outside it are listed and added by a last kernel with atomics.  All four gradients have the type and the
+ * shapes of their inputs and are overwritten.  float16 / bfloat16 (W a multiple of 8): 16-bit operands in the tensor-core
+ * kernels, float32 similarities in the workspace, 16-bit gradients (the listed points then add with 16-bit atomics).  `workspace`: sapa_deform_fused_backward_workspace() bytes, 16-byte
  * aligned.  Other configurations: SAPA_ERR_UNSUPPORTED (the workspace query returns 0).  No counterpart in the reference. */
 size_t sapa_deform_fused_backward_workspace(int B, int H, int W, int P, int s, int G, int dtype);
+/* float16 / bfloat16 only (0 otherwise): bytes of the float32 side buffers in which the key / value gradients of the
+ * listed points are collected.  sapa_deform_fused_backward_dense then needs a workspace of
+ * round_up(sapa_deform_fused_backward_workspace(), 16) + sapa_deform_fused_backward_scatter_bytes() bytes. */
+size_t sapa_deform_fused_backward_scatter_bytes(int B, int Cq, int C, int H, int W, int dtype);
 int sapa_deform_fused_backward_dense(const void *grad_out, const void *query, const void *key, const void *value,
                                      const void *offset, const void *attn, void *grad_query, void *grad_key, void *grad_value,
                                      void *grad_offset, void *workspace, size_t workspace_bytes, int B, int Cq, int C, int H,

@@ -51,7 +51,8 @@ _SIGNATURES = {
     "sapa_deform_fused_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
 }
 EXPORTS = sorted(list(_SIGNATURES) + ["sapa_last_error", "sapa_last_kernels", "sapa_abi_version", "sapa_fused_backward_workspace",
-                                           "sapa_deform_fused_forward_workspace", "sapa_deform_fused_backward_workspace", "sapa_project_workspace",
+                                           "sapa_deform_fused_forward_workspace", "sapa_deform_fused_backward_workspace",
+                                           "sapa_deform_fused_backward_scatter_bytes", "sapa_project_workspace",
                                            "sapa_fused_backward_static_capacity", "sapa_wait_timeout_flags"])
 
 
@@ -82,6 +83,8 @@ def lib() -> ctypes.CDLL:
     handle.sapa_abi_version.restype = ctypes.c_int
     handle.sapa_fused_backward_workspace.argtypes = [_i, _i, _i, _i, _i, _i]
     handle.sapa_fused_backward_workspace.restype = ctypes.c_size_t
+    handle.sapa_deform_fused_backward_scatter_bytes.argtypes = [_i, _i, _i, _i, _i, _i]
+    handle.sapa_deform_fused_backward_scatter_bytes.restype = ctypes.c_size_t
     handle.sapa_deform_fused_forward_workspace.argtypes = [_i, _i, _i, _i, _i, _i, _i]
     handle.sapa_deform_fused_forward_workspace.restype = ctypes.c_size_t
     handle.sapa_deform_fused_backward_workspace.argtypes = [_i, _i, _i, _i, _i, _i, _i]

@@ -502,8 +502,8 @@ constexpr int BWD_FUSED = 0, BWD_AV = 1, BWD_QK = 2;
 template <typename T, int NP, int MODE>
 __global__ void __launch_bounds__(WIN_THREADS, 4)
 deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ value, const T *__restrict__ offset,
-                         const T *__restrict__ attn, const T *__restrict__ dense /* D [B*G, 25, hi] */,
-                         const T *__restrict__ dwin /* dWd [B*G, 25, hi] */, T *__restrict__ ddense /* dD, out */,
+                         const T *__restrict__ attn, const float *__restrict__ dense /* D [B*G, 25, hi] */,
+                         const float *__restrict__ dwin /* dWd [B*G, 25, hi] */, T *__restrict__ ddense /* dD, out */,
                          T *__restrict__ window /* Wd, out */, T *__restrict__ grad_offset, T *__restrict__ grad_attn /* BWD_AV only */,
                          OutlierGrad *__restrict__ taps,
                          unsigned int *__restrict__ tap_count, int B, int C, int H, int W, int P_runtime, int G) {
@@ -524,11 +524,11 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
         const long long bg = live ? i / (long long)hi : 0;
         const int qw = (int)(pix % sW), qh = (int)(pix / sW), py = qh >> 1, px = qw >> 1;
         float oh[PMAX], ow[PMAX], at[PMAX];
-        const T *dp = dense + (size_t)bg * 25 * hi + pix, *wp = dwin + (size_t)bg * 25 * hi + pix;
+        const float *dp = dense + (size_t)bg * 25 * hi + pix, *wp = dwin + (size_t)bg * 25 * hi + pix;
 #pragma unroll
         for (int k = 0; k < 25; ++k) {
-            sd[k][tid] = (MODE != BWD_AV && live) ? to_acc(__ldcs(dp + (size_t)k * hi)) : 0.f;
-            sw[k][tid] = (MODE != BWD_QK && live) ? to_acc(__ldcs(wp + (size_t)k * hi)) : 0.f;
+            sd[k][tid] = (MODE != BWD_AV && live) ? __ldcs(dp + (size_t)k * hi) : 0.f;
+            sw[k][tid] = (MODE != BWD_QK && live) ? __ldcs(wp + (size_t)k * hi) : 0.f;
         }
         const T *offp = offset + (size_t)bg * P * 2 * hi + pix, *ap = attn + (size_t)bg * P * hi + pix;
 #pragma unroll
@@ -642,11 +642,14 @@ deform_window_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ v
 
 // Gradients of the listed outlier points: eight threads per point share its sampling set-up and take every eighth
 // channel; dQ, dKey and dV are added to what the SAPA-B kernels wrote (atomics), the point's offset gradient is written.
-template <typename T>
+// TA = type of the scatter targets grad_key / grad_value: T itself in float32; float for 16-bit tensors, where they are
+// zeroed side buffers that deform_add_scatter_kernel folds into the 16-bit gradients afterwards (a 16-bit atomic per
+// corner and channel was 2x slower than the whole float32 pass and rounds at every addition).
+template <typename T, typename TA>
 __global__ void deform_outlier_bwd_kernel(const OutlierGrad *__restrict__ taps, const unsigned int *__restrict__ tap_count,
                                           const T *__restrict__ grad_out, const T *__restrict__ query, const T *__restrict__ key,
                                           const T *__restrict__ value, const T *__restrict__ offset, T *__restrict__ grad_query,
-                                          T *__restrict__ grad_key, T *__restrict__ grad_value, T *__restrict__ grad_offset,
+                                          TA *__restrict__ grad_key, TA *__restrict__ grad_value, T *__restrict__ grad_offset,
                                           int Cq, int C, int H, int W, int P, int G) {
     const int sW = 2 * W, gq = Cq / G, gc = C / G;
     const size_t hi = (size_t)(2 * H) * sW, lo = (size_t)H * W;
@@ -668,11 +671,11 @@ __global__ void deform_outlier_bwd_kernel(const OutlierGrad *__restrict__ taps, 
             float v00, v01, v10, v11;
             bl.corners(value + (bg * gc + c) * lo, v00, v01, v10, v11);
             const float tw = to_acc(grad_out[(bg * gc + c) * hi + pix]) * t.a;
-            T *gp = grad_value + (bg * gc + c) * lo;
-            if (bl.i00 >= 0) atomicAdd(gp + bl.i00, from_acc<T>(bl.w00 * tw));
-            if (bl.i01 >= 0) atomicAdd(gp + bl.i01, from_acc<T>(bl.w01 * tw));
-            if (bl.i10 >= 0) atomicAdd(gp + bl.i10, from_acc<T>(bl.w10 * tw));
-            if (bl.i11 >= 0) atomicAdd(gp + bl.i11, from_acc<T>(bl.w11 * tw));
+            TA *gp = grad_value + (bg * gc + c) * lo;
+            if (bl.i00 >= 0) atomicAdd(gp + bl.i00, from_acc<TA>(bl.w00 * tw));
+            if (bl.i01 >= 0) atomicAdd(gp + bl.i01, from_acc<TA>(bl.w01 * tw));
+            if (bl.i10 >= 0) atomicAdd(gp + bl.i10, from_acc<TA>(bl.w10 * tw));
+            if (bl.i11 >= 0) atomicAdd(gp + bl.i11, from_acc<TA>(bl.w11 * tw));
             g_w += (-hh * v00 + hh * v01 - bl.lh * v10 + bl.lh * v11) * tw;
             g_h += (-hw * v00 - bl.lw * v01 + hw * v10 + bl.lw * v11) * tw;
         }
@@ -681,11 +684,11 @@ __global__ void deform_outlier_bwd_kernel(const OutlierGrad *__restrict__ taps, 
             bl.corners(key + (bg * gq + c) * lo, v00, v01, v10, v11);
             atomicAdd(grad_query + (bg * gq + c) * hi + pix, from_acc<T>(t.ds * (bl.w00 * v00 + bl.w01 * v01 + bl.w10 * v10 + bl.w11 * v11)));
             const float tw = t.ds * to_acc(query[(bg * gq + c) * hi + pix]);
-            T *gp = grad_key + (bg * gq + c) * lo;
-            if (bl.i00 >= 0) atomicAdd(gp + bl.i00, from_acc<T>(bl.w00 * tw));
-            if (bl.i01 >= 0) atomicAdd(gp + bl.i01, from_acc<T>(bl.w01 * tw));
-            if (bl.i10 >= 0) atomicAdd(gp + bl.i10, from_acc<T>(bl.w10 * tw));
-            if (bl.i11 >= 0) atomicAdd(gp + bl.i11, from_acc<T>(bl.w11 * tw));
+            TA *gp = grad_key + (bg * gq + c) * lo;
+            if (bl.i00 >= 0) atomicAdd(gp + bl.i00, from_acc<TA>(bl.w00 * tw));
+            if (bl.i01 >= 0) atomicAdd(gp + bl.i01, from_acc<TA>(bl.w01 * tw));
+            if (bl.i10 >= 0) atomicAdd(gp + bl.i10, from_acc<TA>(bl.w10 * tw));
+            if (bl.i11 >= 0) atomicAdd(gp + bl.i11, from_acc<TA>(bl.w11 * tw));
             g_w += (-hh * v00 + hh * v01 - bl.lh * v10 + bl.lh * v11) * tw;
             g_h += (-hw * v00 - bl.lw * v01 + hw * v10 + bl.lw * v11) * tw;
         }
@@ -698,6 +701,20 @@ __global__ void deform_outlier_bwd_kernel(const OutlierGrad *__restrict__ taps, 
             grad_offset[(size_t)t.k * 2 * hi + pix] = from_acc<T>(g_w);
             grad_offset[(size_t)t.k * 2 * hi + hi + pix] = from_acc<T>(g_h);
         }
+    }
+}
+
+// dst[i] += side[i] for the 16-bit gradients whose outlier contributions were collected in float32; nothing to do (and
+// nothing read) when the list was empty.
+template <typename T>
+__global__ void deform_add_scatter_kernel(const unsigned int *__restrict__ tap_count, T *__restrict__ dst_a,
+                                          const float *__restrict__ side_a, size_t n_a, T *__restrict__ dst_b,
+                                          const float *__restrict__ side_b, size_t n_b) {
+    if (*tap_count == 0) return;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_a + n_b; i += stride) {
+        if (i < n_a) dst_a[i] = from_acc<T>(to_acc(dst_a[i]) + side_a[i]);
+        else dst_b[i - n_a] = from_acc<T>(to_acc(dst_b[i - n_a]) + side_b[i - n_a]);
     }
 }
 
@@ -1115,11 +1132,20 @@ int sapa_deform_av_forward_dense(const void *attn, const void *value, const void
 }
 
 size_t sapa_deform_fused_backward_workspace(int B, int H, int W, int P, int s, int G, int dtype) {
-    if (B <= 0 || H <= 0 || W <= 0 || P <= 0 || G <= 0 || s != 2 || dtype != SAPA_F32) return 0;
+    if (B <= 0 || H <= 0 || W <= 0 || P <= 0 || G <= 0 || s != 2) return 0;
+    // 16-bit tensors: 16-bit operands in the tensor-core kernels, float32 similarities between them (rows of 16 bytes)
+    if (dtype != SAPA_F32 && !((dtype == SAPA_F16 || dtype == SAPA_BF16) && W % 8 == 0 && fused_tma_supported(W, dtype))) return 0;
     const size_t hi = (size_t)s * H * s * W;
     if ((size_t)B * G * P >= 0xffffffffull || hi >= 0xffffffffull) return 0;
-    // D, dWd, dD, Wd, the outlier list (worst case: every point) and its counter
-    return (size_t)B * G * 100 * hi * dtype_size(dtype) + (size_t)B * G * P * hi * sizeof(OutlierGrad) + 16;
+    // D, dWd (float32), dD, Wd (the tensors' type; sized for float32), the outlier list (worst case: every point) and
+    // its counter
+    return (size_t)B * G * 100 * hi * sizeof(float) + (size_t)B * G * P * hi * sizeof(OutlierGrad) + 16;
+}
+
+// 16-bit tensors only: float32 side buffers for the scattered key / value gradients of the listed points
+size_t sapa_deform_fused_backward_scatter_bytes(int B, int Cq, int C, int H, int W, int dtype) {
+    if (dtype != SAPA_F16 && dtype != SAPA_BF16) return 0;
+    return ((size_t)B * Cq * H * W + (size_t)B * C * H * W) * sizeof(float);
 }
 
 int sapa_deform_fused_backward_dense(const void *grad_out, const void *query, const void *key, const void *value,
@@ -1132,47 +1158,78 @@ int sapa_deform_fused_backward_dense(const void *grad_out, const void *query, co
     SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value);
     SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, grad_query); SAPA_CHECK_PTR(fn, grad_key);
     SAPA_CHECK_PTR(fn, grad_value); SAPA_CHECK_PTR(fn, grad_offset);
-    const size_t need = sapa_deform_fused_backward_workspace(B, H, W, P, s, G, dtype);
-    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
-                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_fused_backward)", fn, MAXP);
+    const size_t base = sapa_deform_fused_backward_workspace(B, H, W, P, s, G, dtype);
+    const size_t side_off = (base + 15) & ~(size_t)15;          // the side buffers of the 16-bit path start here
+    const size_t need = side_off + sapa_deform_fused_backward_scatter_bytes(B, Cq, C, H, W, dtype);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && base != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32, or float16 / bfloat16 with rows of 16 bytes "
+                 "(use sapa_deform_fused_backward)", fn, MAXP);
     SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
                  "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
     const size_t hi = (size_t)s * H * s * W, plane = (size_t)B * G * 25 * hi;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    float *dense = static_cast<float *>(workspace), *dwin = dense + plane, *ddense = dwin + plane, *window = ddense + plane;
-    OutlierGrad *taps = reinterpret_cast<OutlierGrad *>(window + plane);
+    // D and dWd are float32 whatever the tensors' type; dD and Wd are weights of the SAPA-B kernels and have the tensors'
+    // type (those kernels round their weights to it anyway); every region is sized for float32
+    float *dense = static_cast<float *>(workspace), *dwin = dense + plane;
+    void *ddense = dwin + plane, *window = dwin + 2 * plane;
+    OutlierGrad *taps = reinterpret_cast<OutlierGrad *>(dense + 4 * plane);
     unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * P * hi);
     if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
         set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
         return SAPA_ERR_LAUNCH;
     }
-    const float *go = static_cast<const float *>(grad_out), *q = static_cast<const float *>(query), *k = static_cast<const float *>(key);
-    const float *v = static_cast<const float *>(value), *o = static_cast<const float *>(offset), *a = static_cast<const float *>(attn);
     // 1. D = sim(Q, Key) and dWd = sim(dOut, Value), the B x G groups as images
-    if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
-    if (int e = run_sim(grad_out, value, dwin, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
+    if (dtype == SAPA_F32) {
+        if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
+        if (int e = run_sim(grad_out, value, dwin, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
+    } else {
+        if (int e = run_sim_mixed(query, key, dense, B * G, Cq / G, H, W, H, 0, dtype, st)) return e;
+        if (int e = run_sim_mixed(grad_out, value, dwin, B * G, C / G, H, W, H, 0, dtype, st)) return e;
+    }
     // 2. per pixel: softmax backward over the points, dD, Wd, offset gradients, list of the points outside the window
     {
         const long long total = (long long)B * G * hi;
         const int grid = grid_1d(total, WIN_THREADS);
-        float *goff = static_cast<float *>(grad_offset);
-        if (P == 9)
-            deform_window_bwd_kernel<float, 9, BWD_FUSED><<<grid, WIN_THREADS, 0, st>>>(go, v, o, a, dense, dwin, ddense, window, goff, nullptr, taps, tap_count,
-                                                                           B, C, H, W, P, G);
-        else
-            deform_window_bwd_kernel<float, 0, BWD_FUSED><<<grid, WIN_THREADS, 0, st>>>(go, v, o, a, dense, dwin, ddense, window, goff, nullptr, taps, tap_count,
-                                                                           B, C, H, W, P, G);
-        if (int e = check_launch("deform_window_bwd_kernel")) return e;
+        const int e = SAPA_DISPATCH_FAST(dtype, [&] {
+            const scalar_t *go = static_cast<const scalar_t *>(grad_out), *v = static_cast<const scalar_t *>(value);
+            const scalar_t *o = static_cast<const scalar_t *>(offset), *a = static_cast<const scalar_t *>(attn);
+            scalar_t *dd = static_cast<scalar_t *>(ddense), *wn = static_cast<scalar_t *>(window), *goff = static_cast<scalar_t *>(grad_offset);
+            if (P == 9)
+                deform_window_bwd_kernel<scalar_t, 9, BWD_FUSED><<<grid, WIN_THREADS, 0, st>>>(go, v, o, a, dense, dwin, dd, wn, goff, nullptr, taps,
+                                                                                      tap_count, B, C, H, W, P, G);
+            else
+                deform_window_bwd_kernel<scalar_t, 0, BWD_FUSED><<<grid, WIN_THREADS, 0, st>>>(go, v, o, a, dense, dwin, dd, wn, goff, nullptr, taps,
+                                                                                      tap_count, B, C, H, W, P, G);
+            return check_launch("deform_window_bwd_kernel");
+        });
+        if (e) return e;
     }
     // 3. dQ = agg(dD, Key), dKey = gath(Q, dD), dV = gath(dOut, Wd): SAPA-B kernels per group, all outputs overwritten
     if (int e = run_agg(ddense, key, grad_query, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
     if (int e = run_gath(query, ddense, grad_key, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
     if (int e = run_gath(grad_out, window, grad_value, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
-    // 4. the listed points
-    deform_outlier_bwd_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, go, q, k, v, o, static_cast<float *>(grad_query),
-                                                              static_cast<float *>(grad_key), static_cast<float *>(grad_value),
-                                                              static_cast<float *>(grad_offset), Cq, C, H, W, P, G);
-    return check_launch("deform_outlier_bwd_kernel");
+    // 4. the listed points.  float32: atomics straight into the gradients.  16-bit: key / value contributions go to zeroed
+    //    float32 side buffers behind the list and are folded into the 16-bit gradients by one more kernel.
+    if (dtype == SAPA_F32) {
+        deform_outlier_bwd_kernel<float, float><<<148 * 8, 256, 0, st>>>(
+            taps, tap_count, static_cast<const float *>(grad_out), static_cast<const float *>(query), static_cast<const float *>(key),
+            static_cast<const float *>(value), static_cast<const float *>(offset), static_cast<float *>(grad_query),
+            static_cast<float *>(grad_key), static_cast<float *>(grad_value), static_cast<float *>(grad_offset), Cq, C, H, W, P, G);
+        return check_launch("deform_outlier_bwd_kernel");
+    }
+    const size_t n_k = (size_t)B * Cq * H * W, n_v = (size_t)B * C * H * W;
+    float *side_k = reinterpret_cast<float *>(static_cast<char *>(workspace) + side_off), *side_v = side_k + n_k;
+    if (int e = memset_async(side_k, (n_k + n_v) * sizeof(float), st, fn)) return e;
+    return SAPA_DISPATCH_FAST(dtype, [&] {
+        deform_outlier_bwd_kernel<scalar_t, float><<<148 * 8, 256, 0, st>>>(
+            taps, tap_count, static_cast<const scalar_t *>(grad_out), static_cast<const scalar_t *>(query),
+            static_cast<const scalar_t *>(key), static_cast<const scalar_t *>(value), static_cast<const scalar_t *>(offset),
+            static_cast<scalar_t *>(grad_query), side_k, side_v, static_cast<scalar_t *>(grad_offset), Cq, C, H, W, P, G);
+        if (int e = check_launch("deform_outlier_bwd_kernel")) return e;
+        deform_add_scatter_kernel<scalar_t><<<148 * 8, 256, 0, st>>>(tap_count, static_cast<scalar_t *>(grad_key), side_k, n_k,
+                                                                    static_cast<scalar_t *>(grad_value), side_v, n_v);
+        return check_launch("deform_add_scatter_kernel");
+    });
 }
 
 // Backward of deform_av and of deform_qk alone through the dense window (s = 2, float32): the two halves of
@@ -1208,7 +1265,7 @@ int sapa_deform_av_backward_dense(const void *grad_out, const void *attn, const 
         tap_count, B, C, H, W, P, G);
     if (int e = check_launch("deform_window_bwd_kernel<av>")) return e;
     if (int e = run_gath(grad_out, window, grad_value, B * G, C / G, H, W, 5, 2, dtype, st)) return e;  // dV
-    deform_outlier_bwd_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, go, nullptr, nullptr, v, o, nullptr, nullptr,
+    deform_outlier_bwd_kernel<float, float><<<148 * 8, 256, 0, st>>>(taps, tap_count, go, nullptr, nullptr, v, o, nullptr, nullptr,
                                                               static_cast<float *>(grad_value), static_cast<float *>(grad_offset),
                                                               C, C, H, W, P, G);
     return check_launch("deform_outlier_bwd_kernel");
@@ -1247,7 +1304,7 @@ int sapa_deform_qk_backward_dense(const void *grad_out, const void *query, const
     if (int e = check_launch("deform_window_bwd_kernel<qk>")) return e;
     if (int e = run_agg(ddense, key, grad_query, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;       // dQ
     if (int e = run_gath(query, ddense, grad_key, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;      // dKey
-    deform_outlier_bwd_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, nullptr, q, k, nullptr, o,
+    deform_outlier_bwd_kernel<float, float><<<148 * 8, 256, 0, st>>>(taps, tap_count, nullptr, q, k, nullptr, o,
                                                               static_cast<float *>(grad_query), static_cast<float *>(grad_key), nullptr,
                                                               static_cast<float *>(grad_offset), Cq, Cq, H, W, P, G);
     return check_launch("deform_outlier_bwd_kernel");

@@ -226,10 +226,25 @@ class DeformSapaFusedFunction(Function):
         num_point, scale_factor, groups = ctx.cfg
         grad_output = grad_output.contiguous()
         n, cq, h, w = key.shape
-        nbytes = 0
+        nbytes = native = 0
         if query.dtype in (torch.float32, torch.float16, torch.bfloat16) and num_point <= 16:
-            nbytes = int(_lib.lib().sapa_deform_fused_backward_workspace(n, h, w, num_point, scale_factor, groups, _lib.SAPA_F32))
-        if nbytes:          # s = 2: the dense-window path on the SAPA-B kernels (float32; 16-bit tensors are widened for it)
+            tensors = (grad_output, query, key, value, offset, attn)
+            if query.dtype != torch.float32 and all(t.data_ptr() % 16 == 0 for t in tensors):
+                native = int(_lib.lib().sapa_deform_fused_backward_workspace(n, h, w, num_point, scale_factor, groups,
+                                                                             _lib.dtype_code(query)))
+            nbytes = native or int(_lib.lib().sapa_deform_fused_backward_workspace(n, h, w, num_point, scale_factor, groups,
+                                                                                  _lib.SAPA_F32))
+        if native:          # 16-bit tensors with rows of 16 bytes: 16-bit operands, float32 similarities, 16-bit gradients
+            grad_query, grad_key, grad_value = torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
+            grad_offset = torch.empty_like(offset)
+            nbytes = ((native + 15) & ~15) + int(_lib.lib().sapa_deform_fused_backward_scatter_bytes(
+                n, cq, value.size(1), h, w, _lib.dtype_code(query)))
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
+            _lib.call("sapa_deform_fused_backward_dense", query.device, grad_output, query, key, value, offset, attn, grad_query,
+                      grad_key, grad_value, grad_offset, workspace, nbytes, n, cq, value.size(1), h, w, num_point, scale_factor,
+                      groups, _lib.dtype_code(query))
+            return grad_query, grad_key, grad_value, grad_offset, None, None, None
+        if nbytes:          # s = 2: the dense-window path on the SAPA-B kernels (float32; other 16-bit shapes are widened for it)
             dt = query.dtype
             f = (lambda t: t) if dt == torch.float32 else (lambda t: t.float())
             q32, k32, v32, o32 = f(query), f(key), f(value), f(offset)

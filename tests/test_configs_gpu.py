@@ -204,6 +204,33 @@ def test_dense_window_deform_matches_the_separate_ops(shape):
     assert _lib.wait_timeout_flags(dev) == 0
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 3e-2), (torch.float16, 4e-3)])
+@pytest.mark.parametrize("sigma", [0.5, 1.5])
+def test_deform_16bit_dense_window_forward_and_backward(sp, dtype, tol, sigma):
+    """float16 / bfloat16 SAPA-D with rows of 16 bytes runs the dense-window chain natively (16-bit operands, float32
+    similarities, 16-bit window weights; the scattered gradients of far points are collected in float32): output and all
+    four gradients against the float32 chain on the same rounded inputs, also with a quarter of the points far."""
+    from sapa_b200 import _lib
+    B, d, C, H, W, G, P, s = 2, 32, 64, 20, 24, 4, 9, 2
+    g = torch.Generator(device=DEV).manual_seed(43)
+    shapes = ((B, d, s * H, s * W), (B, d, H, W), (B, C, H, W), (B, 2 * G * P, s * H, s * W), (B, C, s * H, s * W))
+    q, k, v, off, go = (torch.randn(*sh, generator=g, device=DEV) for sh in shapes)
+    t16 = [t.to(dtype).requires_grad_() for t in (q, k, v, sigma * off)]
+    t32 = [t.detach().float().requires_grad_() for t in t16]
+    go16 = go.to(dtype)
+    out = sp.deform_sapa_fused(*t16, P, s, G)
+    assert _lib.last_kernels()[0] == "sapa_tma_fused_16_kernel<sim>"
+    got = torch.autograd.grad(out, t16, go16)
+    kernels = _lib.last_kernels()
+    assert kernels[:2] == ["sapa_tma_fused_16_kernel<sim>"] * 2 and kernels[-1] == "deform_add_scatter_kernel"
+    ref_out = sp.deform_sapa_fused(*t32, P, s, G)
+    ref = torch.autograd.grad(ref_out, t32, go16.float())
+    for a, b in [(out, ref_out)] + list(zip(got, ref)):
+        assert a.dtype == dtype
+        assert rel_err(f32(a), f32(b)) < tol
+    assert _lib.wait_timeout_flags(torch.device(DEV)) == 0
+
+
 @pytest.mark.parametrize("sigma,halo", [(0.5, None), (1.5, None), (0.2, 2)])
 def test_deform_row_slabs_with_halos_equal_the_unsharded_rows(sp, sigma, halo):
     """sapa_deform_fused_forward_slab on three row slabs of one image (key / value padded with the neighbours' rows, zeros
