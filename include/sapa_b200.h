@@ -227,7 +227,8 @@ int sapa_deform_fused_forward_slab(const void *query, const void *key, const voi
                                    int B, int Cq, int C, int H, int W, int halo_top, int halo_bottom,
                                    int P, int s, int G, int dtype, void *stream);
 
-/* sapa_deform_qk_forward and sapa_deform_av_forward by way of the dense 5 x 5 window (s = 2, float32): the two halves of
+/* sapa_deform_qk_forward and sapa_deform_av_forward by way of the dense 5 x 5 window (s = 2; float32, or float16 /
+ * bfloat16 with W a multiple of 8): the two halves of
  * sapa_deform_fused_forward_dense with the reference's op boundaries - raw logits out (deform_qk_cuda_kernel.cu:139-197)
  * and attention in (deform_av_cuda_kernel.cu:139-195).  Same results as the gather kernels; `workspace`:
  * sapa_deform_fused_forward_workspace() bytes, 16-byte aligned. */

@@ -1084,19 +1084,26 @@ int sapa_deform_qk_forward_dense(const void *query, const void *key, const void 
     if (int e = check_deform(fn, B, Cq, Cq, H, W, P, s, G, dtype)) return e;
     SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, out);
     const size_t need = sapa_deform_fused_forward_workspace(B, H, W, P, s, G, dtype);
-    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
-                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_qk_forward)", fn, MAXP);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && need != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32, or float16 / bfloat16 with rows of 16 bytes "
+                 "(use sapa_deform_qk_forward)", fn, MAXP);
     SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
                  "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
     const size_t hi = (size_t)s * H * s * W;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     float *dense = static_cast<float *>(workspace);
-    if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
+    if (dtype == SAPA_F32) {
+        if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;
+    } else {
+        if (int e = run_sim_mixed(query, key, dense, B * G, Cq / G, H, W, H, 0, dtype, st)) return e;
+    }
     const long long total = (long long)B * G * hi;
-    const float *q = static_cast<const float *>(query), *k = static_cast<const float *>(key), *o = static_cast<const float *>(offset);
-    deform_window_kernel<float, 0, WIN_LOGITS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-        q, k, o, dense, static_cast<float *>(out), nullptr, nullptr, nullptr, B, Cq, H, W, P, G, H, 0);
-    return check_launch("deform_window_kernel<logits>");
+    return SAPA_DISPATCH_FAST(dtype, [&] {
+        deform_window_kernel<scalar_t, 0, WIN_LOGITS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+            static_cast<const scalar_t *>(query), static_cast<const scalar_t *>(key), static_cast<const scalar_t *>(offset), dense,
+            static_cast<scalar_t *>(out), nullptr, nullptr, nullptr, B, Cq, H, W, P, G, H, 0);
+        return check_launch("deform_window_kernel<logits>");
+    });
 }
 
 int sapa_deform_av_forward_dense(const void *attn, const void *value, const void *offset, void *out, void *workspace,
@@ -1106,29 +1113,36 @@ int sapa_deform_av_forward_dense(const void *attn, const void *value, const void
     if (int e = check_deform(fn, B, C, C, H, W, P, s, G, dtype)) return e;
     SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset); SAPA_CHECK_PTR(fn, out);
     const size_t need = sapa_deform_fused_forward_workspace(B, H, W, P, s, G, dtype);
-    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
-                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_av_forward)", fn, MAXP);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && need != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32, or float16 / bfloat16 with rows of 16 bytes "
+                 "(use sapa_deform_av_forward)", fn, MAXP);
     SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
                  "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
     const size_t hi = (size_t)s * H * s * W;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    float *window = static_cast<float *>(workspace) + (size_t)B * G * 25 * hi;
-    OutlierTap *taps = reinterpret_cast<OutlierTap *>(window + (size_t)B * G * 25 * hi);
+    float *region = static_cast<float *>(workspace) + (size_t)B * G * 25 * hi;      // the window weights (tensor type) live here
+    OutlierTap *taps = reinterpret_cast<OutlierTap *>(region + (size_t)B * G * 25 * hi);
     unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * hi);
     if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
         set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
         return SAPA_ERR_LAUNCH;
     }
     const long long total = (long long)B * G * hi;
-    const float *o = static_cast<const float *>(offset);
     // the attention is only read in this mode
-    deform_window_kernel<float, 0, WIN_WEIGHTS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-        nullptr, nullptr, o, nullptr, const_cast<float *>(static_cast<const float *>(attn)), window, taps, tap_count, B, C, H, W, P, G, H, 0);
-    if (int e = check_launch("deform_window_kernel<weights>")) return e;
-    if (int e = run_agg(window, value, out, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
-    deform_outlier_kernel<float><<<148 * 8, 256, 0, st>>>(taps, tap_count, static_cast<const float *>(value), o,
-                                                          static_cast<float *>(out), C, H, W, P, G, H, 0);
-    return check_launch("deform_outlier_kernel");
+    if (int e = SAPA_DISPATCH_FAST(dtype, [&] {
+            deform_window_kernel<scalar_t, 0, WIN_WEIGHTS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                nullptr, nullptr, static_cast<const scalar_t *>(offset), nullptr, const_cast<scalar_t *>(static_cast<const scalar_t *>(attn)),
+                reinterpret_cast<scalar_t *>(region), taps, tap_count, B, C, H, W, P, G, H, 0);
+            return check_launch("deform_window_kernel<weights>");
+        }))
+        return e;
+    if (int e = run_agg(region, value, out, B * G, C / G, H, W, 5, 2, dtype, st)) return e;
+    return SAPA_DISPATCH_FAST(dtype, [&] {
+        deform_outlier_kernel<scalar_t><<<148 * 8, 256, 0, st>>>(taps, tap_count, static_cast<const scalar_t *>(value),
+                                                                 static_cast<const scalar_t *>(offset), static_cast<scalar_t *>(out), C, H,
+                                                                 W, P, G, H, 0);
+        return check_launch("deform_outlier_kernel");
+    });
 }
 
 size_t sapa_deform_fused_backward_workspace(int B, int H, int W, int P, int s, int G, int dtype) {

@@ -24,11 +24,15 @@ def _check_offset(offset, ref_lo, num_point, scale_factor, groups):
     assert num_point >= 1
 
 
-def _dense_workspace_bytes(t, n, h, w, num_point, scale_factor, groups) -> int:
-    """Workspace of the dense-window kernels for this problem, 0 when they do not apply (needs s = 2 and float32)."""
-    if t.dtype != torch.float32 or num_point > 16 or t.data_ptr() % 16 != 0:
+def _dense_workspace_bytes(t, n, h, w, num_point, scale_factor, groups, others=()) -> int:
+    """Workspace of the dense-window forward kernels for this problem, 0 when they do not apply (they need s = 2 and
+    float32, or float16 / bfloat16 with rows of 16 bytes and every tensor of the call - ``t`` and ``others`` - on a
+    16-byte boundary)."""
+    if t.dtype not in (torch.float32, torch.float16, torch.bfloat16) or num_point > 16 or t.data_ptr() % 16 != 0:
         return 0
-    return int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, _lib.SAPA_F32))
+    if t.dtype != torch.float32 and any(o.data_ptr() % 16 != 0 for o in others):
+        return 0
+    return int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, _lib.dtype_code(t)))
 
 
 def _dense_backward_bytes(t, grad_output, n, h, w, num_point, scale_factor, groups) -> int:
@@ -56,8 +60,8 @@ class DeformQKFunction(Function):
         ctx.cfg = (num_point, scale_factor, groups)
         n, c, h, w = query.shape
         out = torch.empty((n, groups, num_point, h, w), dtype=query.dtype, device=query.device)
-        nbytes = _dense_workspace_bytes(query, n, key.size(2), key.size(3), num_point, scale_factor, groups)
-        if nbytes:          # s = 2, float32: dense 5x5 similarity of the SAPA-B kernel + bilinear combination per point
+        nbytes = _dense_workspace_bytes(query, n, key.size(2), key.size(3), num_point, scale_factor, groups, (key, offset))
+        if nbytes:          # s = 2: dense 5x5 similarity of the SAPA-B kernel + bilinear combination per point
             workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
             _lib.call("sapa_deform_qk_forward_dense", query.device, query, key, offset, out, workspace, nbytes, n, c, key.size(2),
                       key.size(3), num_point, scale_factor, groups, _lib.dtype_code(query))
@@ -117,8 +121,8 @@ class DeformAVFunction(Function):
         ctx.cfg = (num_point, scale_factor, groups)
         n, c, h, w = value.shape
         out = torch.empty((n, c, scale_factor * h, scale_factor * w), dtype=value.dtype, device=value.device)
-        nbytes = _dense_workspace_bytes(value, n, h, w, num_point, scale_factor, groups)
-        if nbytes:          # s = 2, float32: window weights per pixel + the SAPA-B aggregation kernel
+        nbytes = _dense_workspace_bytes(value, n, h, w, num_point, scale_factor, groups, (attn, offset))
+        if nbytes:          # s = 2: window weights per pixel + the SAPA-B aggregation kernel
             workspace = torch.empty(nbytes, dtype=torch.uint8, device=value.device)
             _lib.call("sapa_deform_av_forward_dense", value.device, attn, value, offset, out, workspace, nbytes, n, c, h, w,
                       num_point, scale_factor, groups, _lib.dtype_code(value))

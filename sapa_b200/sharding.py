@@ -348,7 +348,7 @@ def _deform_slab_forward(query, key, value, offset, num_point, s, groups, halo, 
     C = value.size(1)
     if not query.is_cuda:
         return None
-    nbytes = _dense_workspace_bytes(query, B, Hl, W, num_point, s, groups)
+    nbytes = _dense_workspace_bytes(query, B, Hl, W, num_point, s, groups, (key, value, offset))
     if not nbytes or (W * query.element_size()) % 16 != 0:
         return None
     key_p, value_p = _pad_rows(key, halo), _pad_rows(value, halo)
