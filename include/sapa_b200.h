@@ -239,10 +239,11 @@ int sapa_deform_av_forward_dense(const void *attn, const void *value, const void
                                  size_t workspace_bytes, int B, int C, int H, int W, int P, int s, int G, int dtype,
                                  void *stream);
 
-/* sapa_deform_av_backward and sapa_deform_qk_backward by way of the dense 5 x 5 window (s = 2, float32): the two halves
- * of sapa_deform_fused_backward_dense without the softmax between them (deform_av_cuda_kernel.cu:230-292,
- * deform_qk_cuda_kernel.cu:233-296).  All gradients are float32 tensors of the shapes of their inputs and are
- * overwritten; `workspace`: sapa_deform_fused_backward_workspace() bytes, 16-byte aligned. */
+/* sapa_deform_av_backward and sapa_deform_qk_backward by way of the dense 5 x 5 window (s = 2; float32, or float16 /
+ * bfloat16 with W a multiple of 8): the two halves of sapa_deform_fused_backward_dense without the softmax between them
+ * (deform_av_cuda_kernel.cu:230-292, deform_qk_cuda_kernel.cu:233-296).  All gradients have the type and the shapes of
+ * their inputs and are overwritten; `workspace`: sapa_deform_fused_backward_workspace() bytes, 16-byte aligned, for 16-bit
+ * tensors rounded up to 16 plus sapa_deform_fused_backward_scatter_bytes(B, 0, C, ...) (av) or (B, Cq, 0, ...) (qk). */
 int sapa_deform_av_backward_dense(const void *grad_out, const void *attn, const void *value, const void *offset,
                                   void *grad_attn, void *grad_value, void *grad_offset, void *workspace,
                                   size_t workspace_bytes, int B, int C, int H, int W, int P, int s, int G, int dtype,

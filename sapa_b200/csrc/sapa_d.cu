@@ -1256,33 +1256,58 @@ int sapa_deform_av_backward_dense(const void *grad_out, const void *attn, const 
     if (int e = check_deform(fn, B, C, C, H, W, P, s, G, dtype)) return e;
     SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, attn); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, offset);
     SAPA_CHECK_PTR(fn, grad_attn); SAPA_CHECK_PTR(fn, grad_value); SAPA_CHECK_PTR(fn, grad_offset);
-    const size_t need = sapa_deform_fused_backward_workspace(B, H, W, P, s, G, dtype);
-    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
-                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_av_backward)", fn, MAXP);
+    const size_t base = sapa_deform_fused_backward_workspace(B, H, W, P, s, G, dtype);
+    const size_t side_off = (base + 15) & ~(size_t)15;
+    const size_t need = side_off + sapa_deform_fused_backward_scatter_bytes(B, 0, C, H, W, dtype);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && base != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32, or float16 / bfloat16 with rows of 16 bytes "
+                 "(use sapa_deform_av_backward)", fn, MAXP);
     SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
                  "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
     const size_t hi = (size_t)s * H * s * W, plane = (size_t)B * G * 25 * hi;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    float *dwin = static_cast<float *>(workspace) + plane, *window = dwin + 2 * plane;
-    OutlierGrad *taps = reinterpret_cast<OutlierGrad *>(window + plane);
+    float *dwin = static_cast<float *>(workspace) + plane;
+    void *window = dwin + 2 * plane;                                   // Wd, in the tensors' type
+    OutlierGrad *taps = reinterpret_cast<OutlierGrad *>(static_cast<float *>(workspace) + 4 * plane);
     unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * P * hi);
     if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
         set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
         return SAPA_ERR_LAUNCH;
     }
-    const float *go = static_cast<const float *>(grad_out), *v = static_cast<const float *>(value);
-    const float *o = static_cast<const float *>(offset), *a = static_cast<const float *>(attn);
-    if (int e = run_sim(grad_out, value, dwin, B * G, C / G, H, W, 5, 2, dtype, st)) return e;        // dWd
+    if (dtype == SAPA_F32) {
+        if (int e = run_sim(grad_out, value, dwin, B * G, C / G, H, W, 5, 2, dtype, st)) return e;        // dWd
+    } else {
+        if (int e = run_sim_mixed(grad_out, value, dwin, B * G, C / G, H, W, H, 0, dtype, st)) return e;
+    }
     const long long total = (long long)B * G * hi;
-    deform_window_bwd_kernel<float, 0, BWD_AV><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-        go, v, o, a, nullptr, dwin, nullptr, window, static_cast<float *>(grad_offset), static_cast<float *>(grad_attn), taps,
-        tap_count, B, C, H, W, P, G);
-    if (int e = check_launch("deform_window_bwd_kernel<av>")) return e;
+    if (int e = SAPA_DISPATCH_FAST(dtype, [&] {
+            deform_window_bwd_kernel<scalar_t, 0, BWD_AV><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                static_cast<const scalar_t *>(grad_out), static_cast<const scalar_t *>(value), static_cast<const scalar_t *>(offset),
+                static_cast<const scalar_t *>(attn), nullptr, dwin, nullptr, static_cast<scalar_t *>(window),
+                static_cast<scalar_t *>(grad_offset), static_cast<scalar_t *>(grad_attn), taps, tap_count, B, C, H, W, P, G);
+            return check_launch("deform_window_bwd_kernel<av>");
+        }))
+        return e;
     if (int e = run_gath(grad_out, window, grad_value, B * G, C / G, H, W, 5, 2, dtype, st)) return e;  // dV
-    deform_outlier_bwd_kernel<float, float><<<148 * 8, 256, 0, st>>>(taps, tap_count, go, nullptr, nullptr, v, o, nullptr, nullptr,
-                                                              static_cast<float *>(grad_value), static_cast<float *>(grad_offset),
-                                                              C, C, H, W, P, G);
-    return check_launch("deform_outlier_bwd_kernel");
+    if (dtype == SAPA_F32) {
+        deform_outlier_bwd_kernel<float, float><<<148 * 8, 256, 0, st>>>(
+            taps, tap_count, static_cast<const float *>(grad_out), nullptr, nullptr, static_cast<const float *>(value),
+            static_cast<const float *>(offset), nullptr, nullptr, static_cast<float *>(grad_value), static_cast<float *>(grad_offset),
+            C, C, H, W, P, G);
+        return check_launch("deform_outlier_bwd_kernel");
+    }
+    const size_t n_v = (size_t)B * C * H * W;
+    float *side_v = reinterpret_cast<float *>(static_cast<char *>(workspace) + side_off);
+    if (int e = memset_async(side_v, n_v * sizeof(float), st, fn)) return e;
+    return SAPA_DISPATCH_FAST(dtype, [&] {
+        deform_outlier_bwd_kernel<scalar_t, float><<<148 * 8, 256, 0, st>>>(
+            taps, tap_count, static_cast<const scalar_t *>(grad_out), nullptr, nullptr, static_cast<const scalar_t *>(value),
+            static_cast<const scalar_t *>(offset), nullptr, nullptr, side_v, static_cast<scalar_t *>(grad_offset), C, C, H, W, P, G);
+        if (int e = check_launch("deform_outlier_bwd_kernel")) return e;
+        deform_add_scatter_kernel<scalar_t><<<148 * 8, 256, 0, st>>>(tap_count, static_cast<scalar_t *>(grad_value), side_v, n_v,
+                                                                    static_cast<scalar_t *>(nullptr), nullptr, 0);
+        return check_launch("deform_add_scatter_kernel");
+    });
 }
 
 int sapa_deform_qk_backward_dense(const void *grad_out, const void *query, const void *key, const void *offset, void *grad_query,
@@ -1293,35 +1318,60 @@ int sapa_deform_qk_backward_dense(const void *grad_out, const void *query, const
     if (int e = check_deform(fn, B, Cq, Cq, H, W, P, s, G, dtype)) return e;
     SAPA_CHECK_PTR(fn, grad_out); SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, offset);
     SAPA_CHECK_PTR(fn, grad_query); SAPA_CHECK_PTR(fn, grad_key); SAPA_CHECK_PTR(fn, grad_offset);
-    const size_t need = sapa_deform_fused_backward_workspace(B, H, W, P, s, G, dtype);
-    SAPA_REQUIRE(s == 2 && P <= MAXP && dtype == SAPA_F32 && need != 0, SAPA_ERR_UNSUPPORTED,
-                 "%s: the dense-window path needs s = 2, num_point <= %d and float32 (use sapa_deform_qk_backward)", fn, MAXP);
+    const size_t base = sapa_deform_fused_backward_workspace(B, H, W, P, s, G, dtype);
+    const size_t side_off = (base + 15) & ~(size_t)15;
+    const size_t need = side_off + sapa_deform_fused_backward_scatter_bytes(B, Cq, 0, H, W, dtype);
+    SAPA_REQUIRE(s == 2 && P <= MAXP && base != 0, SAPA_ERR_UNSUPPORTED,
+                 "%s: the dense-window path needs s = 2, num_point <= %d and float32, or float16 / bfloat16 with rows of 16 bytes "
+                 "(use sapa_deform_qk_backward)", fn, MAXP);
     SAPA_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned16(workspace), SAPA_ERR_WORKSPACE,
                  "%s: a 16-byte aligned workspace of %zu bytes is required, got %zu", fn, need, workspace_bytes);
     const size_t hi = (size_t)s * H * s * W, plane = (size_t)B * G * 25 * hi;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    float *dense = static_cast<float *>(workspace), *ddense = dense + 2 * plane;
+    float *dense = static_cast<float *>(workspace);
+    void *ddense = dense + 2 * plane;                                  // dD, in the tensors' type
     OutlierGrad *taps = reinterpret_cast<OutlierGrad *>(dense + 4 * plane);
     unsigned int *tap_count = reinterpret_cast<unsigned int *>(taps + (size_t)B * G * P * hi);
     if (cudaMemsetAsync(tap_count, 0, sizeof(unsigned int), st) != cudaSuccess) {
         set_error("%s: clearing the outlier counter failed: %s", fn, cudaGetErrorString(cudaGetLastError()));
         return SAPA_ERR_LAUNCH;
     }
-    const float *ds = static_cast<const float *>(grad_out), *q = static_cast<const float *>(query), *k = static_cast<const float *>(key);
-    const float *o = static_cast<const float *>(offset);
-    if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;             // D, for the offset gradients
+    if (dtype == SAPA_F32) {
+        if (int e = run_sim(query, key, dense, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;         // D, for the offset gradients
+    } else {
+        if (int e = run_sim_mixed(query, key, dense, B * G, Cq / G, H, W, H, 0, dtype, st)) return e;
+    }
     const long long total = (long long)B * G * hi;
     // the logit gradients enter where the fused chain reads the attention
-    deform_window_bwd_kernel<float, 0, BWD_QK><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-        nullptr, nullptr, o, ds, dense, nullptr, ddense, nullptr, static_cast<float *>(grad_offset), nullptr, taps, tap_count,
-        B, Cq, H, W, P, G);
-    if (int e = check_launch("deform_window_bwd_kernel<qk>")) return e;
+    if (int e = SAPA_DISPATCH_FAST(dtype, [&] {
+            deform_window_bwd_kernel<scalar_t, 0, BWD_QK><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                nullptr, nullptr, static_cast<const scalar_t *>(offset), static_cast<const scalar_t *>(grad_out), dense, nullptr,
+                static_cast<scalar_t *>(ddense), nullptr, static_cast<scalar_t *>(grad_offset), nullptr, taps, tap_count, B, Cq, H, W, P, G);
+            return check_launch("deform_window_bwd_kernel<qk>");
+        }))
+        return e;
     if (int e = run_agg(ddense, key, grad_query, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;       // dQ
     if (int e = run_gath(query, ddense, grad_key, B * G, Cq / G, H, W, 5, 2, dtype, st)) return e;      // dKey
-    deform_outlier_bwd_kernel<float, float><<<148 * 8, 256, 0, st>>>(taps, tap_count, nullptr, q, k, nullptr, o,
-                                                              static_cast<float *>(grad_query), static_cast<float *>(grad_key), nullptr,
-                                                              static_cast<float *>(grad_offset), Cq, Cq, H, W, P, G);
-    return check_launch("deform_outlier_bwd_kernel");
+    if (dtype == SAPA_F32) {
+        deform_outlier_bwd_kernel<float, float><<<148 * 8, 256, 0, st>>>(
+            taps, tap_count, nullptr, static_cast<const float *>(query), static_cast<const float *>(key), nullptr,
+            static_cast<const float *>(offset), static_cast<float *>(grad_query), static_cast<float *>(grad_key), nullptr,
+            static_cast<float *>(grad_offset), Cq, Cq, H, W, P, G);
+        return check_launch("deform_outlier_bwd_kernel");
+    }
+    const size_t n_k = (size_t)B * Cq * H * W;
+    float *side_k = reinterpret_cast<float *>(static_cast<char *>(workspace) + side_off);
+    if (int e = memset_async(side_k, n_k * sizeof(float), st, fn)) return e;
+    return SAPA_DISPATCH_FAST(dtype, [&] {
+        deform_outlier_bwd_kernel<scalar_t, float><<<148 * 8, 256, 0, st>>>(
+            taps, tap_count, nullptr, static_cast<const scalar_t *>(query), static_cast<const scalar_t *>(key), nullptr,
+            static_cast<const scalar_t *>(offset), static_cast<scalar_t *>(grad_query), side_k, nullptr,
+            static_cast<scalar_t *>(grad_offset), Cq, Cq, H, W, P, G);
+        if (int e = check_launch("deform_outlier_bwd_kernel")) return e;
+        deform_add_scatter_kernel<scalar_t><<<148 * 8, 256, 0, st>>>(tap_count, static_cast<scalar_t *>(grad_key), side_k, n_k,
+                                                                    static_cast<scalar_t *>(nullptr), nullptr, 0);
+        return check_launch("deform_add_scatter_kernel");
+    });
 }
 
 }  // extern "C"

@@ -35,11 +35,23 @@ def _dense_workspace_bytes(t, n, h, w, num_point, scale_factor, groups, others=(
     return int(_lib.lib().sapa_deform_fused_forward_workspace(n, h, w, num_point, scale_factor, groups, _lib.dtype_code(t)))
 
 
-def _dense_backward_bytes(t, grad_output, n, h, w, num_point, scale_factor, groups) -> int:
-    """Workspace of the dense-window backward kernels, 0 when they do not apply (needs s = 2 and float32)."""
-    if t.dtype != torch.float32 or num_point > 16 or t.data_ptr() % 16 != 0 or grad_output.data_ptr() % 16 != 0:
+def _dense_backward_bytes(t, grad_output, n, h, w, num_point, scale_factor, groups, others=(), cq=0, c=0) -> int:
+    """Workspace of the dense-window backward kernels, 0 when they do not apply (they need s = 2 and float32, or
+    float16 / bfloat16 with rows of 16 bytes and every tensor of the call on a 16-byte boundary; the 16-bit form adds
+    float32 side buffers for the scattered gradients of ``cq`` key and ``c`` value channels)."""
+    if t.dtype not in (torch.float32, torch.float16, torch.bfloat16) or num_point > 16:
         return 0
-    return int(_lib.lib().sapa_deform_fused_backward_workspace(n, h, w, num_point, scale_factor, groups, _lib.SAPA_F32))
+    if t.data_ptr() % 16 != 0 or grad_output.data_ptr() % 16 != 0:
+        return 0
+    if t.dtype == torch.float32:
+        return int(_lib.lib().sapa_deform_fused_backward_workspace(n, h, w, num_point, scale_factor, groups, _lib.SAPA_F32))
+    if any(o.data_ptr() % 16 != 0 for o in others):
+        return 0
+    code = _lib.dtype_code(t)
+    base = int(_lib.lib().sapa_deform_fused_backward_workspace(n, h, w, num_point, scale_factor, groups, code))
+    if not base:
+        return 0
+    return ((base + 15) & ~15) + int(_lib.lib().sapa_deform_fused_backward_scatter_bytes(n, cq, c, h, w, code))
 
 
 class DeformQKFunction(Function):
@@ -82,17 +94,18 @@ class DeformQKFunction(Function):
 
 
 def deform_qk_backward_raw(grad_output, query, key, offset, num_point, scale_factor, groups):
+    n, c, h, w = key.shape
+    grad_offset = torch.empty_like(offset)
+    nbytes = _dense_backward_bytes(query, grad_output, n, h, w, num_point, scale_factor, groups, (key, offset), cq=c)
+    if nbytes:              # s = 2: SAPA-B kernels around one per-pixel kernel; the gradients have the tensors' type
+        grad_query, grad_key = torch.empty_like(query), torch.empty_like(key)
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
+        _lib.call("sapa_deform_qk_backward_dense", query.device, grad_output, query, key, offset, grad_query, grad_key,
+                  grad_offset, workspace, nbytes, n, c, h, w, num_point, scale_factor, groups, _lib.dtype_code(query))
+        return grad_query, grad_key, grad_offset
     acc = _acc_dtype(query)
     grad_query = torch.empty(query.shape, dtype=acc, device=query.device)
     grad_key = torch.empty(key.shape, dtype=acc, device=key.device)
-    grad_offset = torch.empty_like(offset)
-    n, c, h, w = key.shape
-    nbytes = _dense_backward_bytes(query, grad_output, n, h, w, num_point, scale_factor, groups)
-    if nbytes:              # s = 2, float32: SAPA-B kernels around one per-pixel kernel
-        workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
-        _lib.call("sapa_deform_qk_backward_dense", query.device, grad_output, query, key, offset, grad_query, grad_key,
-                  grad_offset, workspace, nbytes, n, c, h, w, num_point, scale_factor, groups, _lib.SAPA_F32)
-        return grad_query, grad_key, grad_offset
     _lib.call("sapa_deform_qk_backward", query.device, grad_output, query, key, offset, grad_query, grad_key,
               grad_offset, n, c, h, w, num_point, scale_factor, groups, _lib.dtype_code(query))
     return grad_query.to(query.dtype), grad_key.to(key.dtype), grad_offset
@@ -144,15 +157,16 @@ class DeformAVFunction(Function):
 
 def deform_av_backward_raw(grad_output, attn, value, offset, num_point, scale_factor, groups):
     grad_attn = torch.empty_like(attn)
-    grad_value = torch.empty(value.shape, dtype=_acc_dtype(value), device=value.device)
     grad_offset = torch.empty_like(offset)
     n, c, h, w = value.shape
-    nbytes = _dense_backward_bytes(value, grad_output, n, h, w, num_point, scale_factor, groups)
-    if nbytes:
+    nbytes = _dense_backward_bytes(value, grad_output, n, h, w, num_point, scale_factor, groups, (attn, offset), c=c)
+    if nbytes:              # the gradients have the tensors' type
+        grad_value = torch.empty_like(value)
         workspace = torch.empty(nbytes, dtype=torch.uint8, device=value.device)
         _lib.call("sapa_deform_av_backward_dense", value.device, grad_output, attn, value, offset, grad_attn, grad_value,
-                  grad_offset, workspace, nbytes, n, c, h, w, num_point, scale_factor, groups, _lib.SAPA_F32)
+                  grad_offset, workspace, nbytes, n, c, h, w, num_point, scale_factor, groups, _lib.dtype_code(value))
         return grad_attn, grad_value, grad_offset
+    grad_value = torch.empty(value.shape, dtype=_acc_dtype(value), device=value.device)
     _lib.call("sapa_deform_av_backward", value.device, grad_output, attn, value, offset, grad_attn, grad_value,
               grad_offset, n, c, h, w, num_point, scale_factor, groups, _lib.dtype_code(value))
     return grad_attn, grad_value.to(value.dtype), grad_offset

@@ -231,6 +231,40 @@ def test_deform_16bit_dense_window_forward_and_backward(sp, dtype, tol, sigma):
     assert _lib.wait_timeout_flags(torch.device(DEV)) == 0
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 3e-2), (torch.float16, 4e-3)])
+def test_deform_16bit_separate_ops_through_the_window(sp, dtype, tol):
+    """deform_qk / deform_av and their backward in float16 / bfloat16 (rows of 16 bytes) run through the dense window like
+    float32; results and gradients against the float32 ops on the same rounded inputs (sigma = 1: a quarter of the
+    points leave the window, so the float32 side buffers of the scattered gradients are exercised)."""
+    from sapa_b200 import _lib
+    B, d, C, H, W, G, P, s = 2, 32, 64, 20, 24, 4, 9, 2
+    g = torch.Generator(device=DEV).manual_seed(47)
+    shapes = ((B, d, s * H, s * W), (B, d, H, W), (B, C, H, W), (B, 2 * G * P, s * H, s * W), (B, G, P, s * H, s * W),
+              (B, C, s * H, s * W))
+    q, k, v, off, gs, go = (torch.randn(*sh, generator=g, device=DEV) for sh in shapes)
+    q16, k16, v16, o16 = (t.to(dtype).requires_grad_() for t in (q, k, v, off))
+    q32, k32, v32, o32 = (t.detach().float().requires_grad_() for t in (q16, k16, v16, o16))
+    sim = sp.deform_qk(q16, k16, o16, P, s, G)
+    assert _lib.last_kernels() == ["sapa_tma_fused_16_kernel<sim>", "deform_window_kernel<logits>"]
+    got = torch.autograd.grad(sim, (q16, k16, o16), gs.to(dtype))
+    assert _lib.last_kernels()[-1] == "deform_add_scatter_kernel"
+    sim32 = sp.deform_qk(q32, k32, o32, P, s, G)
+    ref = torch.autograd.grad(sim32, (q32, k32, o32), gs.to(dtype).float())
+    for a, b in [(sim, sim32)] + list(zip(got, ref)):
+        assert a.dtype == dtype and rel_err(f32(a), f32(b)) < tol
+    a16 = torch.softmax(sim32.detach(), dim=2).to(dtype).requires_grad_()
+    a32 = a16.detach().float().requires_grad_()
+    out = sp.deform_av(a16, v16, o16, P, s, G)
+    assert _lib.last_kernels()[:2] == ["deform_window_kernel<weights>", "sapa_tma_fused_16_kernel<agg>"]
+    got = torch.autograd.grad(out, (a16, v16, o16), go.to(dtype))
+    assert _lib.last_kernels()[-1] == "deform_add_scatter_kernel"
+    out32 = sp.deform_av(a32, v32, o32, P, s, G)
+    ref = torch.autograd.grad(out32, (a32, v32, o32), go.to(dtype).float())
+    for a, b in [(out, out32)] + list(zip(got, ref)):
+        assert a.dtype == dtype and rel_err(f32(a), f32(b)) < tol
+    assert _lib.wait_timeout_flags(torch.device(DEV)) == 0
+
+
 @pytest.mark.parametrize("sigma,halo", [(0.5, None), (1.5, None), (0.2, 2)])
 def test_deform_row_slabs_with_halos_equal_the_unsharded_rows(sp, sigma, halo):
     """sapa_deform_fused_forward_slab on three row slabs of one image (key / value padded with the neighbours' rows, zeros
