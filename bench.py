@@ -701,6 +701,18 @@ def main():
                                                   "its float32 accumulation buffers; bytes = dOut, attention read; q, k, v, offsets read and "
                                                   "their gradients written"}
         del qd, kd, vd, od, out_d
+        if dtype == torch.float32:      # the same two calls on bfloat16 tensors (16-bit operands, float32 similarities)
+            h16 = [x.to(torch.bfloat16) for x in (t["q"], t["k"], t["v"], off, g_out)]
+            ms_d16 = time_path(lambda: sapa_b200.deform_sapa_fused(h16[0], h16[1], h16[2], h16[3], P_, s, G_), 10)
+            k16 = sapa_b200._lib.last_kernels()
+            r16 = [x.detach().clone().requires_grad_() for x in h16[:4]]
+            out16 = sapa_b200.deform_sapa_fused(*r16, P_, s, G_)
+            ms_db16 = time_path(lambda: torch.autograd.grad(out16, r16, h16[4], retain_graph=True), 10)
+            paths["sapa_d_fused_bf16"] = {"forward_ms": ms_d16, "backward_ms": ms_db16,
+                                          "forward_roofline_frac": bytes_d / 2 / (ms_d16 * 1e-3) / 1e9 / peak_gbs,
+                                          "backward_roofline_frac": bytes_db / 2 / (ms_db16 * 1e-3) / 1e9 / peak_gbs,
+                                          "forward_kernels": k16, "backward_kernels": sapa_b200._lib.last_kernels()}
+            del h16, r16, out16
         del t, off, g_out, attn_b
         # Decoder pyramid (stand-in wiring, random init, forward only, bf16, B = 16): features of 64 / 128 / 320 / 512
         # channels at 128^2 / 64^2 / 32^2 / 16^2, each projected to 256 channels by a 1x1 convolution, then three
