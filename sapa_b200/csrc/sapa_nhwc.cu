@@ -2,13 +2,15 @@
 //   query [B, sH, sW, d], key [B, H, W, d], value [B, H, W, C] -> out [B, sH, sW, C] (attention [B, sH, sW, K*K] optional).
 // Same arithmetic as sapa_fused_forward (sim -> softmax over the K*K window slots -> atn, zero padding at the border;
 // reference: qk_cuda_kernel.cu:29-68, av_cuda_kernel.cu:29-75, sapa_base.py:38-40), other memory layout: with the channels
-// contiguous a window cell is one vector, so the kernel needs no tiles and no shared memory.
+// contiguous a window cell is one vector, so the kernel needs no tiles (shared memory only holds a warp's weights).
 // One warp per 2 x 2 group of high-res pixels of one parent (per pixel when s is odd): they share the parent's window, so
-// every key / value vector that is loaded serves four pixels.  Logits: lane k < K*K owns window slot k and walks the d channels of its key cell with
-// 16-byte loads (the query vector is the same address in every lane: a broadcast load).  Softmax: two warp reductions.
-// Aggregation: the lanes switch to channels - lane l owns 16 bytes of channels at a time - and take the K*K weights from
-// the other lanes by shuffle; every load of the value tensor is a 512-byte run of one cell.  Neighbouring pixels read
-// the same cells, so the key / value traffic is served by L1 / L2.
+// every key / value vector that is loaded serves four pixels.  Logits: eight lanes read the d channels of one window
+// slot's key cell with 16-byte loads (one 128-byte line per slot and load instruction; four slots at a time) and add
+// their partial dot products by shuffle; the query vectors are broadcast loads.  Softmax: lane k owns slot k, two warp
+// reductions per pixel; the weights then go to a per-warp scratch row in shared memory.  Aggregation: the lanes switch
+// to channels - lane l owns 16 bytes of channels at a time - and read the four weights of a slot as one broadcast
+// 16-byte shared-memory load; every load of the value tensor is a 512-byte run of one cell.  Neighbouring pixel groups
+// read the same cells, so the key / value traffic is served by L1 / L2.
 #include "common.cuh"
 
 namespace sapa {
@@ -64,86 +66,129 @@ __device__ __forceinline__ void store_vec(__nv_bfloat16 *p, const float (&v)[8])
 }
 
 // NPX = high-res pixels of one parent handled together (they share the parent's window): 4 when s is even, else 1.
+// Per warp: lg[slot][pixel] = logits, then the aggregation weights (0 for a slot outside the image: its value is zero
+// padding); cell_k / cell_v = element offset of the slot's cell in the key / value image, -1 / 0 outside the image.
+// Addresses are one 64-bit base per tensor and group plus 32-bit offsets: an image of any one tensor must hold fewer
+// than 2^31 elements (checked by the entry point).
 template <typename T, int NPX>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, sizeof(T) == 4 ? 5 : 4) == 4 ? 5 : 3)
 sapa_nhwc_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ value, T *__restrict__ out,
                      T *__restrict__ attn, int B, int d, int C, int H, int W, int K, int s) {
     constexpr int VN = Vec<T>::N;
     constexpr int PW = NPX == 4 ? 2 : 1;             // pixel group = PW x PW
+    __shared__ __align__(16) float lg_all[WARPS][32 * NPX];
+    __shared__ int cell_all[WARPS][64];
+    float *lg = lg_all[threadIdx.x >> 5];
+    int *cell_k = cell_all[threadIdx.x >> 5], *cell_v = cell_k + 32;
     const int lane = threadIdx.x & 31, KK = K * K, r = (K - 1) / 2;
     const int sH = s * H, sW = s * W, gw = sW / PW, gh = sH / PW;
-    const long long groups = (long long)B * gh * gw;
-    const long long warp0 = (long long)blockIdx.x * WARPS + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * WARPS;
-    for (long long gi = warp0; gi < groups; gi += nwarps) {
-        const int gx = (int)(gi % gw), gy = (int)((gi / gw) % gh), b = (int)(gi / ((long long)gw * gh));
+    const unsigned groups = (unsigned)B * gh * gw;
+    const unsigned warp0 = blockIdx.x * WARPS + (threadIdx.x >> 5), nwarps = gridDim.x * WARPS;
+    const int sub = lane & 7, quarter = lane >> 3;           // logits: eight lanes per window slot, four slots at a time
+    const bool slot = lane < KK;
+    const int dy = lane / K - r, dx = lane % K - r;          // this lane's window slot
+    int poff[NPX];                                           // pixel j of a group relative to its first pixel
+#pragma unroll
+    for (int j = 0; j < NPX; ++j) poff[j] = (j / PW) * sW + j % PW;
+    for (unsigned gi = warp0; gi < groups; gi += nwarps) {
+        const int gx = (int)(gi % (unsigned)gw), gy = (int)((gi / (unsigned)gw) % (unsigned)gh), b = (int)(gi / ((unsigned)gw * gh));
         const int qh0 = gy * PW, qw0 = gx * PW, ph = qh0 / s, pw = qw0 / s;      // the group lies inside one parent
-        // ---- logits: lane k owns window slot k, for the NPX pixels of the group
-        const int ky = ph + lane / K - r, kx = pw + lane % K - r;
-        const bool slot = lane < KK, inside = slot && ky >= 0 && ky < H && kx >= 0 && kx < W;
-        const int cell = inside ? (ky * W + kx) : -1;
-        size_t pix[NPX];
+        const size_t pix0 = ((size_t)b * sH + qh0) * sW + qw0;
+        const T *q0 = query + pix0 * d, *kimg = key + (size_t)b * H * W * d, *vimg = value + (size_t)b * H * W * C;
+        __syncwarp();                      // the previous group's weights have been read by every lane
+        bool inside = false;
+        if (slot) {
+            const int ky = ph + dy, kx = pw + dx;
+            inside = ky >= 0 && ky < H && kx >= 0 && kx < W;
+            cell_k[lane] = inside ? (ky * W + kx) * d : -1;
+            cell_v[lane] = inside ? (ky * W + kx) * C : 0;
+        }
+        __syncwarp();
+        // ---- logits: the key vector of a slot is read by eight lanes, 16 bytes each (one 128-byte line per slot and
+        // load), the partial dot products are added over the eight lanes; a slot outside the image has logit exactly 0
+        for (int k0 = 0; k0 < KK; k0 += 4) {
+            const int k = k0 + quarter;
+            const int cell = k < KK ? cell_k[k] : -1;
+            float part[NPX];
 #pragma unroll
-        for (int j = 0; j < NPX; ++j) pix[j] = ((size_t)b * sH + qh0 + j / PW) * sW + qw0 + j % PW;
-        float logit[NPX];
+            for (int j = 0; j < NPX; ++j) part[j] = 0.f;
+            if (cell >= 0) {
+                const T *kp = kimg + cell;
+                for (int c = sub * VN; c < d; c += 8 * VN) {
+                    float kv[VN];
+                    load_vec(kp + c, kv);
 #pragma unroll
-        for (int j = 0; j < NPX; ++j) logit[j] = 0.f;   // a cell outside the image is zero padding: its logit is exactly 0
-        if (inside) {
-            const T *kp = key + ((size_t)b * H * W + cell) * d;
-            for (int c = 0; c < d; c += VN) {
-                float kv[VN];
-                load_vec(kp + c, kv);
+                    for (int j = 0; j < NPX; ++j) {
+                        float qv[VN];
+                        load_vec(q0 + (poff[j] * d + c), qv);
 #pragma unroll
-                for (int j = 0; j < NPX; ++j) {
-                    float qv[VN];
-                    load_vec(query + pix[j] * d + c, qv);        // the same address in every lane: a broadcast load
-#pragma unroll
-                    for (int i = 0; i < VN; ++i) logit[j] += qv[i] * kv[i];
+                        for (int i = 0; i < VN; ++i) part[j] += qv[i] * kv[i];
+                    }
                 }
             }
+#pragma unroll
+            for (int j = 0; j < NPX; ++j) {
+                part[j] += __shfl_xor_sync(0xffffffffu, part[j], 1);
+                part[j] += __shfl_xor_sync(0xffffffffu, part[j], 2);
+                part[j] += __shfl_xor_sync(0xffffffffu, part[j], 4);
+            }
+            if (sub == 0 && k < KK) {
+#pragma unroll
+                for (int j = 0; j < NPX; ++j) lg[k * NPX + j] = part[j];
+            }
         }
-        // ---- softmax over the K*K slots
+        __syncwarp();
+        // ---- softmax over the K*K slots: lane k owns slot k
         float a[NPX];
 #pragma unroll
         for (int j = 0; j < NPX; ++j) {
-            float m = slot ? logit[j] : -INFINITY;
+            const float x = slot ? lg[lane * NPX + j] : -INFINITY;
+            float m = x;
 #pragma unroll
             for (int sh = 16; sh > 0; sh >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, sh));
-            const float e = slot ? expf(logit[j] - m) : 0.f;
+            const float e = slot ? expf(x - m) : 0.f;
             float z = e;
 #pragma unroll
             for (int sh = 16; sh > 0; sh >>= 1) z += __shfl_xor_sync(0xffffffffu, z, sh);
             a[j] = e / z;
-            if (attn != nullptr && slot) attn[pix[j] * KK + lane] = from_acc<T>(a[j]);
+            if (attn != nullptr && slot) attn[(pix0 + poff[j]) * KK + lane] = from_acc<T>(a[j]);
         }
-        // ---- aggregation: lane l owns VN channels at a time; the weights and the cells come from the slot lanes by shuffle
-        // (the loop bounds are the same in every lane: the shuffles need the whole warp); one value vector serves NPX pixels
-        const T *vimg = value + (size_t)b * H * W * C;
+        __syncwarp();                      // every lane has read its logits
+        if (slot) {
+#pragma unroll
+            for (int j = 0; j < NPX; ++j) lg[lane * NPX + j] = inside ? a[j] : 0.f;
+        }
+        __syncwarp();
+        // ---- aggregation: lane l owns VN channels at a time; the NPX weights of a slot are one broadcast read of the
+        // scratch row, the slot's value vector one 16-byte load per lane (a 512-byte run of the cell per warp); a slot
+        // outside the image reads cell 0 with weight 0, so the loop has no branch
+        T *o0 = out + pix0 * C;
         for (int base = 0; base < C; base += 32 * VN) {
             const int c0 = base + lane * VN;
-            const bool mine = c0 < C;
-            float acc[NPX][VN];
+            if (c0 < C) {
+                const T *vb = vimg + c0;
+                float acc[NPX][VN];
 #pragma unroll
-            for (int j = 0; j < NPX; ++j)
+                for (int j = 0; j < NPX; ++j)
 #pragma unroll
-                for (int i = 0; i < VN; ++i) acc[j][i] = 0.f;
+                    for (int i = 0; i < VN; ++i) acc[j][i] = 0.f;
 #pragma unroll 5
-            for (int k = 0; k < KK; ++k) {
-                const int ck = __shfl_sync(0xffffffffu, cell, k);
-                float ak[NPX];
-#pragma unroll
-                for (int j = 0; j < NPX; ++j) ak[j] = __shfl_sync(0xffffffffu, a[j], k);
-                if (mine && ck >= 0) {
-                    float vv[VN];
-                    load_vec(vimg + (size_t)ck * C + c0, vv);
+                for (int k = 0; k < KK; ++k) {
+                    float vv[VN], ak[NPX];
+                    load_vec(vb + cell_v[k], vv);
+                    if (NPX == 4) {
+                        const float4 w4 = *reinterpret_cast<const float4 *>(lg + k * NPX);
+                        ak[0] = w4.x; ak[1 % NPX] = w4.y; ak[2 % NPX] = w4.z; ak[3 % NPX] = w4.w;
+                    } else {
+                        ak[0] = lg[k];
+                    }
 #pragma unroll
                     for (int j = 0; j < NPX; ++j)
 #pragma unroll
                         for (int i = 0; i < VN; ++i) acc[j][i] += ak[j] * vv[i];
                 }
-            }
-            if (mine) {
 #pragma unroll
-                for (int j = 0; j < NPX; ++j) store_vec(out + pix[j] * C + c0, acc[j]);
+                for (int j = 0; j < NPX; ++j) store_vec(o0 + (poff[j] * C + c0), acc[j]);
             }
         }
     }
@@ -167,7 +212,9 @@ extern "C" int sapa_fused_forward_nhwc(const void *query, const void *key, const
                  "%s: needs kernel_size <= 5 and channel counts that are multiples of %d (16-byte vectors)", fn, vn);
     SAPA_CHECK_PTR(fn, query); SAPA_CHECK_PTR(fn, key); SAPA_CHECK_PTR(fn, value); SAPA_CHECK_PTR(fn, out);
     SAPA_REQUIRE(all_aligned16(query, key, value, out), SAPA_ERR_ALIGNMENT, "%s: tensors must be 16-byte aligned", fn);
-    SAPA_REQUIRE((long long)B * s * H * s * W < (1LL << 40), SAPA_ERR_ARGUMENT, "%s: image too large", fn);
+    SAPA_REQUIRE((long long)B * s * H * s * W < (1LL << 32) && (long long)H * W * (C > d ? C : d) < (1LL << 31) &&
+                     (long long)(s * W + 1) * (C > d ? C : d) < (1LL << 31),
+                 SAPA_ERR_ARGUMENT, "%s: image too large", fn);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool quad = s % 2 == 0;           // 2 x 2 pixel groups never straddle two parents when s is even
     const long long groups = (long long)B * s * H * s * W / (quad ? 4 : 1);
