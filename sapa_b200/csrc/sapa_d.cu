@@ -1099,9 +1099,14 @@ int sapa_deform_qk_forward_dense(const void *query, const void *key, const void 
     }
     const long long total = (long long)B * G * hi;
     return SAPA_DISPATCH_FAST(dtype, [&] {
-        deform_window_kernel<scalar_t, 0, WIN_LOGITS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-            static_cast<const scalar_t *>(query), static_cast<const scalar_t *>(key), static_cast<const scalar_t *>(offset), dense,
-            static_cast<scalar_t *>(out), nullptr, nullptr, nullptr, B, Cq, H, W, P, G, H, 0);
+        if (P == 9)      // the 3 x 3 points of the reference modules' default: loops unrolled for nine points
+            deform_window_kernel<scalar_t, 9, WIN_LOGITS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                static_cast<const scalar_t *>(query), static_cast<const scalar_t *>(key), static_cast<const scalar_t *>(offset), dense,
+                static_cast<scalar_t *>(out), nullptr, nullptr, nullptr, B, Cq, H, W, P, G, H, 0);
+        else
+            deform_window_kernel<scalar_t, 0, WIN_LOGITS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                static_cast<const scalar_t *>(query), static_cast<const scalar_t *>(key), static_cast<const scalar_t *>(offset), dense,
+                static_cast<scalar_t *>(out), nullptr, nullptr, nullptr, B, Cq, H, W, P, G, H, 0);
         return check_launch("deform_window_kernel<logits>");
     });
 }
@@ -1130,9 +1135,14 @@ int sapa_deform_av_forward_dense(const void *attn, const void *value, const void
     const long long total = (long long)B * G * hi;
     // the attention is only read in this mode
     if (int e = SAPA_DISPATCH_FAST(dtype, [&] {
-            deform_window_kernel<scalar_t, 0, WIN_WEIGHTS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-                nullptr, nullptr, static_cast<const scalar_t *>(offset), nullptr, const_cast<scalar_t *>(static_cast<const scalar_t *>(attn)),
-                reinterpret_cast<scalar_t *>(region), taps, tap_count, B, C, H, W, P, G, H, 0);
+            if (P == 9)      // the 3 x 3 points of the reference modules' default: loops unrolled for nine points
+                deform_window_kernel<scalar_t, 9, WIN_WEIGHTS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                    nullptr, nullptr, static_cast<const scalar_t *>(offset), nullptr, const_cast<scalar_t *>(static_cast<const scalar_t *>(attn)),
+                    reinterpret_cast<scalar_t *>(region), taps, tap_count, B, C, H, W, P, G, H, 0);
+            else
+                deform_window_kernel<scalar_t, 0, WIN_WEIGHTS><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                    nullptr, nullptr, static_cast<const scalar_t *>(offset), nullptr, const_cast<scalar_t *>(static_cast<const scalar_t *>(attn)),
+                    reinterpret_cast<scalar_t *>(region), taps, tap_count, B, C, H, W, P, G, H, 0);
             return check_launch("deform_window_kernel<weights>");
         }))
         return e;
@@ -1281,10 +1291,16 @@ int sapa_deform_av_backward_dense(const void *grad_out, const void *attn, const 
     }
     const long long total = (long long)B * G * hi;
     if (int e = SAPA_DISPATCH_FAST(dtype, [&] {
-            deform_window_bwd_kernel<scalar_t, 0, BWD_AV><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-                static_cast<const scalar_t *>(grad_out), static_cast<const scalar_t *>(value), static_cast<const scalar_t *>(offset),
-                static_cast<const scalar_t *>(attn), nullptr, dwin, nullptr, static_cast<scalar_t *>(window),
-                static_cast<scalar_t *>(grad_offset), static_cast<scalar_t *>(grad_attn), taps, tap_count, B, C, H, W, P, G);
+            if (P == 9)      // the 3 x 3 points of the reference modules' default: loops unrolled for nine points
+                deform_window_bwd_kernel<scalar_t, 9, BWD_AV><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                    static_cast<const scalar_t *>(grad_out), static_cast<const scalar_t *>(value), static_cast<const scalar_t *>(offset),
+                    static_cast<const scalar_t *>(attn), nullptr, dwin, nullptr, static_cast<scalar_t *>(window),
+                    static_cast<scalar_t *>(grad_offset), static_cast<scalar_t *>(grad_attn), taps, tap_count, B, C, H, W, P, G);
+            else
+                deform_window_bwd_kernel<scalar_t, 0, BWD_AV><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                    static_cast<const scalar_t *>(grad_out), static_cast<const scalar_t *>(value), static_cast<const scalar_t *>(offset),
+                    static_cast<const scalar_t *>(attn), nullptr, dwin, nullptr, static_cast<scalar_t *>(window),
+                    static_cast<scalar_t *>(grad_offset), static_cast<scalar_t *>(grad_attn), taps, tap_count, B, C, H, W, P, G);
             return check_launch("deform_window_bwd_kernel<av>");
         }))
         return e;
@@ -1344,9 +1360,14 @@ int sapa_deform_qk_backward_dense(const void *grad_out, const void *query, const
     const long long total = (long long)B * G * hi;
     // the logit gradients enter where the fused chain reads the attention
     if (int e = SAPA_DISPATCH_FAST(dtype, [&] {
-            deform_window_bwd_kernel<scalar_t, 0, BWD_QK><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
-                nullptr, nullptr, static_cast<const scalar_t *>(offset), static_cast<const scalar_t *>(grad_out), dense, nullptr,
-                static_cast<scalar_t *>(ddense), nullptr, static_cast<scalar_t *>(grad_offset), nullptr, taps, tap_count, B, Cq, H, W, P, G);
+            if (P == 9)      // the 3 x 3 points of the reference modules' default: loops unrolled for nine points
+                deform_window_bwd_kernel<scalar_t, 9, BWD_QK><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                    nullptr, nullptr, static_cast<const scalar_t *>(offset), static_cast<const scalar_t *>(grad_out), dense, nullptr,
+                    static_cast<scalar_t *>(ddense), nullptr, static_cast<scalar_t *>(grad_offset), nullptr, taps, tap_count, B, Cq, H, W, P, G);
+            else
+                deform_window_bwd_kernel<scalar_t, 0, BWD_QK><<<grid_1d(total, WIN_THREADS), WIN_THREADS, 0, st>>>(
+                    nullptr, nullptr, static_cast<const scalar_t *>(offset), static_cast<const scalar_t *>(grad_out), dense, nullptr,
+                    static_cast<scalar_t *>(ddense), nullptr, static_cast<scalar_t *>(grad_offset), nullptr, taps, tap_count, B, Cq, H, W, P, G);
             return check_launch("deform_window_bwd_kernel<qk>");
         }))
         return e;
