@@ -90,6 +90,9 @@ sapa_nhwc_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, con
     int poff[NPX];                                           // pixel j of a group relative to its first pixel
 #pragma unroll
     for (int j = 0; j < NPX; ++j) poff[j] = (j / PW) * sW + j % PW;
+    int qoff[NPX];                                           // the same in elements of the query tensor
+#pragma unroll
+    for (int j = 0; j < NPX; ++j) qoff[j] = poff[j] * d;
     for (unsigned gi = warp0; gi < groups; gi += nwarps) {
         const int gx = (int)(gi % (unsigned)gw), gy = (int)((gi / (unsigned)gw) % (unsigned)gh), b = (int)(gi / ((unsigned)gw * gh));
         const int qh0 = gy * PW, qw0 = gx * PW, ph = qh0 / s, pw = qw0 / s;      // the group lies inside one parent
@@ -106,6 +109,7 @@ sapa_nhwc_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, con
         __syncwarp();
         // ---- logits: the key vector of a slot is read by eight lanes, 16 bytes each (one 128-byte line per slot and
         // load), the partial dot products are added over the eight lanes; a slot outside the image has logit exactly 0
+        const T *qs = q0 + sub * VN;           // this lane's 16 bytes of the first query vector
         for (int k0 = 0; k0 < KK; k0 += 4) {
             const int k = k0 + quarter;
             const int cell = k < KK ? cell_k[k] : -1;
@@ -113,14 +117,14 @@ sapa_nhwc_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, con
 #pragma unroll
             for (int j = 0; j < NPX; ++j) part[j] = 0.f;
             if (cell >= 0) {
-                const T *kp = kimg + cell;
-                for (int c = sub * VN; c < d; c += 8 * VN) {
+                const T *kp = kimg + cell + sub * VN;
+                for (int c = 0; c < d - sub * VN; c += 8 * VN) {
                     float kv[VN];
                     load_vec(kp + c, kv);
 #pragma unroll
                     for (int j = 0; j < NPX; ++j) {
                         float qv[VN];
-                        load_vec(q0 + (poff[j] * d + c), qv);
+                        load_vec(qs + (qoff[j] + c), qv);
 #pragma unroll
                         for (int i = 0; i < VN; ++i) part[j] += qv[i] * kv[i];
                     }
