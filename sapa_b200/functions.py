@@ -161,14 +161,7 @@ def sapa_fused(query, key, value, kernel_size=5, scale_factor=2):
     return SapaFusedFunction.apply(query, key, value, kernel_size, scale_factor)
 
 
-def sapa_fused_nhwc(query, key, value, kernel_size=5, scale_factor=2, return_attn=False):
-    """Fused SAPA-B forward on channels-last tensors: ``query`` [B, sH, sW, d], ``key`` [B, H, W, d], ``value``
-    [B, H, W, C] -> [B, sH, sW, C] (plus the attention [B, sH, sW, K*K] when ``return_attn``).  Forward only: for
-    gradients use the channels-first ops.  The reference has no channels-last path."""
-    if not value.is_cuda:
-        raise NotImplementedError
-    if torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value)):
-        raise NotImplementedError("sapa_fused_nhwc is forward only; use sapa_fused (channels-first) for training")
+def _nhwc_forward(query, key, value, kernel_size, scale_factor, return_attn):
     _lib.check_tensors(("value", value), ("query", query), ("key", key))
     n, hq, wq, d = query.shape
     h, w, c = value.shape[1:]
@@ -178,4 +171,47 @@ def sapa_fused_nhwc(query, key, value, kernel_size=5, scale_factor=2, return_att
     attn = torch.empty((n, hq, wq, kernel_size ** 2), dtype=value.dtype, device=value.device) if return_attn else None
     _lib.call("sapa_fused_forward_nhwc", value.device, query, key, value, out, attn, n, d, c, h, w, kernel_size, scale_factor,
               _lib.dtype_code(value))
-    return (out, attn) if return_attn else out
+    return out, attn
+
+
+class _SapaFusedNhwcFunction(Function):
+    """Channels-last forward kernel; the backward goes through the channels-first kernels: the saved tensors and the
+    incoming gradient are permuted to [B, C, H, W], the fused forward is run again there for its attention map, the
+    fused backward follows, and the three gradients are permuted back (five layout copies and one forward more than a
+    native channels-last backward would need)."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, kernel_size, scale_factor):
+        out, _ = _nhwc_forward(query, key, value, kernel_size, scale_factor, False)
+        if any(ctx.needs_input_grad[:3]):
+            ctx.cfg = (kernel_size, scale_factor)
+            ctx.save_for_backward(query, key, value)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        query, key, value = ctx.saved_tensors
+        kernel_size, scale_factor = ctx.cfg
+        first = [t.detach().permute(0, 3, 1, 2).contiguous().requires_grad_() for t in (query, key, value)]
+        with torch.enable_grad():
+            out = SapaFusedFunction.apply(first[0], first[1], first[2], kernel_size, scale_factor)
+        grads = torch.autograd.grad(out, first, grad_out.permute(0, 3, 1, 2).contiguous())
+        gq, gk, gv = (g.permute(0, 2, 3, 1).contiguous() for g in grads)
+        return gq, gk, gv, None, None
+
+
+def sapa_fused_nhwc(query, key, value, kernel_size=5, scale_factor=2, return_attn=False):
+    """Fused SAPA-B on channels-last tensors: ``query`` [B, sH, sW, d], ``key`` [B, H, W, d], ``value`` [B, H, W, C] ->
+    [B, sH, sW, C] (plus the attention [B, sH, sW, K*K] when ``return_attn``, which is not differentiable).  The forward
+    is the channels-last kernel; gradients are computed by the channels-first kernels around layout copies (see
+    ``_SapaFusedNhwcFunction``).  The reference has no channels-last path."""
+    if not value.is_cuda:
+        raise NotImplementedError
+    needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value))
+    if return_attn:
+        if needs_grad:
+            raise NotImplementedError("sapa_fused_nhwc(return_attn=True) is forward only")
+        return _nhwc_forward(query, key, value, kernel_size, scale_factor, True)
+    if needs_grad:
+        return _SapaFusedNhwcFunction.apply(query, key, value, kernel_size, scale_factor)
+    return _nhwc_forward(query, key, value, kernel_size, scale_factor, False)[0]

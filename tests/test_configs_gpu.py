@@ -324,4 +324,13 @@ def test_channels_last_forward_matches_channels_first(shape, dtype, tol, oracle)
         ref_out, ref_attn = fused_forward_raw(q.to(dev), k.to(dev), v.to(dev), K, s, True)
         assert float((attn.permute(0, 3, 1, 2).float() - ref_attn.float()).abs().max()) < (1e-5 if dtype == torch.float32 else 1e-2)
     with pytest.raises(NotImplementedError):
-        sapa_b200.sapa_fused_nhwc(ql.requires_grad_(), kl, vl, K, s)
+        sapa_b200.sapa_fused_nhwc(ql.clone().requires_grad_(), kl, vl, K, s, return_attn=True)
+    # gradients: the channels-last forward with the channels-first backward behind it, against the channels-first op
+    if sapa_b200.functions.fused_supported(K, s, dtype):
+        go = torch.randn(B, s * H, s * W, C, generator=g).to(dtype).to(dev)
+        a = [t.clone().requires_grad_() for t in (ql, kl, vl)]
+        got = torch.autograd.grad(sapa_b200.sapa_fused_nhwc(*a, K, s), a, go)
+        b = [t.to(dev).requires_grad_() for t in (q, k, v)]
+        ref = torch.autograd.grad(sapa_b200.sapa_fused(*b, K, s), b, go.permute(0, 3, 1, 2).contiguous())
+        for x, y in zip(got, ref):
+            assert x.shape == y.permute(0, 2, 3, 1).shape and torch.equal(x, y.permute(0, 2, 3, 1))
