@@ -70,10 +70,11 @@ __device__ __forceinline__ void store_vec(__nv_bfloat16 *p, const float (&v)[8])
 // padding); cell_k / cell_v = element offset of the slot's cell in the key / value image, -1 / 0 outside the image.
 // Addresses are one 64-bit base per tensor and group plus 32-bit offsets: an image of any one tensor must hold fewer
 // than 2^31 elements (checked by the entry point).
-template <typename T, int NPX>
-__global__ void __launch_bounds__(WARPS * 32, sizeof(T) == 4 ? 5 : 3)
+template <typename T, int NPX, int KFIX>     // KFIX: kernel_size known at compile time (0: read K at run time)
+__global__ void __launch_bounds__(WARPS * 32, sizeof(T) == 4 ? 4 : 3)
 sapa_nhwc_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ value, T *__restrict__ out,
-                     T *__restrict__ attn, int B, int d, int C, int H, int W, int K, int s) {
+                     T *__restrict__ attn, int B, int d, int C, int H, int W, int K_runtime, int s) {
+    const int K = KFIX > 0 ? KFIX : K_runtime;
     constexpr int VN = Vec<T>::N;
     constexpr int PW = NPX == 4 ? 2 : 1;             // pixel group = PW x PW
     __shared__ __align__(16) float lg_all[WARPS][32 * NPX];
@@ -176,7 +177,7 @@ sapa_nhwc_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, con
                 for (int j = 0; j < NPX; ++j)
 #pragma unroll
                     for (int i = 0; i < VN; ++i) acc[j][i] = 0.f;
-#pragma unroll 5
+#pragma unroll (KFIX > 0 ? KFIX * KFIX : 5)
                 for (int k = 0; k < KK; ++k) {
                     float vv[VN], ak[NPX];
                     load_vec(vb + cell_v[k], vv);
@@ -228,8 +229,9 @@ extern "C" int sapa_fused_forward_nhwc(const void *query, const void *key, const
         const scalar_t *q = static_cast<const scalar_t *>(query), *k = static_cast<const scalar_t *>(key);
         const scalar_t *v = static_cast<const scalar_t *>(value);
         scalar_t *o = static_cast<scalar_t *>(out), *at = static_cast<scalar_t *>(attn);
-        if (quad) nhwc::sapa_nhwc_fwd_kernel<scalar_t, 4><<<grid, nhwc::WARPS * 32, 0, st>>>(q, k, v, o, at, B, d, C, H, W, K, s);
-        else nhwc::sapa_nhwc_fwd_kernel<scalar_t, 1><<<grid, nhwc::WARPS * 32, 0, st>>>(q, k, v, o, at, B, d, C, H, W, K, s);
+        if (quad && K == 5) nhwc::sapa_nhwc_fwd_kernel<scalar_t, 4, 5><<<grid, nhwc::WARPS * 32, 0, st>>>(q, k, v, o, at, B, d, C, H, W, K, s);
+        else if (quad) nhwc::sapa_nhwc_fwd_kernel<scalar_t, 4, 0><<<grid, nhwc::WARPS * 32, 0, st>>>(q, k, v, o, at, B, d, C, H, W, K, s);
+        else nhwc::sapa_nhwc_fwd_kernel<scalar_t, 1, 0><<<grid, nhwc::WARPS * 32, 0, st>>>(q, k, v, o, at, B, d, C, H, W, K, s);
         return check_launch("sapa_nhwc_fwd_kernel");
     });
 }
