@@ -111,6 +111,7 @@ sapa_nhwc_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, con
         // ---- logits: the key vector of a slot is read by eight lanes, 16 bytes each (one 128-byte line per slot and
         // load), the partial dot products are added over the eight lanes; a slot outside the image has logit exactly 0
         const T *qs = q0 + sub * VN;           // this lane's 16 bytes of the first query vector
+#pragma unroll (KFIX > 0 && sizeof(T) == 2 ? (KFIX * KFIX + 3) / 4 : 1)      // float32 is short of registers here
         for (int k0 = 0; k0 < KK; k0 += 4) {
             const int k = k0 + quarter;
             const int cell = k < KK ? cell_k[k] : -1;
