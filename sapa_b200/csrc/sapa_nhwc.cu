@@ -71,7 +71,7 @@ __device__ __forceinline__ void store_vec(__nv_bfloat16 *p, const float (&v)[8])
 // Addresses are one 64-bit base per tensor and group plus 32-bit offsets: an image of any one tensor must hold fewer
 // than 2^31 elements (checked by the entry point).
 template <typename T, int NPX, int KFIX>     // KFIX: kernel_size known at compile time (0: read K at run time)
-__global__ void __launch_bounds__(WARPS * 32, sizeof(T) == 4 ? 4 : 3)
+__global__ void __launch_bounds__(WARPS * 32, 4)
 sapa_nhwc_fwd_kernel(const T *__restrict__ query, const T *__restrict__ key, const T *__restrict__ value, T *__restrict__ out,
                      T *__restrict__ attn, int B, int d, int C, int H, int W, int K_runtime, int s) {
     const int K = KFIX > 0 ? KFIX : K_runtime;
