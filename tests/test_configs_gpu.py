@@ -265,21 +265,24 @@ def test_deform_16bit_separate_ops_through_the_window(sp, dtype, tol):
     assert _lib.wait_timeout_flags(torch.device(DEV)) == 0
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
 @pytest.mark.parametrize("sigma,halo", [(0.5, None), (1.5, None), (0.2, 2)])
-def test_deform_row_slabs_with_halos_equal_the_unsharded_rows(sp, sigma, halo):
+def test_deform_row_slabs_with_halos_equal_the_unsharded_rows(sp, sigma, halo, dtype, tol):
     """sapa_deform_fused_forward_slab on three row slabs of one image (key / value padded with the neighbours' rows, zeros
     at the image's top and bottom; halo depth from max |offset_y|, or a given bound) against the unsharded fused op:
     far points included (sigma = 1.5 sends a quarter of the points out of the 5 x 5 window)."""
     from sapa_b200 import _lib, sharding
     B, d, C, H, W, G, P, s = 2, 32, 64, 36, 24, 4, 9, 2
     g = torch.Generator(device=DEV).manual_seed(41)
-    q = torch.randn(B, d, s * H, s * W, generator=g, device=DEV)
-    k = torch.randn(B, d, H, W, generator=g, device=DEV)
-    v = torch.randn(B, C, H, W, generator=g, device=DEV)
+    q = torch.randn(B, d, s * H, s * W, generator=g, device=DEV).to(dtype)
+    k = torch.randn(B, d, H, W, generator=g, device=DEV).to(dtype)
+    v = torch.randn(B, C, H, W, generator=g, device=DEV).to(dtype)
     off = sigma * torch.randn(B, 2 * G * P, s * H, s * W, generator=g, device=DEV)
     if halo is not None:
-        off = off.clamp(-halo + 0.01, halo - 0.01)
+        off = off.clamp(-halo + 0.05, halo - 0.05)
+    off = off.to(dtype)
     full = sp.deform_sapa_fused(q, k, v, off, P, s, G)
+    code = _lib.dtype_code(q)
     depth = sharding.deform_halo_rows(off) if halo is None else halo
     assert depth >= int(off[:, 1::2].abs().max()) + 1 and (halo is not None or depth == int(off[:, 1::2].abs().max()) + 1)
     hl = H // 3
@@ -291,13 +294,13 @@ def test_deform_row_slabs_with_halos_equal_the_unsharded_rows(sp, sigma, halo):
         ks = kp[:, :, r * hl:(r + 1) * hl + 2 * depth].contiguous()
         vs = vp[:, :, r * hl:(r + 1) * hl + 2 * depth].contiguous()
         qs, os_ = q[:, :, hi].contiguous(), off[:, :, hi].contiguous()
-        nbytes = int(_lib.lib().sapa_deform_fused_forward_workspace(B, hl, W, P, s, G, _lib.SAPA_F32))
+        nbytes = int(_lib.lib().sapa_deform_fused_forward_workspace(B, hl, W, P, s, G, code))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
-        out = torch.empty(B, C, s * hl, s * W, device=DEV)
+        out = torch.empty(B, C, s * hl, s * W, device=DEV, dtype=dtype)
         _lib.call("sapa_deform_fused_forward_slab", q.device, qs, ks, vs, os_, out, None, ws, nbytes, B, d, C, hl, W, depth, depth,
-                  P, s, G, _lib.SAPA_F32)
+                  P, s, G, code)
         assert "deform_window_kernel" in _lib.last_kernels()
-        assert rel_err(f32(out), f32(full[:, :, hi])) < 1e-5, r
+        assert rel_err(f32(out), f32(full[:, :, hi])) < tol, r
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2), (torch.float16, 2e-3)])
