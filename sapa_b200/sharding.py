@@ -414,19 +414,21 @@ class DeformRowSlab:
     and the step stays asynchronous), and runs the slab form of the dense-window kernels on the rank's own query /
     offset rows.  Every rank must own at least ``max_halo`` rows (checked once, here, on all ranks together); a step
     whose depth exceeds ``max_halo`` raises ``ValueError`` on every rank (the depth is the same everywhere).
-    float32, scale factor 2 (the dense-window kernels).  The reference has no multi-device code.
+    Scale factor 2; float32, or float16 / bfloat16 with rows of 16 bytes (the dense-window kernels).  The reference has
+    no multi-device code.
     """
 
     def __init__(self, batch, channels_qk, channels_v, local_rows, width, max_halo, device, num_point=9, groups=4,
-                 group=None):
+                 group=None, dtype=torch.float32):
         if max_halo < 2:
             raise ValueError("max_halo must be at least 2 (the 5 x 5 window of the dense similarity)")
         check_row_split(local_rows, max_halo, group)
         self.group, self.cap, self.rows, self.width = group, int(max_halo), int(local_rows), int(width)
         self.num_point, self.groups = num_point, groups
         rows = local_rows + 2 * self.cap
-        self.key_padded = torch.zeros((batch, channels_qk, rows, width), dtype=torch.float32, device=device)
-        self.value_padded = torch.zeros((batch, channels_v, rows, width), dtype=torch.float32, device=device)
+        self.dtype = dtype
+        self.key_padded = torch.zeros((batch, channels_qk, rows, width), dtype=dtype, device=device)
+        self.value_padded = torch.zeros((batch, channels_v, rows, width), dtype=dtype, device=device)
         self.key = self.key_padded[:, :, self.cap:self.cap + local_rows, :]
         self.value = self.value_padded[:, :, self.cap:self.cap + local_rows, :]
         self._workspace = None
@@ -444,13 +446,14 @@ class DeformRowSlab:
             lo, hi = self.cap - depth, self.cap + Hl + depth
             _exchange_into([self.key_padded[:, :, lo:hi, :], self.value_padded[:, :, lo:hi, :]], depth, self.group)
         _lib.check_tensors(("query", query), ("key", self.key_padded), ("value", self.value_padded), ("offset", offset))
-        nbytes = int(_lib.lib().sapa_deform_fused_forward_workspace(B, Hl, W, P, s, G, _lib.SAPA_F32))
+        code = _lib.dtype_code(self.key_padded)
+        nbytes = int(_lib.lib().sapa_deform_fused_forward_workspace(B, Hl, W, P, s, G, code))
         if nbytes == 0:
-            raise RuntimeError("DeformRowSlab needs float32, at most 16 points and rows of 16 bytes")
+            raise RuntimeError("DeformRowSlab needs float32 (or float16 / bfloat16 with rows of 16 bytes) and at most 16 points")
         if self._workspace is None or self._workspace.numel() < nbytes:
             self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=query.device)
         if out is None:
-            out = torch.empty((B, C, s * Hl, s * W), dtype=torch.float32, device=query.device)
+            out = torch.empty((B, C, s * Hl, s * W), dtype=self.dtype, device=query.device)
         _lib.call("sapa_deform_fused_forward_slab", query.device, query, self.key_padded, self.value_padded, offset, out, None,
-                  self._workspace, nbytes, B, d, C, Hl, W, self.cap, self.cap, P, s, G, _lib.SAPA_F32)
+                  self._workspace, nbytes, B, d, C, Hl, W, self.cap, self.cap, P, s, G, code)
         return out

@@ -120,6 +120,13 @@ def _worker_deform(rank, world, port, ret):
             ok = False
         except ValueError:
             pass
+        # the same in bfloat16 (16-bit operands, float32 similarities), against the unsharded bfloat16 op
+        h = [t.detach().to(torch.bfloat16) for t in (q, k, v, off)]
+        full16 = sapa_b200.deform_sapa_fused(*h, P, s, G)
+        slab16 = sharding.DeformRowSlab(B, d, C, rows.stop - rows.start, W, depth + 2, dev, P, G, dtype=torch.bfloat16)
+        slab16.key.copy_(h[1][:, :, rows]); slab16.value.copy_(h[2][:, :, rows])
+        got16 = slab16.forward(h[0][:, :, hi].contiguous(), h[3][:, :, hi].contiguous())
+        ok = ok and got16.dtype == torch.bfloat16 and close(got16.float(), full16[:, :, hi].float(), 1e-2)
         for got, want, sl in zip(mine_grads, grads, (hi, rows, rows, hi)):
             ok = ok and close(got, want[:, :, sl])
         ret[rank] = ok
